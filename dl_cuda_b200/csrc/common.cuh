@@ -1,0 +1,130 @@
+// Shared device/host helpers for the sm_100a layer kernels: 16-byte vector
+// access with streaming cache hints, storage-type traits (fp32 / bf16 storage,
+// fp32 arithmetic), warp reductions, and the status/launch bookkeeping that
+// the C ABI reports through.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/dlcuda_b200.h"
+
+namespace dlb {
+
+// ---------------------------------------------------------------- host side
+void set_error(const char *fmt, ...);
+extern std::atomic<uint64_t> g_launches;
+int sm_count();  // SMs of the current device (cached per device)
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline bool aligned16(const void *p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+// Every launch goes through this: counts it and turns a launch error into a
+// status instead of leaving it for the next runtime call to trip over.
+#define DLB_LAUNCH_CHECK(name)                                                  \
+  do {                                                                          \
+    ::dlb::g_launches.fetch_add(1, std::memory_order_relaxed);                  \
+    cudaError_t e__ = cudaGetLastError();                                       \
+    if (e__ != cudaSuccess) {                                                   \
+      ::dlb::set_error("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+      return DLB_ERR_CUDA;                                                      \
+    }                                                                           \
+  } while (0)
+
+#define DLB_REQUIRE(cond, status, ...) \
+  do {                                 \
+    if (!(cond)) {                     \
+      ::dlb::set_error(__VA_ARGS__);   \
+      return status;                   \
+    }                                  \
+  } while (0)
+
+template <typename T>
+inline T ceil_div(T a, T b) {
+  return (a + b - 1) / b;
+}
+
+// -------------------------------------------------------------- device side
+constexpr int kWarp = 32;
+
+// Storage traits: a 16-byte vector holds kPerVec elements of storage type T.
+template <typename T>
+struct Store;
+
+template <>
+struct Store<float> {
+  static constexpr int kPerVec = 4;
+  __device__ __forceinline__ static void unpack(const uint4 &v, float (&f)[4]) {
+    f[0] = __uint_as_float(v.x);
+    f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z);
+    f[3] = __uint_as_float(v.w);
+  }
+  __device__ __forceinline__ static uint4 pack(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]),
+                      __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+  __device__ __forceinline__ static float to_float(float v) { return v; }
+  __device__ __forceinline__ static float from_float(float v) { return v; }
+};
+
+template <>
+struct Store<__nv_bfloat16> {
+  static constexpr int kPerVec = 8;
+  __device__ __forceinline__ static void unpack(const uint4 &v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      // bf16 -> fp32 is a 16-bit shift; the low half of the word is element 2i.
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ __forceinline__ static uint4 pack(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t *>(&p);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ __forceinline__ static float to_float(__nv_bfloat16 v) {
+    return __bfloat162float(v);
+  }
+  __device__ __forceinline__ static __nv_bfloat16 from_float(float v) {
+    return __float2bfloat16_rn(v);
+  }
+};
+
+// Streaming (touch-once) 16-byte accesses: evict-first in L1/L2 so that the
+// small reused operands (gamma, beta, bias, PE rows, hot table rows) stay put.
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+  return __ldcs(reinterpret_cast<const uint4 *>(p));
+}
+__device__ __forceinline__ void st_stream(void *p, const uint4 &v) {
+  __stcs(reinterpret_cast<uint4 *>(p), v);
+}
+// Read-only, cached 16-byte access for operands that are reused across rows.
+__device__ __forceinline__ uint4 ld_keep(const void *p) {
+  return __ldg(reinterpret_cast<const uint4 *>(p));
+}
+__device__ __forceinline__ float4 ld_keep_f4(const float *p) {
+  return __ldg(reinterpret_cast<const float4 *>(p));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+}  // namespace dlb

@@ -1,0 +1,654 @@
+// Token embedding for sm_100a: the gather with the sinusoidal positional-
+// encoding add folded in, and the gradient of the table as a deterministic
+// sorted-segment sum (no atomics, no memset).
+//
+// Backward in three steps.
+//  1. dlb_embed_sort_tokens: a stable LSD radix sort of (id, token index) pairs
+//     (8-bit digits, 2048-token tiles, warp match-any ranking), then per id the
+//     start of its run in the sorted list (binary search), then the list of
+//     "long" ids (more than kSubLen tokens) with their sub-segment offsets.
+//  2. scatter_rows_kernel: one thread group per table row.  A row with at most
+//     kSubLen tokens is summed in ascending token order and written once (zero
+//     if no token refers to it).  Long rows are cut into sub-segments of
+//     kSubLen tokens, each summed by its own thread group into a scratch row.
+//  3. combine_long_kernel: adds a long row's scratch rows in sub-segment order.
+// The order of every addition is a function of ids alone, so two runs give the
+// same bits whatever the scheduling.
+#include "common.cuh"
+
+namespace dlb {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kSubLen = 32;  // tokens per sub-segment of a long row
+
+// ------------------------------------------------------------------ gather
+// blockDim = (tx, ty): tx threads cover tx column vectors, ty positions per
+// CTA.  A thread keeps the PE vector of its (position, column) and walks the
+// tokens that share the position (t = s, s+S, s+2S, ...), four gathers in flight.
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+embed_gather_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids,
+                    const float *__restrict__ pe, T *__restrict__ out, int num_tokens, int vocab,
+                    int d, int stride_s) {
+  using S = Store<T>;
+  constexpr int E = S::kPerVec;
+  constexpr int U = 4;
+  const int ncv = d / E;
+  const int cv = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.y * blockDim.y + threadIdx.y;
+  if (cv >= ncv || s >= stride_s) return;
+
+  float pv[E];
+#pragma unroll
+  for (int e = 0; e < E; e++) pv[e] = 0.f;
+  if (pe != nullptr) {
+#pragma unroll
+    for (int q = 0; q < E / 4; q++) {
+      const float4 p4 = ld_keep_f4(pe + static_cast<size_t>(s) * d + cv * E + 4 * q);
+      pv[4 * q] = p4.x; pv[4 * q + 1] = p4.y; pv[4 * q + 2] = p4.z; pv[4 * q + 3] = p4.w;
+    }
+  }
+  for (int t0 = s; t0 < num_tokens; t0 += U * stride_s) {
+    uint4 row[U];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int t = t0 + u * stride_s;
+      ok[u] = t < num_tokens;
+      if (ok[u]) {
+        int id = __ldg(ids + t);
+        id = max(0, min(id, vocab - 1));  // out-of-range ids cannot leave the table
+        row[u] = ld_keep(table + static_cast<size_t>(id) * d + cv * E);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      if (ok[u]) {
+        float v[E];
+        S::unpack(row[u], v);
+#pragma unroll
+        for (int e = 0; e < E; e++) v[e] = v[e] + pv[e];
+        const size_t t = static_cast<size_t>(t0) + static_cast<size_t>(u) * stride_s;
+        st_stream(out + t * d + cv * E, S::pack(v));
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+embed_gather_scalar_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids,
+                           const float *__restrict__ pe, T *__restrict__ out, int num_tokens,
+                           int vocab, int d, int seq_len) {
+  using S = Store<T>;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x;
+  if (i >= static_cast<int64_t>(num_tokens) * d) return;
+  const int t = static_cast<int>(i / d), c = static_cast<int>(i % d);
+  int id = ids[t];
+  id = max(0, min(id, vocab - 1));
+  float v = S::to_float(table[static_cast<size_t>(id) * d + c]);
+  if (pe != nullptr) v = v + pe[static_cast<size_t>(t % seq_len) * d + c];
+  out[i] = S::from_float(v);
+}
+
+// -------------------------------------------------------------------- sort
+constexpr int kSortItems = 8;                        // keys per thread
+constexpr int kSortTile = kBlock * kSortItems;       // 2048 tokens per CTA
+constexpr int kDigits = 256;
+
+__global__ void __launch_bounds__(kBlock)
+sort_hist_kernel(const uint32_t *__restrict__ keys, int n, int shift, int nblocks,
+                 int32_t *__restrict__ block_hist) {
+  __shared__ int hist[kDigits];
+  hist[threadIdx.x] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * kSortTile;
+#pragma unroll
+  for (int j = 0; j < kSortItems; j++) {
+    const int i = base + j * kBlock + threadIdx.x;
+    if (i < n) atomicAdd(&hist[(keys[i] >> shift) & 255u], 1);  // integer counts: order-free
+  }
+  __syncthreads();
+  block_hist[threadIdx.x * nblocks + blockIdx.x] = hist[threadIdx.x];
+}
+
+// Exclusive scan of `data[0..n)` in place by one CTA of 1024 threads: thread i
+// owns a contiguous chunk.  Returns (to every thread) the total.
+__device__ int cta_exclusive_scan_inplace(int32_t *data, int n, int *smem /*[33]*/) {
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int per = (n + nthreads - 1) / nthreads;
+  const int b = min(n, tid * per), e = min(n, b + per);
+  int sum = 0;
+  for (int i = b; i < e; i++) sum += data[i];
+  // exclusive scan of the per-thread sums
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if ((tid & 31) >= o) incl += t;
+  }
+  __syncthreads();
+  if ((tid & 31) == 31) smem[tid >> 5] = incl;
+  __syncthreads();
+  if (tid < 32) {
+    const int nw = nthreads >> 5;
+    int w = tid < nw ? smem[tid] : 0;
+    int wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (tid >= o) wi += t;
+    }
+    smem[tid] = wi - w;  // exclusive warp offsets
+    if (tid == 31) smem[32] = wi;
+  }
+  __syncthreads();
+  int run = smem[tid >> 5] + incl - sum;
+  const int total = smem[32];
+  for (int i = b; i < e; i++) {
+    const int v = data[i];
+    data[i] = run;
+    run += v;
+  }
+  return total;
+}
+
+__global__ void __launch_bounds__(1024) scan_inplace_kernel(int32_t *data, int n) {
+  __shared__ int smem[33];
+  cta_exclusive_scan_inplace(data, n, smem);
+}
+
+// Stable scatter of one radix pass.  Items are taken in index order: warp w,
+// round j, lane l holds item tile + (w*8+j)*32 + l; its rank among equal digits
+// is (digits in earlier warps) + (earlier rounds of this warp) + (lower lanes).
+__global__ void __launch_bounds__(kBlock)
+sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const int32_t *__restrict__ vals_in,
+                    uint32_t *__restrict__ keys_out, int32_t *__restrict__ vals_out, int n,
+                    int shift, int nblocks, const int32_t *__restrict__ block_base) {
+  constexpr int kWarps = kBlock / 32;
+  __shared__ int cnt[kWarps][kDigits];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kWarps * kDigits; i += kBlock) (&cnt[0][0])[i] = 0;
+  __syncthreads();
+
+  uint32_t key[kSortItems];
+  int32_t val[kSortItems];
+  int rank[kSortItems];
+  const int base = blockIdx.x * kSortTile + warp * (kSortItems * 32);
+#pragma unroll
+  for (int j = 0; j < kSortItems; j++) {
+    const int i = base + j * 32 + lane;
+    const bool ok = i < n;
+    key[j] = ok ? keys_in[i] : 0u;
+    val[j] = ok ? (vals_in ? vals_in[i] : i) : -1;
+    const uint32_t digit = ok ? ((key[j] >> shift) & 255u) : 256u;  // 256: padding lanes
+    const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+    const int below = __popc(peers & ((1u << lane) - 1u));
+    int prev = 0;
+    if (ok) prev = cnt[warp][digit];
+    __syncwarp();
+    if (ok && below == 0) cnt[warp][digit] = prev + __popc(peers);
+    __syncwarp();
+    rank[j] = prev + below;
+  }
+  __syncthreads();
+  {
+    const int dgt = threadIdx.x;  // kBlock == kDigits
+    int run = block_base[dgt * nblocks + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < kWarps; w++) {
+      const int c = cnt[w][dgt];
+      cnt[w][dgt] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kSortItems; j++) {
+    if (val[j] >= 0) {
+      const int pos = cnt[warp][(key[j] >> shift) & 255u] + rank[j];
+      keys_out[pos] = key[j];
+      vals_out[pos] = val[j];
+    }
+  }
+}
+
+// seg_start[v] = first position in the sorted keys whose key is >= v, v in [0,V].
+__global__ void __launch_bounds__(kBlock)
+segment_start_kernel(const uint32_t *__restrict__ sorted_keys, int n, int vocab,
+                     int32_t *__restrict__ seg_start) {
+  const int v = blockIdx.x * kBlock + threadIdx.x;
+  if (v > vocab) return;
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (sorted_keys[mid] < static_cast<uint32_t>(v)) lo = mid + 1; else hi = mid;
+  }
+  seg_start[v] = lo;
+}
+
+// One CTA: lists the long rows (more than kSubLen tokens) in ascending id with
+// the exclusive prefix of their sub-segment counts.  meta = {n_long, n_sub}.
+__global__ void __launch_bounds__(1024)
+plan_long_rows_kernel(const int32_t *__restrict__ seg_start, int vocab,
+                      int32_t *__restrict__ long_row, int32_t *__restrict__ long_first,
+                      int32_t *__restrict__ meta) {
+  __shared__ int wsum[2][33];
+  const int tid = threadIdx.x;
+  const int per = (vocab + 1023) / 1024;
+  const int b = min(vocab, tid * per), e = min(vocab, b + per);
+  int nl = 0, ns = 0;
+  for (int v = b; v < e; v++) {
+    const int c = seg_start[v + 1] - seg_start[v];
+    if (c > kSubLen) { nl++; ns += (c + kSubLen - 1) / kSubLen; }
+  }
+  int il = nl, is = ns;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int tl = __shfl_up_sync(0xffffffffu, il, o);
+    const int ts = __shfl_up_sync(0xffffffffu, is, o);
+    if ((tid & 31) >= o) { il += tl; is += ts; }
+  }
+  if ((tid & 31) == 31) { wsum[0][tid >> 5] = il; wsum[1][tid >> 5] = is; }
+  __syncthreads();
+  if (tid < 32) {
+    const int wl = wsum[0][tid], ws = wsum[1][tid];
+    int xl = wl, xs = ws;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int tl = __shfl_up_sync(0xffffffffu, xl, o);
+      const int ts = __shfl_up_sync(0xffffffffu, xs, o);
+      if (tid >= o) { xl += tl; xs += ts; }
+    }
+    wsum[0][tid] = xl - wl; wsum[1][tid] = xs - ws;
+    if (tid == 31) { wsum[0][32] = xl; wsum[1][32] = xs; }
+  }
+  __syncthreads();
+  int li = wsum[0][tid >> 5] + il - nl;
+  int si = wsum[1][tid >> 5] + is - ns;
+  for (int v = b; v < e; v++) {
+    const int c = seg_start[v + 1] - seg_start[v];
+    if (c > kSubLen) {
+      long_row[li] = v;
+      long_first[li] = si;
+      li++;
+      si += (c + kSubLen - 1) / kSubLen;
+    }
+  }
+  if (tid == 0) {
+    meta[0] = wsum[0][32];
+    meta[1] = wsum[1][32];
+    long_first[wsum[0][32]] = wsum[1][32];
+  }
+}
+
+// ---------------------------------------------------------------- scatter
+struct Plan {
+  uint32_t *keys[2];
+  int32_t *vals[2];
+  int32_t *block_hist;
+  int32_t *seg_start;   // [V+1]
+  int32_t *long_row;    // [max_long]
+  int32_t *long_first;  // [max_long+1]
+  int32_t *meta;        // {n_long, n_sub}
+  float *scratch;       // [max_sub][d]
+  int passes, nblocks, max_long, max_sub;
+  size_t bytes;
+};
+
+size_t align_up(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+Plan make_plan(void *workspace, int num_tokens, int vocab, int d) {
+  Plan p{};
+  int bits = 1;
+  while (bits < 32 && (static_cast<uint64_t>(1) << bits) < static_cast<uint64_t>(vocab)) bits++;
+  p.passes = (bits + 7) / 8;
+  p.nblocks = ceil_div(num_tokens, kSortTile);
+  // A long row has more than kSubLen tokens, so there are fewer than T/kSubLen of
+  // them, and their sub-segments number at most T/kSubLen + (number of long rows).
+  p.max_long = num_tokens / kSubLen + 1;
+  p.max_sub = 2 * (num_tokens / kSubLen) + 2;
+  char *base = static_cast<char *>(workspace);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    char *ptr = base ? base + off : nullptr;
+    off += align_up(bytes);
+    return ptr;
+  };
+  const size_t tok = sizeof(int32_t) * static_cast<size_t>(num_tokens);
+  p.keys[0] = reinterpret_cast<uint32_t *>(take(tok));
+  p.keys[1] = reinterpret_cast<uint32_t *>(take(tok));
+  p.vals[0] = reinterpret_cast<int32_t *>(take(tok));
+  p.vals[1] = reinterpret_cast<int32_t *>(take(tok));
+  p.block_hist = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * kDigits * p.nblocks));
+  p.seg_start = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * (static_cast<size_t>(vocab) + 1)));
+  p.long_row = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * p.max_long));
+  p.long_first = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * (p.max_long + 1)));
+  p.meta = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * 4));
+  p.scratch = reinterpret_cast<float *>(take(sizeof(float) * static_cast<size_t>(p.max_sub) * d));
+  p.bytes = off;
+  return p;
+}
+
+// Sum of dy rows perm[b..e) over this thread's KV column vectors, in order.
+template <typename T, int KV>
+__device__ __forceinline__ void sum_tokens(const T *__restrict__ dy, const int32_t *__restrict__ perm,
+                                           int b, int e, int d, int cv0, int tx, int ncv,
+                                           float (&acc)[KV][Store<T>::kPerVec]) {
+  using S = Store<T>;
+  constexpr int E = S::kPerVec;
+#pragma unroll
+  for (int k = 0; k < KV; k++)
+#pragma unroll
+    for (int q = 0; q < E; q++) acc[k][q] = 0.f;
+  int j = b;
+  for (; j + 2 <= e; j += 2) {
+    const size_t r0 = static_cast<size_t>(__ldg(perm + j)) * d;
+    const size_t r1 = static_cast<size_t>(__ldg(perm + j + 1)) * d;
+    uint4 v0[KV], v1[KV];
+#pragma unroll
+    for (int k = 0; k < KV; k++) {
+      const int cv = cv0 + k * tx;
+      if (cv < ncv) {
+        v0[k] = ld_stream(dy + r0 + static_cast<size_t>(cv) * E);
+        v1[k] = ld_stream(dy + r1 + static_cast<size_t>(cv) * E);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < KV; k++) {
+      if (cv0 + k * tx < ncv) {
+        float f0[E], f1[E];
+        S::unpack(v0[k], f0);
+        S::unpack(v1[k], f1);
+#pragma unroll
+        for (int q = 0; q < E; q++) {
+          acc[k][q] += f0[q];
+          acc[k][q] += f1[q];
+        }
+      }
+    }
+  }
+  if (j < e) {
+    const size_t r0 = static_cast<size_t>(__ldg(perm + j)) * d;
+#pragma unroll
+    for (int k = 0; k < KV; k++) {
+      const int cv = cv0 + k * tx;
+      if (cv < ncv) {
+        float f0[E];
+        S::unpack(ld_stream(dy + r0 + static_cast<size_t>(cv) * E), f0);
+#pragma unroll
+        for (int q = 0; q < E; q++) acc[k][q] += f0[q];
+      }
+    }
+  }
+}
+
+// blockDim = (tx, ty).  grid.x = sub_groups + row_groups; grid.y tiles columns
+// when a row has more than tx*KV vectors.  The sub-segment groups come first so
+// that the heaviest work starts first.
+template <typename T, int KV>
+__global__ void __launch_bounds__(kBlock)
+scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
+                    const int32_t *__restrict__ seg_start, const int32_t *__restrict__ long_row,
+                    const int32_t *__restrict__ long_first, const int32_t *__restrict__ meta,
+                    float *__restrict__ grad, float *__restrict__ scratch, int vocab, int d,
+                    int sub_groups) {
+  using S = Store<T>;
+  constexpr int E = S::kPerVec;
+  const int tx = blockDim.x, ty = blockDim.y;
+  const int ncv = d / E;
+  const int cv0 = blockIdx.y * (tx * KV) + threadIdx.x;
+  float acc[KV][E];
+  float *dst;
+  if (static_cast<int>(blockIdx.x) < sub_groups) {
+    const int idx = blockIdx.x * ty + threadIdx.y;
+    const int n_long = meta[0], n_sub = meta[1];
+    if (idx >= n_sub) return;
+    int lo = 0, hi = n_long;  // last long row whose first sub-segment is <= idx
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (long_first[mid] <= idx) lo = mid; else hi = mid;
+    }
+    const int v = long_row[lo];
+    const int b = seg_start[v] + (idx - long_first[lo]) * kSubLen;
+    const int e = min(seg_start[v + 1], b + kSubLen);
+    sum_tokens<T, KV>(dy, perm, b, e, d, cv0, tx, ncv, acc);
+    dst = scratch + static_cast<size_t>(idx) * d;
+  } else {
+    const int v = (blockIdx.x - sub_groups) * ty + threadIdx.y;
+    if (v >= vocab) return;
+    const int b = seg_start[v], e = seg_start[v + 1];
+    if (e - b > kSubLen) return;  // long row: written by combine_long_kernel
+    sum_tokens<T, KV>(dy, perm, b, e, d, cv0, tx, ncv, acc);
+    dst = grad + static_cast<size_t>(v) * d;
+  }
+#pragma unroll
+  for (int k = 0; k < KV; k++) {
+    const int cv = cv0 + k * tx;
+    if (cv < ncv) {
+#pragma unroll
+      for (int q = 0; q < E / 4; q++) {
+        const uint4 o = make_uint4(__float_as_uint(acc[k][4 * q]), __float_as_uint(acc[k][4 * q + 1]),
+                                   __float_as_uint(acc[k][4 * q + 2]), __float_as_uint(acc[k][4 * q + 3]));
+        st_stream(dst + static_cast<size_t>(cv) * E + 4 * q, o);
+      }
+    }
+  }
+}
+
+// grad[v,:] = scratch rows of v added in sub-segment order (one float4 column
+// vector per thread).
+__global__ void __launch_bounds__(kBlock)
+combine_long_kernel(const float *__restrict__ scratch, const int32_t *__restrict__ long_row,
+                    const int32_t *__restrict__ long_first, const int32_t *__restrict__ meta,
+                    float *__restrict__ grad, int d) {
+  const int li = blockIdx.x;
+  if (li >= meta[0]) return;
+  const int v = long_row[li];
+  const int s0 = long_first[li], s1 = long_first[li + 1];
+  for (int c = (blockIdx.y * kBlock + threadIdx.x) * 4; c < d; c += gridDim.y * kBlock * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s = s0; s < s1; s++) {
+      const float4 p = __ldcs(reinterpret_cast<const float4 *>(scratch + static_cast<size_t>(s) * d + c));
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    __stcs(reinterpret_cast<float4 *>(grad + static_cast<size_t>(v) * d + c), acc);
+  }
+}
+
+// Any d / alignment: one thread per (row, column) walks the row's tokens.
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+scatter_scalar_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
+                      const int32_t *__restrict__ seg_start, float *__restrict__ grad, int vocab,
+                      int d) {
+  using S = Store<T>;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x;
+  if (i >= static_cast<int64_t>(vocab) * d) return;
+  const int v = static_cast<int>(i / d), c = static_cast<int>(i % d);
+  const int b = seg_start[v], e = seg_start[v + 1];
+  float total = 0.f;
+  // Same association as the vector path: sub-segments of kSubLen, then their sum.
+  if (e - b <= kSubLen) {
+    for (int j = b; j < e; j++) total += S::to_float(dy[static_cast<size_t>(perm[j]) * d + c]);
+  } else {
+    for (int b2 = b; b2 < e; b2 += kSubLen) {
+      float part = 0.f;
+      const int e2 = min(e, b2 + kSubLen);
+      for (int j = b2; j < e2; j++) part += S::to_float(dy[static_cast<size_t>(perm[j]) * d + c]);
+      total += part;
+    }
+  }
+  grad[i] = total;
+}
+
+struct BlockShape {
+  int tx, ty;
+};
+BlockShape shape_for(int ncv) {
+  int tx = 1;
+  while (tx < kBlock && tx < ncv) tx *= 2;
+  return {tx, kBlock / tx};
+}
+
+template <typename T>
+int gather_typed(const void *table, const int32_t *ids, const float *pe, int seq_len, void *out,
+                 int num_tokens, int vocab, int d, cudaStream_t st) {
+  constexpr int E = Store<T>::kPerVec;
+  const bool vec = d % E == 0 && aligned16(table) && aligned16(out) && (pe == nullptr || aligned16(pe));
+  if (vec) {
+    const int ncv = d / E;
+    const BlockShape bs = shape_for(ncv);
+    // Without PE any grouping of tokens works: walk 8 (or, for very many
+    // tokens, more) tokens per thread so that grid.y stays within its limit.
+    int stride_s = min(seq_len, num_tokens);
+    if (pe == nullptr) {
+      int64_t per_thread = ceil_div<int64_t>(num_tokens, 65535LL * bs.ty);
+      if (per_thread < 8) per_thread = 8;
+      stride_s = static_cast<int>(ceil_div<int64_t>(num_tokens, per_thread));
+    }
+    dim3 grid(ceil_div(ncv, bs.tx), ceil_div(stride_s, bs.ty));
+    DLB_REQUIRE(grid.y <= 65535u, DLB_ERR_UNSUPPORTED,
+                "embed_gather_fwd: seq_len=%d exceeds %d positions", seq_len, 65535 * bs.ty);
+    embed_gather_kernel<T><<<grid, dim3(bs.tx, bs.ty), 0, st>>>(
+        static_cast<const T *>(table), ids, pe, static_cast<T *>(out), num_tokens, vocab, d, stride_s);
+    DLB_LAUNCH_CHECK("embed_gather");
+    return DLB_OK;
+  }
+  const int64_t total = static_cast<int64_t>(num_tokens) * d;
+  embed_gather_scalar_kernel<T><<<static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st>>>(
+      static_cast<const T *>(table), ids, pe, static_cast<T *>(out), num_tokens, vocab, d, seq_len);
+  DLB_LAUNCH_CHECK("embed_gather_scalar");
+  return DLB_OK;
+}
+
+template <typename T, int KV>
+int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *grad, int vocab, int d,
+                   BlockShape bs, cudaStream_t st) {
+  constexpr int E = Store<T>::kPerVec;
+  const int ncv = d / E;
+  const int sub_groups = ceil_div(p.max_sub, bs.ty);
+  const int row_groups = ceil_div(vocab, bs.ty);
+  dim3 grid(sub_groups + row_groups, ceil_div(ncv, bs.tx * KV));
+  scatter_rows_kernel<T, KV><<<grid, dim3(bs.tx, bs.ty), 0, st>>>(
+      static_cast<const T *>(dy), perm, p.seg_start, p.long_row, p.long_first, p.meta, grad,
+      p.scratch, vocab, d, sub_groups);
+  DLB_LAUNCH_CHECK("scatter_rows");
+  return DLB_OK;
+}
+
+template <typename T>
+int scatter_typed(const Plan &p, const void *dy, float *grad, int vocab, int d, cudaStream_t st) {
+  constexpr int E = Store<T>::kPerVec;
+  const int32_t *perm = p.vals[p.passes & 1];
+  const bool vec = d % E == 0 && aligned16(dy) && aligned16(grad);
+  if (!vec) {
+    const int64_t total = static_cast<int64_t>(vocab) * d;
+    scatter_scalar_kernel<T><<<static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st>>>(
+        static_cast<const T *>(dy), perm, p.seg_start, grad, vocab, d);
+    DLB_LAUNCH_CHECK("scatter_scalar");
+    return DLB_OK;
+  }
+  const int ncv = d / E;
+  const BlockShape bs = shape_for(ncv);
+  const int need = ceil_div(ncv, bs.tx);
+  int rc;
+  if (need >= 4) rc = launch_scatter<T, 4>(p, dy, perm, grad, vocab, d, bs, st);
+  else if (need >= 2) rc = launch_scatter<T, 2>(p, dy, perm, grad, vocab, d, bs, st);
+  else rc = launch_scatter<T, 1>(p, dy, perm, grad, vocab, d, bs, st);
+  if (rc != DLB_OK) return rc;
+  dim3 grid(p.max_long, max(1, min(8, d / (kBlock * 4))));
+  combine_long_kernel<<<grid, kBlock, 0, st>>>(p.scratch, p.long_row, p.long_first, p.meta, grad, d);
+  DLB_LAUNCH_CHECK("combine_long");
+  return DLB_OK;
+}
+
+bool embed_args_ok(int num_tokens, int vocab, int d) {
+  return num_tokens >= 0 && vocab > 0 && d > 0 &&
+         static_cast<int64_t>(vocab) * d <= INT64_MAX / 8;
+}
+
+}  // namespace
+}  // namespace dlb
+
+using namespace dlb;
+
+extern "C" int dlb_embed_gather_fwd(const void *table, const int32_t *ids, const float *pe,
+                                    int seq_len, void *out, int num_tokens, int vocab, int d,
+                                    int dtype, void *stream) {
+  DLB_REQUIRE(embed_args_ok(num_tokens, vocab, d), DLB_ERR_INVALID_ARG,
+              "embed_gather_fwd: tokens=%d vocab=%d d=%d", num_tokens, vocab, d);
+  DLB_REQUIRE(pe == nullptr || seq_len > 0, DLB_ERR_INVALID_ARG,
+              "embed_gather_fwd: seq_len=%d with a PE table", seq_len);
+  if (num_tokens == 0) return DLB_OK;
+  DLB_REQUIRE(table && ids && out, DLB_ERR_INVALID_ARG, "embed_gather_fwd: null pointer");
+  if (dtype == DLB_F32)
+    return gather_typed<float>(table, ids, pe, seq_len, out, num_tokens, vocab, d, as_stream(stream));
+  if (dtype == DLB_BF16)
+    return gather_typed<__nv_bfloat16>(table, ids, pe, seq_len, out, num_tokens, vocab, d,
+                                       as_stream(stream));
+  set_error("embed_gather_fwd: unknown dtype %d", dtype);
+  return DLB_ERR_INVALID_ARG;
+}
+
+extern "C" size_t dlb_embed_workspace_bytes(int num_tokens, int vocab, int d) {
+  if (!embed_args_ok(num_tokens, vocab, d)) return 0;
+  return make_plan(nullptr, num_tokens, vocab, d).bytes;
+}
+
+extern "C" int dlb_embed_sort_tokens(const int32_t *ids, void *workspace, size_t workspace_bytes,
+                                     int num_tokens, int vocab, int d, void *stream) {
+  DLB_REQUIRE(embed_args_ok(num_tokens, vocab, d), DLB_ERR_INVALID_ARG,
+              "embed_sort_tokens: tokens=%d vocab=%d d=%d", num_tokens, vocab, d);
+  DLB_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 &&
+                  workspace_bytes >= dlb_embed_workspace_bytes(num_tokens, vocab, d),
+              DLB_ERR_WORKSPACE, "embed_sort_tokens: 256-byte aligned workspace of %zu bytes required",
+              dlb_embed_workspace_bytes(num_tokens, vocab, d));
+  DLB_REQUIRE(ids || num_tokens == 0, DLB_ERR_INVALID_ARG, "embed_sort_tokens: null ids");
+  cudaStream_t st = as_stream(stream);
+  const Plan p = make_plan(workspace, num_tokens, vocab, d);
+  const uint32_t *kin = reinterpret_cast<const uint32_t *>(ids);
+  const int32_t *vin = nullptr;
+  for (int pass = 0; pass < p.passes && num_tokens > 0; pass++) {
+    const int shift = 8 * pass;
+    uint32_t *kout = p.keys[(pass + 1) & 1];
+    int32_t *vout = p.vals[(pass + 1) & 1];
+    sort_hist_kernel<<<p.nblocks, kBlock, 0, st>>>(kin, num_tokens, shift, p.nblocks, p.block_hist);
+    DLB_LAUNCH_CHECK("sort_hist");
+    scan_inplace_kernel<<<1, 1024, 0, st>>>(p.block_hist, kDigits * p.nblocks);
+    DLB_LAUNCH_CHECK("sort_scan");
+    sort_scatter_kernel<<<p.nblocks, kBlock, 0, st>>>(kin, vin, kout, vout, num_tokens, shift,
+                                                      p.nblocks, p.block_hist);
+    DLB_LAUNCH_CHECK("sort_scatter");
+    kin = kout;
+    vin = vout;
+  }
+  segment_start_kernel<<<ceil_div(vocab + 1, kBlock), kBlock, 0, st>>>(
+      p.keys[p.passes & 1], num_tokens, vocab, p.seg_start);
+  DLB_LAUNCH_CHECK("segment_start");
+  plan_long_rows_kernel<<<1, 1024, 0, st>>>(p.seg_start, vocab, p.long_row, p.long_first, p.meta);
+  DLB_LAUNCH_CHECK("plan_long_rows");
+  return DLB_OK;
+}
+
+extern "C" int dlb_embed_scatter_bwd(const void *dy, const int32_t *ids, float *grad,
+                                     void *workspace, size_t workspace_bytes, int num_tokens,
+                                     int vocab, int d, int dtype, void *stream) {
+  (void)ids;
+  DLB_REQUIRE(embed_args_ok(num_tokens, vocab, d), DLB_ERR_INVALID_ARG,
+              "embed_scatter_bwd: tokens=%d vocab=%d d=%d", num_tokens, vocab, d);
+  DLB_REQUIRE(grad, DLB_ERR_INVALID_ARG, "embed_scatter_bwd: null grad");
+  DLB_REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 &&
+                  workspace_bytes >= dlb_embed_workspace_bytes(num_tokens, vocab, d),
+              DLB_ERR_WORKSPACE, "embed_scatter_bwd: 256-byte aligned workspace of %zu bytes required",
+              dlb_embed_workspace_bytes(num_tokens, vocab, d));
+  DLB_REQUIRE(dy || num_tokens == 0, DLB_ERR_INVALID_ARG, "embed_scatter_bwd: null dy");
+  const Plan p = make_plan(workspace, num_tokens, vocab, d);
+  if (dtype == DLB_F32) return scatter_typed<float>(p, dy, grad, vocab, d, as_stream(stream));
+  if (dtype == DLB_BF16)
+    return scatter_typed<__nv_bfloat16>(p, dy, grad, vocab, d, as_stream(stream));
+  set_error("embed_scatter_bwd: unknown dtype %d", dtype);
+  return DLB_ERR_INVALID_ARG;
+}

@@ -1,0 +1,173 @@
+"""torch-tensor front end of the C ABI, for tests and benchmarks.
+
+Each function forwards to one entry point of libdlcuda_b200.so on the current
+CUDA stream.  Outputs and workspaces can be passed in (benchmarks do, so that
+nothing is allocated inside a timed region) or are allocated here.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import capi
+from .capi import check, current_stream, dtype_of, ptr
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("device tensors required: the kernels have no CPU path")
+        if t is not None and not t.is_contiguous():
+            raise ValueError("contiguous tensors required")
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    # 256-byte aligned by the caching allocator (512-byte granularity).
+    return torch.empty(max(nbytes, 16), dtype=torch.uint8, device=device)
+
+
+def residual_add(a, b, out=None):
+    _need_cuda(a, b, out)
+    out = torch.empty_like(a) if out is None else out
+    check(capi.lib().dlb_residual_add(ptr(a), ptr(b), ptr(out), a.numel(), dtype_of(a), current_stream()))
+    return out
+
+
+def ln_residual_fwd(a, b, gamma, beta, eps=1e-5, y=None, xhat=None, inv_std=None, cache=True):
+    """Returns (y, xhat, inv_std); xhat/inv_std are None when cache is False."""
+    _need_cuda(a, b, gamma, beta, y, xhat, inv_std)
+    rows, d = a.shape
+    y = torch.empty_like(a) if y is None else y
+    if cache:
+        xhat = torch.empty_like(a) if xhat is None else xhat
+        inv_std = torch.empty(rows, dtype=torch.float32, device=a.device) if inv_std is None else inv_std
+    else:
+        xhat = inv_std = None
+    check(capi.lib().dlb_ln_residual_fwd(ptr(a), ptr(b), ptr(gamma), ptr(beta), ptr(y), ptr(xhat),
+                                         ptr(inv_std), rows, d, eps, dtype_of(a), current_stream()))
+    return y, xhat, inv_std
+
+
+def ln_bwd_workspace(rows, d, device):
+    return _workspace(capi.lib().dlb_ln_bwd_workspace_bytes(rows, d), device)
+
+
+def ln_bwd(dy_a, dy_b, xhat, inv_std, gamma, dx=None, dgamma=None, dbeta=None, workspace=None):
+    """Returns (dx, dgamma, dbeta)."""
+    _need_cuda(dy_a, dy_b, xhat, inv_std, gamma, dx, dgamma, dbeta)
+    rows, d = dy_a.shape
+    dx = torch.empty_like(dy_a) if dx is None else dx
+    dgamma = torch.empty(d, dtype=torch.float32, device=dy_a.device) if dgamma is None else dgamma
+    dbeta = torch.empty(d, dtype=torch.float32, device=dy_a.device) if dbeta is None else dbeta
+    workspace = ln_bwd_workspace(rows, d, dy_a.device) if workspace is None else workspace
+    check(capi.lib().dlb_ln_bwd(ptr(dy_a), ptr(dy_b), ptr(xhat), ptr(inv_std), ptr(gamma), ptr(dx),
+                                ptr(dgamma), ptr(dbeta), ptr(workspace), workspace.numel(), rows, d,
+                                dtype_of(dy_a), current_stream()))
+    return dx, dgamma, dbeta
+
+
+def pe_table(seq_len: int, d: int) -> torch.Tensor:
+    """The sinusoidal table, built on the host (float powf/sinf/cosf), as a CPU tensor."""
+    t = torch.empty(seq_len, d, dtype=torch.float32)
+    check(capi.lib().dlb_pe_build_table_host(t.data_ptr(), seq_len, d))
+    return t
+
+
+def pe_add_fwd(x, pe, out=None):
+    _need_cuda(x, pe, out)
+    batch, seq_len, d = x.shape
+    out = torch.empty_like(x) if out is None else out
+    check(capi.lib().dlb_pe_add_fwd(ptr(x), ptr(pe), ptr(out), batch, seq_len, d, dtype_of(x), current_stream()))
+    return out
+
+
+def pe_add_bwd(dy, dx=None):
+    _need_cuda(dy, dx)
+    dx = torch.empty_like(dy) if dx is None else dx
+    check(capi.lib().dlb_pe_add_bwd(ptr(dy), ptr(dx), dy.numel(), dtype_of(dy), current_stream()))
+    return dx
+
+
+def embed_gather_fwd(table, ids, pe=None, seq_len=0, out=None):
+    _need_cuda(table, ids, pe, out)
+    vocab, d = table.shape
+    n = ids.numel()
+    out = torch.empty(n, d, dtype=table.dtype, device=table.device) if out is None else out
+    check(capi.lib().dlb_embed_gather_fwd(ptr(table), ptr(ids), ptr(pe), seq_len, ptr(out), n, vocab, d,
+                                          dtype_of(table), current_stream()))
+    return out
+
+
+def embed_workspace(num_tokens, vocab, d, device):
+    return _workspace(capi.lib().dlb_embed_workspace_bytes(num_tokens, vocab, d), device)
+
+
+def embed_sort_tokens(ids, vocab, d, workspace=None):
+    _need_cuda(ids)
+    n = ids.numel()
+    workspace = embed_workspace(n, vocab, d, ids.device) if workspace is None else workspace
+    check(capi.lib().dlb_embed_sort_tokens(ptr(ids), ptr(workspace), workspace.numel(), n, vocab, d,
+                                           current_stream()))
+    return workspace
+
+
+def embed_scatter_bwd(dy, ids, vocab, workspace, grad=None):
+    """workspace must hold the plan embed_sort_tokens built for these ids."""
+    _need_cuda(dy, ids, grad, workspace)
+    n, d = dy.shape
+    grad = torch.empty(vocab, d, dtype=torch.float32, device=dy.device) if grad is None else grad
+    check(capi.lib().dlb_embed_scatter_bwd(ptr(dy), ptr(ids), ptr(grad), ptr(workspace), workspace.numel(),
+                                           n, vocab, d, dtype_of(dy), current_stream()))
+    return grad
+
+
+def act_cache(kind, x):
+    return _workspace(capi.lib().dlb_act_cache_bytes(kind, x.numel(), dtype_of(x)), x.device)
+
+
+def act_fwd(kind, x, bias=None, y=None, cache=None, want_cache=True):
+    """Returns (y, cache)."""
+    _need_cuda(x, bias, y, cache)
+    rows, cols = (x.shape[0], x.shape[1]) if x.dim() == 2 else (1, x.numel())
+    y = torch.empty_like(x) if y is None else y
+    if want_cache and cache is None:
+        cache = act_cache(kind, x)
+    check(capi.lib().dlb_act_fwd(kind, ptr(x), ptr(bias), ptr(y), ptr(cache) if want_cache else None,
+                                 rows, cols, dtype_of(x), current_stream()))
+    return y, cache
+
+
+def act_bwd_workspace(kind, rows, cols, device):
+    return _workspace(capi.lib().dlb_act_bwd_workspace_bytes(kind, rows, cols), device)
+
+
+def act_bwd(kind, dy, cache, dx=None, dbias=None, want_dbias=False, workspace=None):
+    """Returns (dx, dbias)."""
+    _need_cuda(dy, cache, dx, dbias)
+    rows, cols = (dy.shape[0], dy.shape[1]) if dy.dim() == 2 else (1, dy.numel())
+    dx = torch.empty_like(dy) if dx is None else dx
+    if want_dbias:
+        dbias = torch.empty(cols, dtype=torch.float32, device=dy.device) if dbias is None else dbias
+        workspace = act_bwd_workspace(kind, rows, cols, dy.device) if workspace is None else workspace
+    else:
+        dbias = None
+    check(capi.lib().dlb_act_bwd(kind, ptr(dy), ptr(cache), ptr(dx), ptr(dbias), ptr(workspace),
+                                 workspace.numel() if workspace is not None else 0, rows, cols,
+                                 dtype_of(dy), current_stream()))
+    return dx, dbias
+
+
+def bias_grad(dy, dbias=None, workspace=None):
+    _need_cuda(dy, dbias)
+    rows, cols = dy.shape
+    dbias = torch.empty(cols, dtype=torch.float32, device=dy.device) if dbias is None else dbias
+    if workspace is None:
+        workspace = _workspace(capi.lib().dlb_bias_grad_workspace_bytes(rows, cols), dy.device)
+    check(capi.lib().dlb_bias_grad(ptr(dy), ptr(dbias), ptr(workspace), workspace.numel(), rows, cols,
+                                   dtype_of(dy), current_stream()))
+    return dbias
+
+
+def sgd_update(params, grads, lr):
+    _need_cuda(params, grads)
+    check(capi.lib().dlb_sgd_update(ptr(params), ptr(grads), lr, params.numel(), current_stream()))
+    return params

@@ -1,0 +1,188 @@
+/*
+ * dlcuda_b200.h -- C ABI of the B200 (sm_100a) fused layer kernels.
+ *
+ * Every entry point takes raw DEVICE pointers (unless a parameter is named
+ * h_*), plain integer sizes, a storage-type tag and a CUDA stream passed as
+ * void* (a cudaStream_t; NULL = the legacy default stream).  Nothing here
+ * allocates, frees, synchronises or exits: scratch memory is passed in by the
+ * caller (its size comes from the matching *_workspace_bytes query) and every
+ * call returns a dlb_status.  dlb_last_error() gives the text of the last
+ * failure on the calling thread.
+ *
+ * Storage types.  DLB_F32: every tensor is float.  DLB_BF16: activation-sized
+ * tensors (a, b, y, xhat, dy, dx, x, cache, embedding table, gather output)
+ * are bfloat16, while parameters (gamma, beta, bias), the positional-encoding
+ * table, inv_std, every gradient of a parameter and all arithmetic stay fp32.
+ *
+ * Each declaration cites the interface of Cameron-Lyons/dl-cuda that it
+ * replaces (path inside that project : lines).
+ */
+#ifndef DLCUDA_B200_H
+#define DLCUDA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DLB_API __attribute__((visibility("default")))
+#else
+#define DLB_API
+#endif
+
+typedef enum dlb_status {
+  DLB_OK = 0,
+  DLB_ERR_INVALID_ARG = 1, /* null pointer, negative size, unknown enum      */
+  DLB_ERR_WORKSPACE = 2,   /* workspace missing or smaller than required     */
+  DLB_ERR_UNSUPPORTED = 3, /* shape outside what the kernels were built for  */
+  DLB_ERR_CUDA = 4,        /* a CUDA runtime call or launch failed           */
+  DLB_ERR_NO_DEVICE = 5    /* no CUDA device: there is no CPU fallback       */
+} dlb_status;
+
+typedef enum dlb_dtype { DLB_F32 = 0, DLB_BF16 = 1 } dlb_dtype;
+
+typedef enum dlb_act {
+  DLB_ACT_RELU = 0,
+  DLB_ACT_SIGMOID = 1,
+  DLB_ACT_TANH = 2,
+  DLB_ACT_GELU = 3
+} dlb_act;
+
+/* ---- library ----------------------------------------------------------- */
+
+DLB_API int dlb_version(void);
+DLB_API const char *dlb_status_string(int status);
+DLB_API const char *dlb_last_error(void);
+/* Number of kernels this library has launched from the calling process since
+ * load (every stream, every thread).  Used by benchmarks to report launches. */
+DLB_API uint64_t dlb_launch_count(void);
+
+/* ---- residual add -------------------------------------------------------
+ * out[i] = a[i] + b[i].  out may alias a or b.
+ * Replaces transformerResidualAddKernel (src/transformer.cuh:216-222) and
+ * addVectorsKernel (src/layers.cuh:256-262) where they are used on their own;
+ * the adds that feed a layer norm are folded into the calls below instead. */
+DLB_API int dlb_residual_add(const void *a, const void *b, void *out, int64_t n,
+                             int dtype, void *stream);
+
+/* ---- layer norm with the residual add folded in --------------------------
+ * Forward: s = a + b (b may be NULL: s = a); per row of d features
+ *   mean = sum(s)/d; var = sum((s-mean)^2)/d (biased, two-pass);
+ *   inv_std = 1/sqrtf(var+eps); xhat = (s-mean)*inv_std; y = gamma*xhat+beta.
+ * xhat [rows,d] and inv_std [rows] are the caches backward needs; pass both
+ * NULL for inference.  y may alias a or b.
+ * Replaces transformerResidualAddKernel + layerNormForwardCachingKernel
+ * (src/transformer.cuh:216-222, 136-164; call sites :499-507, :526-533). */
+DLB_API int dlb_ln_residual_fwd(const void *a, const void *b, const float *gamma,
+                                const float *beta, void *y, void *xhat,
+                                float *inv_std, int rows, int d, float eps,
+                                int dtype, void *stream);
+
+/* Backward: dy = dy_a + dy_b (dy_b may be NULL);
+ *   g = dy*gamma; c1 = mean(g); c2 = mean(g*xhat);
+ *   dx = (g - c1 - xhat*c2)*inv_std;
+ *   dgamma[j] = sum_rows dy*xhat; dbeta[j] = sum_rows dy   (overwritten).
+ * One pass over dy/xhat; the column sums are reduced through `workspace` in a
+ * fixed order, so results are bitwise reproducible.  dx may alias dy_a.
+ * Replaces layerNormBackwardKernel + layerNormParamGradKernel and the gradient
+ * residual add in front of them (src/transformer.cuh:166-207; call sites
+ * :557-560, :583-585, :594-598). */
+DLB_API size_t dlb_ln_bwd_workspace_bytes(int rows, int d);
+DLB_API int dlb_ln_bwd(const void *dy_a, const void *dy_b, const void *xhat,
+                       const float *inv_std, const float *gamma, void *dx,
+                       float *dgamma, float *dbeta, void *workspace,
+                       size_t workspace_bytes, int rows, int d, int dtype,
+                       void *stream);
+
+/* ---- sinusoidal positional encoding --------------------------------------
+ * h_table[pos*d + i] = (i even ? sinf : cosf)(pos / powf(10000, 2*(i/2)/d)),
+ * built on the HOST with the C library's float functions, exactly as
+ * PositionalEncoding's constructor does (src/positional_encoding.cuh:33-41). */
+DLB_API int dlb_pe_build_table_host(float *h_table, int seq_len, int d);
+
+/* out[i] = in[i] + pe[i mod (seq_len*d)] over batch*seq_len*d elements.
+ * Replaces addPositionalEncodingKernel (src/positional_encoding.cuh:7-17). */
+DLB_API int dlb_pe_add_fwd(const void *in, const float *pe, void *out, int batch,
+                           int seq_len, int d, int dtype, void *stream);
+/* dx = dy (identity).  Replaces the device-to-device copy in
+ * PositionalEncoding::backward (src/positional_encoding.cuh:66-70). */
+DLB_API int dlb_pe_add_bwd(const void *dy, void *dx, int64_t n, int dtype,
+                           void *stream);
+
+/* ---- token embedding ------------------------------------------------------
+ * Gather with the positional-encoding add folded in:
+ *   out[t,:] = table[ids[t],:] + (pe ? pe[(t mod seq_len),:] : 0).
+ * ids are int32 in [0,vocab); the call does not validate them on the device.
+ * Replaces embeddingForwardKernel (src/embedding.cuh:8-17) followed by
+ * addPositionalEncodingKernel (src/positional_encoding.cuh:7-17). */
+DLB_API int dlb_embed_gather_fwd(const void *table, const int32_t *ids,
+                                 const float *pe, int seq_len, void *out,
+                                 int num_tokens, int vocab, int d, int dtype,
+                                 void *stream);
+
+/* Gradient of the table: grad[v,:] = sum over tokens t with ids[t]==v of
+ * dy[t,:]; rows no token refers to are written as zero (no separate memset).
+ * The tokens are sorted by id (stable radix sort) and each output row is
+ * summed in ascending token order, long rows through fixed-size sub-segments,
+ * so the result does not depend on scheduling: two runs give identical bits.
+ * grad is always fp32.  Replaces cudaMemset + embeddingBackwardKernel
+ * (src/embedding.cuh:19-30, 82-92), whose fp32 atomicAdd order is arbitrary.
+ *
+ * dlb_embed_sort_tokens builds the sorted-segment plan from ids alone into
+ * `workspace`; dlb_embed_scatter_bwd consumes it.  A plan stays valid for as
+ * long as ids do, so a layer builds it once per batch. */
+DLB_API size_t dlb_embed_workspace_bytes(int num_tokens, int vocab, int d);
+DLB_API int dlb_embed_sort_tokens(const int32_t *ids, void *workspace,
+                                  size_t workspace_bytes, int num_tokens,
+                                  int vocab, int d, void *stream);
+DLB_API int dlb_embed_scatter_bwd(const void *dy, const int32_t *ids,
+                                  float *grad, void *workspace,
+                                  size_t workspace_bytes, int num_tokens,
+                                  int vocab, int d, int dtype, void *stream);
+
+/* ---- bias + activation epilogues -------------------------------------------
+ * Forward: pre = x + (bias ? bias[col] : 0); y = act(pre) over [rows,cols].
+ *   RELU    y = pre>0 ? pre : 0           cache = 1 bit per element (pre>0)
+ *   SIGMOID y = 1/(1+expf(-pre))          cache = y
+ *   TANH    y = tanhf(pre)                cache = y
+ *   GELU    y = pre*0.5*(1+tanhf(k(pre+0.044715 pre^3)))   cache = pre
+ * `cache` is owned by the layer (dlb_act_cache_bytes), written in the same
+ * pass, and may be NULL for inference.  y may alias x.
+ * Backward: RELU dx = dy*(bit?1.0f:0.0f); SIGMOID dx = dy*s*(1-s);
+ *   TANH dx = dy*(1-t*t); GELU as geluBackwardKernel.  When dbias is non-NULL
+ *   dbias[col] = sum_rows dx (overwritten) is produced in the same pass through
+ *   `workspace` (fixed order, reproducible).  dx may alias dy.
+ * Replaces reluKernel/sigmoidKernel/tanhActivationKernel/geluForwardKernel and
+ * their backward kernels with the cudaMemcpy cache copies around them
+ * (src/activation.cuh:5-55, 75-118, 203-226, 278-289), tanhBackwardElementKernel
+ * (src/layers.cuh:247-254), the bias add at the end of linearLayerKernel
+ * (src/layers.cuh:34) and linearBackwardBiasKernel (src/layers.cuh:70-82). */
+DLB_API size_t dlb_act_cache_bytes(int kind, int64_t n, int dtype);
+DLB_API int dlb_act_fwd(int kind, const void *x, const float *bias, void *y,
+                        void *cache, int64_t rows, int64_t cols, int dtype,
+                        void *stream);
+DLB_API size_t dlb_act_bwd_workspace_bytes(int kind, int64_t rows, int64_t cols);
+DLB_API int dlb_act_bwd(int kind, const void *dy, const void *cache, void *dx,
+                        float *dbias, void *workspace, size_t workspace_bytes,
+                        int64_t rows, int64_t cols, int dtype, void *stream);
+
+/* dbias[col] = sum_rows dy[row,col] on its own (fixed order, reproducible).
+ * Replaces linearBackwardBiasKernel (src/layers.cuh:70-82). */
+DLB_API size_t dlb_bias_grad_workspace_bytes(int64_t rows, int64_t cols);
+DLB_API int dlb_bias_grad(const void *dy, float *dbias, void *workspace,
+                          size_t workspace_bytes, int64_t rows, int64_t cols,
+                          int dtype, void *stream);
+
+/* ---- parameter update used by the layers themselves ------------------------
+ * p[i] -= lr*g[i].  Replaces sgdUpdateKernel (src/layers.cuh:84-90), which
+ * EmbeddingLayer::update_weights calls (src/embedding.cuh:94-99). */
+DLB_API int dlb_sgd_update(float *params, const float *grads, float lr,
+                           int64_t n, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DLCUDA_B200_H */

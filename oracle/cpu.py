@@ -1,0 +1,158 @@
+"""TEST INFRASTRUCTURE: numpy front end of oracle/host_ref.cpp (liboracle.so).
+
+Every function takes and returns C-contiguous numpy arrays (float32 unless
+said otherwise) and runs single-threaded on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "_build" / "liboracle.so"
+SUB_LEN = 32  # tokens per sub-segment of the CUDA scatter-add (kSubLen in csrc/embedding.cu)
+
+_lib = None
+
+
+def build() -> Path:
+    subprocess.run(["make", "-s", "-C", str(HERE), "oracle"], check=True)
+    return LIB_PATH
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            build()
+        _lib = C.CDLL(str(LIB_PATH))
+    return _lib
+
+
+def _f(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a
+
+
+def _p(a):
+    return None if a is None else C.c_void_p(a.ctypes.data)
+
+
+def residual_add(a, b):
+    a, b = _f(a), _f(b)
+    out = np.empty_like(a)
+    lib().orc_residual_add(_p(a), _p(b), _p(out), C.c_int64(a.size))
+    return out
+
+
+def ln_residual_fwd(a, b, gamma, beta, eps=1e-5):
+    """Returns (y, xhat, inv_std)."""
+    a, gamma, beta = _f(a), _f(gamma), _f(beta)
+    b = None if b is None else _f(b)
+    rows, d = a.shape
+    y, xhat = np.empty_like(a), np.empty_like(a)
+    inv_std = np.empty(rows, np.float32)
+    lib().orc_ln_residual_fwd(_p(a), _p(b), _p(gamma), _p(beta), _p(y), _p(xhat), _p(inv_std),
+                              rows, d, C.c_float(eps))
+    return y, xhat, inv_std
+
+
+def ln_bwd(dy_a, dy_b, xhat, inv_std, gamma):
+    """Returns (dx, dgamma, dbeta) in the reference's fp32 order."""
+    dy_a, xhat, inv_std, gamma = _f(dy_a), _f(xhat), _f(inv_std), _f(gamma)
+    dy_b = None if dy_b is None else _f(dy_b)
+    rows, d = dy_a.shape
+    dx = np.empty_like(dy_a)
+    dgamma, dbeta = np.empty(d, np.float32), np.empty(d, np.float32)
+    lib().orc_ln_bwd_dx(_p(dy_a), _p(dy_b), _p(xhat), _p(inv_std), _p(gamma), _p(dx), rows, d)
+    lib().orc_ln_param_grad(_p(dy_a), _p(dy_b), _p(xhat), _p(dgamma), _p(dbeta), rows, d)
+    return dx, dgamma, dbeta
+
+
+def ln_param_grad_f64(dy_a, dy_b, xhat):
+    dy_a, xhat = _f(dy_a), _f(xhat)
+    dy_b = None if dy_b is None else _f(dy_b)
+    rows, d = dy_a.shape
+    dgamma, dbeta = np.empty(d, np.float64), np.empty(d, np.float64)
+    lib().orc_ln_param_grad_f64(_p(dy_a), _p(dy_b), _p(xhat), _p(dgamma), _p(dbeta), rows, d)
+    return dgamma, dbeta
+
+
+def pe_table(seq_len, d):
+    t = np.empty((seq_len, d), np.float32)
+    lib().orc_pe_table(_p(t), seq_len, d)
+    return t
+
+
+def pe_add(x, pe):
+    x, pe = _f(x), _f(pe)
+    batch, seq_len, d = x.shape
+    out = np.empty_like(x)
+    lib().orc_pe_add(_p(x), _p(pe), _p(out), batch, seq_len, d)
+    return out
+
+
+def embed_gather(table, ids, pe=None, seq_len=0):
+    table = _f(table)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    pe = None if pe is None else _f(pe)
+    out = np.empty((ids.size, table.shape[1]), np.float32)
+    lib().orc_embed_gather(_p(table), _p(ids), _p(pe), seq_len, _p(out), ids.size, table.shape[1])
+    return out
+
+
+def embed_scatter(dy, ids, vocab, mode="sequential"):
+    """mode: 'sequential' (ascending tokens), 'segmented' (the CUDA kernel's association), 'f64'."""
+    dy = _f(dy)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    n, d = dy.shape
+    if mode == "f64":
+        grad = np.empty((vocab, d), np.float64)
+        lib().orc_embed_scatter_f64(_p(dy), _p(ids), _p(grad), n, vocab, d)
+    elif mode == "segmented":
+        grad = np.empty((vocab, d), np.float32)
+        lib().orc_embed_scatter_segmented(_p(dy), _p(ids), _p(grad), n, vocab, d, SUB_LEN)
+    else:
+        grad = np.empty((vocab, d), np.float32)
+        lib().orc_embed_scatter(_p(dy), _p(ids), _p(grad), n, vocab, d)
+    return grad
+
+
+def act_fwd(kind, x, bias=None):
+    """Returns (y, pre) with pre = x + bias."""
+    x = _f(x)
+    bias = None if bias is None else _f(bias)
+    rows, cols = (x.shape[0], x.shape[1]) if x.ndim == 2 else (1, x.size)
+    y, pre = np.empty_like(x), np.empty_like(x)
+    lib().orc_act_fwd(kind, _p(x), _p(bias), _p(y), _p(pre), C.c_int64(rows), C.c_int64(cols))
+    return y, pre
+
+
+def act_bwd(kind, dy, cache):
+    """cache: forward input (pre) for relu/gelu, forward output for sigmoid/tanh."""
+    dy, cache = _f(dy), _f(cache)
+    dx = np.empty_like(dy)
+    lib().orc_act_bwd(kind, _p(dy), _p(cache), _p(dx), C.c_int64(dy.size))
+    return dx
+
+
+def bias_grad(dy, f64=False):
+    dy = _f(dy)
+    rows, cols = dy.shape
+    if f64:
+        out = np.empty(cols, np.float64)
+        lib().orc_bias_grad_f64(_p(dy), _p(out), C.c_int64(rows), C.c_int64(cols))
+    else:
+        out = np.empty(cols, np.float32)
+        lib().orc_bias_grad(_p(dy), _p(out), C.c_int64(rows), C.c_int64(cols))
+    return out
+
+
+def sgd_update(p, g, lr):
+    p = _f(p).copy()
+    g = _f(g)
+    lib().orc_sgd_update(_p(p), _p(g), C.c_float(lr), C.c_int64(p.size))
+    return p

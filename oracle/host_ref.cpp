@@ -1,0 +1,282 @@
+// TEST INFRASTRUCTURE -- NOT PART OF THE PRODUCT.
+//
+// CPU restatement of the arithmetic of dl-cuda's layer kernels, one row (or one
+// element) at a time on a single host thread, in the reference's own summation
+// order.  It exists to check the CUDA kernels in tests/, in
+// __graft_entry__.smoke() and as the timed host baseline of bench.py; nothing
+// in the shipped library may call it.
+//
+// The reference has no CPU implementation: every function below follows a CUDA
+// kernel of the reference, cited as path:lines inside that project.  nvcc
+// compiles those kernels with its default -fmad=true, i.e. `a*b + c` becomes
+// one fused multiply-add; the places where that happens are written with
+// fmaf() here so that the host result carries the same rounding.  Division,
+// sqrtf and the fp32 adds are IEEE on both sides.  expf/tanhf come from the
+// host C library here and from CUDA's math library on the GPU: those two may
+// differ by a few units in the last place, everything else is bit-for-bit.
+//
+// Parity pin: the embedding known-answer test of the reference
+// (tests/gpu_correctness_tests.cu:196-252) and fixtures written by the
+// reference's own kernels (tests/golden/) are checked against this file by
+// tests/test_oracle_golden.py.
+//
+// Build: g++ -O2 -std=c++17 -shared -fPIC (no -ffast-math, no -march flags: the
+// compiler must not contract or reassociate anything by itself).
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+extern "C" {
+
+// transformerResidualAddKernel, src/transformer.cuh:216-222 (also
+// addVectorsKernel, src/layers.cuh:256-262): out[i] = a[i] + b[i].
+void orc_residual_add(const float *a, const float *b, float *out, int64_t n) {
+  for (int64_t i = 0; i < n; i++) out[i] = a[i] + b[i];
+}
+
+// Residual add (src/transformer.cuh:499-502) followed by
+// layerNormForwardCachingKernel (src/transformer.cuh:136-164): the sum is
+// rounded to float first (the reference stores it in residual_buf), then mean,
+// biased two-pass variance, inv_std, xhat and y, all accumulated left to right.
+void orc_ln_residual_fwd(const float *a, const float *b, const float *gamma, const float *beta,
+                         float *y, float *xhat, float *inv_std, int rows, int d, float eps) {
+  std::vector<float> s(static_cast<size_t>(d));
+  for (int r = 0; r < rows; r++) {
+    const size_t base = static_cast<size_t>(r) * d;
+    for (int j = 0; j < d; j++) s[j] = b ? a[base + j] + b[base + j] : a[base + j];
+    float mean = 0.0f;
+    for (int j = 0; j < d; j++) mean += s[j];
+    mean /= d;
+    float var = 0.0f;
+    for (int j = 0; j < d; j++) {
+      const float diff = s[j] - mean;
+      var = fmaf(diff, diff, var);
+    }
+    var /= d;
+    const float is = 1.0f / sqrtf(var + eps);
+    if (inv_std) inv_std[r] = is;
+    for (int j = 0; j < d; j++) {
+      const float xh = (s[j] - mean) * is;
+      if (xhat) xhat[base + j] = xh;
+      y[base + j] = fmaf(gamma[j], xh, beta[j]);
+    }
+  }
+}
+
+// Gradient residual add (src/transformer.cuh:583-585) followed by
+// layerNormBackwardKernel (src/transformer.cuh:166-190).
+void orc_ln_bwd_dx(const float *dy_a, const float *dy_b, const float *xhat, const float *inv_std,
+                   const float *gamma, float *dx, int rows, int d) {
+  std::vector<float> g(static_cast<size_t>(d));
+  for (int r = 0; r < rows; r++) {
+    const size_t base = static_cast<size_t>(r) * d;
+    const float is = inv_std[r];
+    float c1 = 0.0f, c2 = 0.0f;
+    for (int j = 0; j < d; j++) {
+      const float dy = dy_b ? dy_a[base + j] + dy_b[base + j] : dy_a[base + j];
+      const float dxh = dy * gamma[j];
+      g[j] = dxh;
+      c1 += dxh;
+      c2 = fmaf(dxh, xhat[base + j], c2);
+    }
+    c1 /= d;
+    c2 /= d;
+    for (int j = 0; j < d; j++) dx[base + j] = fmaf(-xhat[base + j], c2, g[j] - c1) * is;
+  }
+}
+
+// layerNormParamGradKernel (src/transformer.cuh:192-207): per column, rows
+// added top to bottom in fp32.
+void orc_ln_param_grad(const float *dy_a, const float *dy_b, const float *xhat, float *dgamma,
+                       float *dbeta, int rows, int d) {
+  for (int j = 0; j < d; j++) {
+    float dg = 0.0f, db = 0.0f;
+    for (int r = 0; r < rows; r++) {
+      const size_t i = static_cast<size_t>(r) * d + j;
+      const float dy = dy_b ? dy_a[i] + dy_b[i] : dy_a[i];
+      dg = fmaf(dy, xhat[i], dg);
+      db += dy;
+    }
+    dgamma[j] = dg;
+    dbeta[j] = db;
+  }
+}
+
+// The same sums carried in double: the value both fp32 summation orders (the
+// reference's top-to-bottom loop and the GPU's tree) approximate.
+void orc_ln_param_grad_f64(const float *dy_a, const float *dy_b, const float *xhat, double *dgamma,
+                           double *dbeta, int rows, int d) {
+  for (int j = 0; j < d; j++) {
+    double dg = 0.0, db = 0.0;
+    for (int r = 0; r < rows; r++) {
+      const size_t i = static_cast<size_t>(r) * d + j;
+      const float dy = dy_b ? dy_a[i] + dy_b[i] : dy_a[i];
+      dg += static_cast<double>(dy) * static_cast<double>(xhat[i]);
+      db += static_cast<double>(dy);
+    }
+    dgamma[j] = dg;
+    dbeta[j] = db;
+  }
+}
+
+// PositionalEncoding's constructor, src/positional_encoding.cuh:33-41.
+void orc_pe_table(float *table, int seq_len, int d) {
+  for (int pos = 0; pos < seq_len; pos++)
+    for (int i = 0; i < d; i++) {
+      const float angle =
+          static_cast<float>(pos) / powf(10000.0f, static_cast<float>(2 * (i / 2)) / d);
+      table[static_cast<size_t>(pos) * d + i] = (i % 2 == 0) ? sinf(angle) : cosf(angle);
+    }
+}
+
+// addPositionalEncodingKernel, src/positional_encoding.cuh:7-17.
+void orc_pe_add(const float *in, const float *pe, float *out, int batch, int seq_len, int d) {
+  const int64_t period = static_cast<int64_t>(seq_len) * d;
+  const int64_t total = period * batch;
+  for (int64_t i = 0; i < total; i++) out[i] = in[i] + pe[i % period];
+}
+
+// embeddingForwardKernel (src/embedding.cuh:8-17), optionally followed by
+// addPositionalEncodingKernel (src/positional_encoding.cuh:7-17).
+void orc_embed_gather(const float *table, const int32_t *ids, const float *pe, int seq_len,
+                      float *out, int num_tokens, int d) {
+  for (int t = 0; t < num_tokens; t++) {
+    const float *src = table + static_cast<size_t>(ids[t]) * d;
+    float *dst = out + static_cast<size_t>(t) * d;
+    if (pe) {
+      const float *p = pe + static_cast<size_t>(t % seq_len) * d;
+      for (int j = 0; j < d; j++) dst[j] = src[j] + p[j];
+    } else {
+      std::memcpy(dst, src, sizeof(float) * d);
+    }
+  }
+}
+
+// cudaMemset + embeddingBackwardKernel (src/embedding.cuh:19-30, 82-92).  The
+// reference adds with atomicAdd in whatever order the hardware picks; here the
+// tokens of a row are added in ascending token order.
+void orc_embed_scatter(const float *dy, const int32_t *ids, float *grad, int num_tokens, int vocab,
+                       int d) {
+  std::memset(grad, 0, sizeof(float) * static_cast<size_t>(vocab) * d);
+  for (int t = 0; t < num_tokens; t++) {
+    float *dst = grad + static_cast<size_t>(ids[t]) * d;
+    const float *src = dy + static_cast<size_t>(t) * d;
+    for (int j = 0; j < d; j++) dst[j] += src[j];
+  }
+}
+
+// The same sum in the association the CUDA kernel fixes: the tokens of a row in
+// ascending order; a row with more than `sub_len` tokens is cut into pieces of
+// sub_len tokens, each summed from 0.0f, and the pieces are added in order.
+void orc_embed_scatter_segmented(const float *dy, const int32_t *ids, float *grad, int num_tokens,
+                                 int vocab, int d, int sub_len) {
+  std::vector<std::vector<int>> rows(static_cast<size_t>(vocab));
+  for (int t = 0; t < num_tokens; t++) rows[ids[t]].push_back(t);
+  std::vector<float> part(static_cast<size_t>(d));
+  for (int v = 0; v < vocab; v++) {
+    float *dst = grad + static_cast<size_t>(v) * d;
+    for (int j = 0; j < d; j++) dst[j] = 0.0f;
+    const std::vector<int> &tok = rows[v];
+    const int n = static_cast<int>(tok.size());
+    if (n <= sub_len) {
+      for (int k = 0; k < n; k++)
+        for (int j = 0; j < d; j++) dst[j] += dy[static_cast<size_t>(tok[k]) * d + j];
+    } else {
+      for (int b = 0; b < n; b += sub_len) {
+        for (int j = 0; j < d; j++) part[j] = 0.0f;
+        for (int k = b; k < n && k < b + sub_len; k++)
+          for (int j = 0; j < d; j++) part[j] += dy[static_cast<size_t>(tok[k]) * d + j];
+        for (int j = 0; j < d; j++) dst[j] += part[j];
+      }
+    }
+  }
+}
+
+void orc_embed_scatter_f64(const float *dy, const int32_t *ids, double *grad, int num_tokens,
+                           int vocab, int d) {
+  for (size_t i = 0; i < static_cast<size_t>(vocab) * d; i++) grad[i] = 0.0;
+  for (int t = 0; t < num_tokens; t++)
+    for (int j = 0; j < d; j++)
+      grad[static_cast<size_t>(ids[t]) * d + j] += static_cast<double>(dy[static_cast<size_t>(t) * d + j]);
+}
+
+// Bias add at the end of linearLayerKernel (src/layers.cuh:34) followed by
+// reluKernel / sigmoidKernel / tanhActivationKernel / geluForwardKernel
+// (src/activation.cuh:5-10, 22-27, 39-45, 203-210).  kind: 0 relu, 1 sigmoid,
+// 2 tanh, 3 gelu.  `pre` (optional) receives x + bias.
+void orc_act_fwd(int kind, const float *x, const float *bias, float *y, float *pre_out, int64_t rows,
+                 int64_t cols) {
+  for (int64_t r = 0; r < rows; r++)
+    for (int64_t c = 0; c < cols; c++) {
+      const int64_t i = r * cols + c;
+      const float pre = bias ? x[i] + bias[c] : x[i];
+      if (pre_out) pre_out[i] = pre;
+      float out;
+      switch (kind) {
+        case 0: out = (pre > 0.0f) ? pre : 0.0f; break;
+        case 1: out = 1.0f / (1.0f + expf(-pre)); break;
+        case 2: out = tanhf(pre); break;
+        default: {
+          // 0.044715f * x * x * x is ((0.044715f*x)*x)*x; the outer add fuses with
+          // the last product.
+          const float inner = 0.7978845608f * fmaf(0.044715f * pre * pre, pre, pre);
+          const float cdf = 0.5f * (1.0f + tanhf(inner));
+          out = pre * cdf;
+        }
+      }
+      y[i] = out;
+    }
+}
+
+// reluBackwardKernel / sigmoidBackwardKernel / tanhBackwardKernel /
+// geluBackwardKernel (src/activation.cuh:12-20, 29-37, 47-55, 212-226;
+// tanhBackwardElementKernel, src/layers.cuh:247-254).  `cache` is what the
+// reference layer cached: the forward INPUT for relu and gelu, the forward
+// OUTPUT for sigmoid and tanh.
+void orc_act_bwd(int kind, const float *dy, const float *cache, float *dx, int64_t n) {
+  for (int64_t i = 0; i < n; i++) {
+    const float c = cache[i];
+    float out;
+    switch (kind) {
+      case 0: out = dy[i] * ((c > 0.0f) ? 1.0f : 0.0f); break;
+      case 1: out = dy[i] * c * (1.0f - c); break;
+      case 2: out = dy[i] * fmaf(-c, c, 1.0f); break;
+      default: {
+        const float x = c;
+        const float x3 = x * x * x;
+        const float inner = 0.7978845608f * fmaf(0.044715f, x3, x);
+        const float tanh_val = tanhf(inner);
+        const float sech2 = fmaf(-tanh_val, tanh_val, 1.0f);
+        const float d_inner = 0.7978845608f * fmaf(0.134145f * x, x, 1.0f);
+        const float cdf = 0.5f * (1.0f + tanh_val);
+        out = dy[i] * fmaf(x * 0.5f * sech2, d_inner, cdf);
+      }
+    }
+    dx[i] = out;
+  }
+}
+
+// linearBackwardBiasKernel, src/layers.cuh:70-82: per column, rows top to bottom.
+void orc_bias_grad(const float *dy, float *dbias, int64_t rows, int64_t cols) {
+  for (int64_t c = 0; c < cols; c++) {
+    float sum = 0.0f;
+    for (int64_t r = 0; r < rows; r++) sum += dy[r * cols + c];
+    dbias[c] = sum;
+  }
+}
+
+void orc_bias_grad_f64(const float *dy, double *dbias, int64_t rows, int64_t cols) {
+  for (int64_t c = 0; c < cols; c++) {
+    double sum = 0.0;
+    for (int64_t r = 0; r < rows; r++) sum += static_cast<double>(dy[r * cols + c]);
+    dbias[c] = sum;
+  }
+}
+
+// sgdUpdateKernel, src/layers.cuh:84-90: p -= lr*g (one fused multiply-add).
+void orc_sgd_update(float *p, const float *g, float lr, int64_t n) {
+  for (int64_t i = 0; i < n; i++) p[i] = fmaf(-lr, g[i], p[i]);
+}
+
+}  // extern "C"

@@ -1,0 +1,192 @@
+// TEST INFRASTRUCTURE -- NOT PART OF THE PRODUCT.
+//
+// Thin extern "C" doorway to the UNMODIFIED kernels and layer classes of the
+// reference (Cameron-Lyons/dl-cuda).  The reference sources are not copied:
+// this file includes them from where the reference checkout lies (the include
+// path is given on the nvcc command line by oracle/Makefile) and launches each
+// kernel with the reference's own grid and block sizes and its own cache
+// copies, on the default stream, as its layer classes do.  Built for sm_100;
+// only tests and the reference arm of bench.py load the resulting library.
+//
+// All pointers are device pointers unless named h_*.  Every function returns
+// the cudaGetLastError() code after its launches.
+#include "activation.cuh"
+#include "embedding.cuh"
+#include "layers.cuh"
+#include "positional_encoding.cuh"
+#include "sequential.cuh"
+#include "transformer.cuh"
+
+#include <cstdint>
+
+#define SHIM_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+inline int blocks_for(int n) { return (n + 255) / 256; }
+}  // namespace
+
+// src/transformer.cuh:499-502
+SHIM_API int ref_residual_add(const float *a, const float *b, float *out, int n) {
+  transformerResidualAddKernel<<<blocks_for(n), 256>>>(a, b, out, n);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/transformer.cuh:504-507
+SHIM_API int ref_ln_fwd(const float *in, const float *gamma, const float *beta, float *out,
+                        float *xhat, float *inv_std, int rows, int d, float eps) {
+  layerNormForwardCachingKernel<<<blocks_for(rows), 256>>>(in, gamma, beta, out, xhat, inv_std,
+                                                           rows, d, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/transformer.cuh:557-560
+SHIM_API int ref_ln_bwd(const float *dy, const float *xhat, const float *inv_std,
+                        const float *gamma, float *dx, float *dgamma, float *dbeta, int rows,
+                        int d) {
+  layerNormBackwardKernel<<<blocks_for(rows), 256>>>(dy, xhat, inv_std, gamma, dx, rows, d);
+  layerNormParamGradKernel<<<blocks_for(d), 256>>>(dy, xhat, dgamma, dbeta, rows, d);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/embedding.cuh:73-80
+SHIM_API int ref_embed_fwd(const float *table, const int *ids, float *out, int num_tokens, int d) {
+  embeddingForwardKernel<<<blocks_for(num_tokens * d), 256>>>(table, ids, out, num_tokens, d);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/embedding.cuh:82-92
+SHIM_API int ref_embed_bwd(const float *dy, const int *ids, float *grad, int num_tokens, int vocab,
+                           int d) {
+  cudaError_t e = cudaMemset(grad, 0, static_cast<size_t>(vocab) * d * sizeof(float));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  embeddingBackwardKernel<<<blocks_for(num_tokens * d), 256>>>(dy, ids, grad, num_tokens, d);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/positional_encoding.cuh:58-64
+SHIM_API int ref_pe_add(const float *in, const float *pe, float *out, int batch, int seq_len,
+                        int d) {
+  addPositionalEncodingKernel<<<blocks_for(batch * seq_len * d), 256>>>(in, pe, out, batch,
+                                                                        seq_len, d);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/positional_encoding.cuh:66-70
+SHIM_API int ref_pe_bwd(const float *dy, float *dx, int n) {
+  return static_cast<int>(
+      cudaMemcpy(dx, dy, static_cast<size_t>(n) * sizeof(float), cudaMemcpyDeviceToDevice));
+}
+
+// The table the reference's PositionalEncoding constructor uploads
+// (src/positional_encoding.cuh:26-45), read back through a forward pass over a
+// zero input so that no private member is touched.
+SHIM_API int ref_pe_table(float *h_table, int seq_len, int d) {
+  PositionalEncoding pe(1, seq_len, d);
+  const size_t n = static_cast<size_t>(seq_len) * d;
+  float *zero = nullptr, *out = nullptr;
+  if (cudaMalloc(&zero, n * sizeof(float)) != cudaSuccess) return -1;
+  if (cudaMalloc(&out, n * sizeof(float)) != cudaSuccess) return -1;
+  cudaMemset(zero, 0, n * sizeof(float));
+  pe.forward(zero, out);
+  cudaError_t e = cudaMemcpy(h_table, out, n * sizeof(float), cudaMemcpyDeviceToHost);
+  cudaFree(zero);
+  cudaFree(out);
+  return static_cast<int>(e);
+}
+
+// Activation forward as the layer classes run it, cache copy included
+// (src/activation.cuh:75-80, 107-112, 249-251, 278-283).  kind: 0 relu,
+// 1 sigmoid, 2 tanh, 3 gelu.  cache may be NULL (kernel only).
+SHIM_API int ref_act_fwd(int kind, const float *in, float *out, float *cache, int n) {
+  const size_t bytes = static_cast<size_t>(n) * sizeof(float);
+  if (cache && (kind == 0 || kind == 3)) cudaMemcpy(cache, in, bytes, cudaMemcpyDeviceToDevice);
+  switch (kind) {
+    case 0: reluKernel<<<blocks_for(n), 256>>>(in, out, n); break;
+    case 1: sigmoidKernel<<<blocks_for(n), 256>>>(in, out, n); break;
+    case 2: tanhActivationKernel<<<blocks_for(n), 256>>>(in, out, n); break;
+    default: geluForwardKernel<<<blocks_for(n), 256>>>(in, out, n); break;
+  }
+  if (cache && (kind == 1 || kind == 2)) cudaMemcpy(cache, out, bytes, cudaMemcpyDeviceToDevice);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/activation.cuh:82-86, 114-118, 253-257, 285-289
+SHIM_API int ref_act_bwd(int kind, const float *dy, const float *cache, float *dx, int n) {
+  switch (kind) {
+    case 0: reluBackwardKernel<<<blocks_for(n), 256>>>(dy, cache, dx, n); break;
+    case 1: sigmoidBackwardKernel<<<blocks_for(n), 256>>>(dy, cache, dx, n); break;
+    case 2: tanhBackwardKernel<<<blocks_for(n), 256>>>(dy, cache, dx, n); break;
+    default: geluBackwardKernel<<<blocks_for(n), 256>>>(dy, cache, dx, n); break;
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/layers.cuh:247-254 (the twin of tanhBackwardKernel used by ElmanRNNLayer)
+SHIM_API int ref_tanh_bwd_element(const float *dh, const float *h, float *d_pre, int n) {
+  tanhBackwardElementKernel<<<blocks_for(n), NUM_THREADS>>>(dh, h, d_pre, n);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/layers.cuh:70-82, launched as at src/transformer.cuh:590-591
+SHIM_API int ref_bias_grad(const float *dy, float *dbias, int rows, int cols) {
+  linearBackwardBiasKernel<<<blocks_for(cols), 256>>>(dy, dbias, rows, cols);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The bias add of the reference lives in the last line of its GEMM kernel
+// (src/layers.cuh:34): Y = sum + b[col].  With in_features = 1, X = pre-bias
+// value and W = 1 that kernel computes exactly x*1 + b[col]; rather than drag a
+// GEMM in, the same broadcast add is taken from addPositionalEncodingKernel
+// (out = in + table[idx mod cols]), which is the identical fp32 add.
+SHIM_API int ref_bias_add(const float *x, const float *bias, float *out, int rows, int cols) {
+  addPositionalEncodingKernel<<<blocks_for(rows * cols), 256>>>(x, bias, out, rows, 1, cols);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src/layers.cuh:84-90
+SHIM_API int ref_sgd(float *p, const float *g, float lr, int n) {
+  sgdUpdateKernel<<<blocks_for(n), 256>>>(p, g, lr, n);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// EmbeddingLayer as a whole (src/embedding.cuh:32-104): construct with the given
+// global seed, copy the cuRAND-initialised table out, optionally write the DLCU
+// checkpoint of a Sequential holding just this layer (src/sequential.cuh:161-205).
+SHIM_API int ref_embedding_init(uint64_t seed, int vocab, int d, int num_tokens, float *h_table,
+                                const char *checkpoint_path) {
+  set_global_init_seed(seed);
+  EmbeddingLayer layer(vocab, d, num_tokens);
+  auto groups = layer.get_param_groups();
+  cudaError_t e = cudaMemcpy(h_table, groups[0].params,
+                             static_cast<size_t>(groups[0].size) * sizeof(float),
+                             cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (checkpoint_path) {
+    Sequential model;
+    model.add(&layer);
+    if (!model.save_weights(checkpoint_path)) return -2;
+  }
+  return 0;
+}
+
+// The reference's own known-answer test of the embedding layer
+// (tests/gpu_correctness_tests.cu:196-252), driven through the class API:
+// returns forward output [num_tokens*d] and table gradient [vocab*d].
+SHIM_API int ref_embedding_layer_run(const float *h_table, const int *h_ids, const float *h_dout,
+                                     int vocab, int d, int num_tokens, float *h_out,
+                                     float *h_grad) {
+  EmbeddingLayer layer(vocab, d, num_tokens);
+  auto groups = layer.get_param_groups();
+  const size_t tn = static_cast<size_t>(vocab) * d, on = static_cast<size_t>(num_tokens) * d;
+  cudaMemcpy(groups[0].params, h_table, tn * sizeof(float), cudaMemcpyHostToDevice);
+  layer.set_token_ids(h_ids);
+  float *d_out = nullptr;
+  if (cudaMalloc(&d_out, on * sizeof(float)) != cudaSuccess) return -1;
+  layer.forward(nullptr, d_out);
+  cudaMemcpy(h_out, d_out, on * sizeof(float), cudaMemcpyDeviceToHost);
+  cudaMemcpy(d_out, h_dout, on * sizeof(float), cudaMemcpyHostToDevice);
+  layer.backward(d_out, nullptr);
+  cudaError_t e = cudaMemcpy(h_grad, groups[0].grads, tn * sizeof(float), cudaMemcpyDeviceToHost);
+  cudaFree(d_out);
+  return static_cast<int>(e);
+}

@@ -1,0 +1,167 @@
+"""Token embedding: gather (+ sinusoidal PE) and the deterministic scatter-add of
+the table gradient, through the C ABI, against the oracle, the reference's
+known-answer vectors and (where present) the reference's own kernels."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits_equal, rel_err, rng_for, zipf_ids
+from dl_cuda_b200 import capi, ops
+from oracle import cpu as oracle
+from oracle import ref as refshim
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(x, dtype=None):
+    if x is None:
+        return None
+    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def scatter(dy_t, ids_t, vocab):
+    ws = ops.embed_sort_tokens(ids_t, vocab, dy_t.shape[1])
+    return ops.embed_scatter_bwd(dy_t, ids_t, vocab, ws)
+
+
+def test_reference_known_answer():
+    # tests/gpu_correctness_tests.cu:196-252 of the reference
+    table = np.arange(15, dtype=np.float32).reshape(5, 3)
+    ids = np.array([1, 3, 1, 4], np.int32)
+    dout = np.repeat(np.arange(1, 5, dtype=np.float32)[:, None], 3, axis=1)
+    out = ops.embed_gather_fwd(dev(table), dev(ids)).cpu().numpy()
+    assert np.array_equal(out, np.array([[3, 4, 5], [9, 10, 11], [3, 4, 5], [12, 13, 14]], np.float32))
+    grad = scatter(dev(dout), dev(ids), 5).cpu().numpy()
+    want = np.zeros((5, 3), np.float32)
+    want[1], want[3], want[4] = 4.0, 2.0, 4.0
+    assert np.array_equal(grad, want)
+    if refshim.available():
+        out_r, grad_r = refshim.embedding_layer_run(table, ids, dout)
+        assert np.array_equal(out, out_r) and np.array_equal(grad, grad_r)
+
+
+CASES = [  # vocab, d, batch, seq
+    (65, 64, 32, 64), (5, 3, 1, 4), (30, 64, 1, 64), (1000, 256, 4, 128), (50, 12, 3, 21), (7, 1024, 2, 9),
+    (300, 4096, 2, 50), (129, 100, 5, 33), (17, 8200, 1, 6), (40000, 8, 8, 512), (2, 16, 1, 1),
+]
+
+
+@pytest.mark.parametrize("vocab,d,batch,seq", CASES)
+def test_gather_pe_bit_exact(vocab, d, batch, seq):
+    n = batch * seq
+    table = (0.02 * rng_for(10, 0).standard_normal((vocab, d))).astype(np.float32)
+    ids = rng_for(10, 1).integers(0, vocab, n).astype(np.int32)
+    ids[0], ids[-1] = 0, vocab - 1
+    pe = ops.pe_table(seq, d)
+    assert bits_equal(pe.numpy(), oracle.pe_table(seq, d))
+    ttable, tids, tpe = dev(table), dev(ids), pe.cuda()
+    fused = ops.embed_gather_fwd(ttable, tids, tpe, seq).cpu().numpy()
+    assert bits_equal(fused, oracle.embed_gather(table, ids, pe.numpy(), seq))
+    plain = ops.embed_gather_fwd(ttable, tids)
+    assert bits_equal(plain.cpu().numpy(), oracle.embed_gather(table, ids))
+    # the unfused PE layer gives the same bits as the fused gather
+    added = ops.pe_add_fwd(plain.view(batch, seq, d), tpe)
+    assert bits_equal(added.cpu().numpy().reshape(n, d), fused)
+    assert bits_equal(added.cpu().numpy(), oracle.pe_add(plain.cpu().numpy().reshape(batch, seq, d), pe.numpy()))
+    if refshim.available():
+        g_r = refshim.embed_fwd(ttable, tids)
+        assert bits_equal(plain.cpu().numpy(), g_r.cpu().numpy())
+        assert bits_equal(added.cpu().numpy(), refshim.pe_add(g_r.view(batch, seq, d), tpe).cpu().numpy())
+        assert bits_equal(pe.numpy(), refshim.pe_table(seq, d).numpy())
+    # backward of PE is the identity
+    assert torch.equal(ops.pe_add_bwd(added), added)
+
+
+@pytest.mark.parametrize("vocab,d,batch,seq", CASES)
+def test_scatter_add_vs_oracle(vocab, d, batch, seq):
+    n = batch * seq
+    ids = zipf_ids(rng_for(20, 0), n, vocab)
+    dy = rng_for(20, 1).standard_normal((n, d)).astype(np.float32)
+    grad = scatter(dev(dy), dev(ids), vocab).cpu().numpy()
+    # the kernel's association is restated exactly by the segmented oracle: bit-equal
+    assert bits_equal(grad, oracle.embed_scatter(dy, ids, vocab, "segmented"))
+    assert rel_err(grad, oracle.embed_scatter(dy, ids, vocab, "f64")) <= 1e-5
+    assert rel_err(grad, oracle.embed_scatter(dy, ids, vocab, "sequential")) <= 1e-5
+    if refshim.available():
+        assert rel_err(grad, refshim.embed_bwd(dev(dy), dev(ids), vocab).cpu().numpy()) <= 1e-5
+
+
+@pytest.mark.parametrize("pattern", ["all_same", "two_hot", "ascending", "descending", "ends"])
+def test_scatter_add_edge_patterns(pattern):
+    vocab, d, n = 300, 128, 5000
+    if pattern == "all_same":
+        ids = np.full(n, 123, np.int32)
+    elif pattern == "two_hot":
+        ids = np.where(np.arange(n) % 3 == 0, 7, 290).astype(np.int32)
+    elif pattern == "ascending":
+        ids = (np.arange(n) % vocab).astype(np.int32)
+    elif pattern == "descending":
+        ids = (vocab - 1 - np.arange(n) % vocab).astype(np.int32)
+    else:
+        ids = np.where(np.arange(n) % 2 == 0, 0, vocab - 1).astype(np.int32)
+    dy = rng_for(30, 0).standard_normal((n, d)).astype(np.float32)
+    grad = scatter(dev(dy), dev(ids), vocab).cpu().numpy()
+    assert bits_equal(grad, oracle.embed_scatter(dy, ids, vocab, "segmented"))
+    assert rel_err(grad, oracle.embed_scatter(dy, ids, vocab, "f64")) <= 1e-5
+
+
+def test_scatter_add_is_deterministic_and_overwrites():
+    vocab, d, n = 2000, 512, 16384
+    ids = zipf_ids(rng_for(40, 0), n, vocab)
+    dy = rng_for(40, 1).standard_normal((n, d)).astype(np.float32)
+    tdy, tids = dev(dy), dev(ids)
+    ws = ops.embed_sort_tokens(tids, vocab, d)
+    grad = torch.full((vocab, d), 7.0, device="cuda")  # stale contents must vanish
+    ops.embed_scatter_bwd(tdy, tids, vocab, ws, grad=grad)
+    first = grad.clone()
+    for _ in range(3):
+        ws2 = ops.embed_sort_tokens(tids, vocab, d)
+        again = ops.embed_scatter_bwd(tdy, tids, vocab, ws2)
+        assert torch.equal(first, again)
+    untouched = np.setdiff1d(np.arange(vocab), ids)
+    assert float(first[torch.from_numpy(untouched).cuda()].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("vocab,d,n", [(1000, 256, 512), (65, 64, 2048), (300, 4096, 100)])
+def test_embedding_bf16_storage(vocab, d, n):
+    bf = torch.bfloat16
+    table = dev((0.02 * rng_for(50, 0).standard_normal((vocab, d))).astype(np.float32), bf)
+    ids = zipf_ids(rng_for(50, 1), n, vocab)
+    seq = n // 4
+    pe = ops.pe_table(seq, d)
+    out = ops.embed_gather_fwd(table, dev(ids), pe.cuda(), seq)
+    want = oracle.embed_gather(table.float().cpu().numpy(), ids, pe.numpy(), seq)
+    assert out.dtype == bf
+    assert rel_err(out.float().cpu().numpy(), want) <= 1e-2
+    dy = dev(rng_for(50, 2).standard_normal((n, d)).astype(np.float32), bf)
+    grad = scatter(dy, dev(ids), vocab)
+    assert grad.dtype == torch.float32
+    # fp32 accumulation of bf16 inputs in the same association: bit-equal to the oracle
+    assert bits_equal(grad.cpu().numpy(), oracle.embed_scatter(dy.float().cpu().numpy(), ids, vocab, "segmented"))
+
+
+def test_out_of_range_ids_stay_inside_the_table():
+    table = np.arange(12, dtype=np.float32).reshape(4, 3)
+    ids = np.array([0, 3, 99, -5], np.int32)
+    out = ops.embed_gather_fwd(dev(table), dev(ids)).cpu().numpy()
+    assert np.array_equal(out[2], table[3]) and np.array_equal(out[3], table[0])
+
+
+def test_sgd_update_matches_reference_formula():
+    p = rng_for(60, 0).standard_normal(10007).astype(np.float32)
+    g = rng_for(60, 1).standard_normal(10007).astype(np.float32)
+    got = ops.sgd_update(dev(p), dev(g), 0.05).cpu().numpy()
+    assert bits_equal(got, oracle.sgd_update(p, g, 0.05))
+    if refshim.available():
+        assert bits_equal(got, refshim.sgd(dev(p), dev(g), 0.05).cpu().numpy())
+
+
+def test_residual_add_bit_exact():
+    for n in (1, 7, 1024, 100003):
+        a = rng_for(70, 0).standard_normal(n).astype(np.float32)
+        b = rng_for(70, 1).standard_normal(n).astype(np.float32)
+        got = ops.residual_add(dev(a), dev(b)).cpu().numpy()
+        assert bits_equal(got, oracle.residual_add(a, b))
+        if refshim.available():
+            assert bits_equal(got, refshim.residual_add(dev(a), dev(b)).cpu().numpy())
