@@ -120,10 +120,11 @@ act_fwd_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, in
   const bool col_ok = cv < ncv;
   const int ty = blockDim.y;
 
+  const bool has_bias = bias != nullptr;
   float bv[E];
 #pragma unroll
   for (int e = 0; e < E; e++) bv[e] = 0.f;
-  if (bias != nullptr && col_ok) {
+  if (has_bias && col_ok) {
 #pragma unroll
     for (int q = 0; q < E / 4; q++) {
       const float4 b4 = ld_keep_f4(bias + cv * E + 4 * q);
@@ -152,7 +153,8 @@ act_fwd_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, in
         S::unpack(in[u], v);
 #pragma unroll
         for (int e = 0; e < E; e++) {
-          const float pre = v[e] + bv[e];
+          // Without a bias the value passes through untouched (x + 0.0f would turn -0.0f into +0.0f).
+          const float pre = has_bias ? v[e] + bv[e] : v[e];
           v[e] = pre;
           out[e] = act_forward<KIND>(pre);
           if (KIND == DLB_ACT_RELU && pre > 0.0f) bits |= 1u << e;

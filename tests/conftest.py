@@ -60,10 +60,22 @@ def ulp_diff(got, want) -> int:
     return int(diff.max()) if diff.size else 0
 
 
-def bits_equal(got, want) -> bool:
+def bits_identical(got, want) -> bool:
+    """Same 32-bit patterns everywhere (used GPU against GPU)."""
     g = np.ascontiguousarray(got, dtype=np.float32)
     w = np.ascontiguousarray(want, dtype=np.float32)
     return g.shape == w.shape and bool(np.array_equal(g.view(np.uint32), w.view(np.uint32)))
+
+
+def bits_equal(got, want) -> bool:
+    """Same 32-bit patterns, except that a NaN matches a NaN: x86 and the GPU produce
+    different default-NaN payloads for inf*0, which is not a difference of value."""
+    g = np.ascontiguousarray(got, dtype=np.float32)
+    w = np.ascontiguousarray(want, dtype=np.float32)
+    if g.shape != w.shape:
+        return False
+    same = (g.view(np.uint32) == w.view(np.uint32)) | (np.isnan(g) & np.isnan(w))
+    return bool(same.all())
 
 
 def zipf_ids(rng: np.random.Generator, n: int, vocab: int, s: float = 1.1, permute: bool = True):

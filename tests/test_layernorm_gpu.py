@@ -58,7 +58,10 @@ def test_ln_fwd_bwd_fp32_vs_oracle(rows, d, two_inputs):
     # backward from the oracle's caches so that forward differences do not leak in
     dx, dg, db = ops.ln_bwd(dev(dy_a), dev(dy_b), dev(xhat0), dev(inv0), dev(gamma))
     dx0, dg0, db0 = oracle.ln_bwd(dy_a, dy_b, xhat0, inv0, gamma)
-    assert rel_err(dx.cpu().numpy(), dx0) <= FP32_TOL
+    if d == 1:  # dx is exactly zero in exact arithmetic; only rounding residue of dy*gamma remains
+        assert np.abs(dx.cpu().numpy()).max() <= 1e-4 * np.abs(dy_a).max() * 4
+    else:
+        assert rel_err(dx.cpu().numpy(), dx0) <= FP32_TOL
     dg64, db64 = oracle.ln_param_grad_f64(dy_a, dy_b, xhat0)
     assert rel_err(dg.cpu().numpy(), dg64) <= FP32_TOL
     assert rel_err(db.cpu().numpy(), db64) <= FP32_TOL
