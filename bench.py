@@ -1,0 +1,640 @@
+#!/usr/bin/env python
+"""Benchmark of the fused layer kernels: the token-sharded transformer-block chain.
+
+A "step" is one forward + backward pass of the non-GEMM chain of a transformer
+block over one batch of synthetic tokens (batch 8 x seq 4096, d_model 4096,
+d_ff 16384, vocab 32000, bf16 storage, fp32 arithmetic):
+
+    forward   sort token ids -> embedding gather + positional encoding
+              -> LN1(x + attn_out) -> bias + ReLU on the d_ff activation -> LN2(y1 + ff_out)
+    backward  LN2 bwd -> ReLU bwd (+ bias grad) -> LN1 bwd with the gradient
+              residual add folded in -> embedding-table scatter-add
+              -> (N > 1) all-reduce of the gamma/beta/bias and table gradients
+
+Random-normal tensors stand in for the GEMM outputs (attn_out, the d_ff
+pre-activation, ff_out and the matching upstream gradients); they live on the
+device, as the reference's own intermediate buffers do.  Token rows are split
+evenly over the N ranks (strong scaling: the global batch is fixed).
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference ...                     # the reference's own CUDA kernels
+
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+BATCH, SEQ, D_MODEL, D_FF, VOCAB = 8, 4096, 4096, 16384, 32000
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+# --------------------------------------------------------------------------- utilities
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def zipf_ids(rng, n, vocab, s=1.1):
+    """Bounded Zipf over [0, vocab), hot ids spread over the table by a fixed permutation."""
+    p = np.arange(1, vocab + 1, dtype=np.float64) ** (-s)
+    p /= p.sum()
+    ids = rng.choice(vocab, size=n, p=p)
+    perm = np.random.Generator(np.random.Philox(key=77)).permutation(vocab)
+    return perm[ids].astype(np.int32)
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, device_index: int, period_s: float = 0.002):
+        self.samples, self.reasons, self.power = [], set(), []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._period = period_s
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            try:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self._nv = pynvml
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    _NAMES = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown",
+    }
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                for bit, name in self._NAMES.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
+            except Exception:
+                pass
+            time.sleep(self._period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples),
+                "power_w_max": round(max(self.power), 1) if self.power else None}
+
+
+class Dist:
+    def __init__(self):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.active = self.world > 1
+
+    def init(self):
+        torch.cuda.set_device(self.local_rank)
+        if self.active:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29500")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.dist = dist
+
+    def barrier(self):
+        if self.active:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_float(self, v: float) -> float:
+        if not self.active:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def finish(self):
+        if self.active:
+            self.dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- the chain (this library)
+class Chain:
+    """Buffers and the step of the block chain for `tokens` local token rows."""
+
+    OPS = ["sort_tokens", "embed_gather_pe", "ln1_fwd", "relu_fwd", "ln2_fwd",
+           "ln2_bwd", "relu_bwd", "ln1_bwd", "embed_scatter", "allreduce"]
+
+    def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist):
+        from dl_cuda_b200 import capi, ops
+        self.capi, self.ops, self.lib = capi, ops, capi.lib()
+        self.T, self.S, self.D, self.F, self.V = tokens, seq, d, f, vocab
+        self.dist = dist
+        self.dtype = dtype
+        self.code = capi.BF16 if dtype == torch.bfloat16 else capi.F32
+        self.e = 2 if dtype == torch.bfloat16 else 4
+        dev = torch.device("cuda", torch.cuda.current_device())
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)
+
+        def randn(*shape, scale=1.0):
+            return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * scale).to(dtype)
+
+        T, D, F, V = tokens, d, f, vocab
+        # parameters (replicated on every rank)
+        gp = torch.Generator(device=dev)
+        gp.manual_seed(4242)
+        self.table = (torch.randn(V, D, generator=gp, device=dev) * 0.02).to(dtype)
+        self.pe = ops.pe_table(seq, D).to(dev)
+        self.gamma1 = torch.rand(D, generator=gp, device=dev) + 0.5
+        self.beta1 = torch.randn(D, generator=gp, device=dev) * 0.1
+        self.gamma2 = torch.rand(D, generator=gp, device=dev) + 0.5
+        self.beta2 = torch.randn(D, generator=gp, device=dev) * 0.1
+        self.bias1 = torch.randn(F, generator=gp, device=dev) * 0.1
+        # token ids: pinned host copy (the only per-step host input) and device copy
+        rng = np.random.Generator(np.random.Philox(key=seed))
+        self.h_ids = torch.from_numpy(zipf_ids(rng, T, V)).pin_memory()
+        self.ids = self.h_ids.to(dev)
+        # stand-ins for GEMM outputs
+        self.attn_out, self.ff_out = randn(T, D), randn(T, D)
+        self.ff_pre = randn(T, F)
+        self.dy, self.d_ff_in = randn(T, D), randn(T, D)
+        self.d_act = randn(T, F)
+        # activations, caches, gradients
+        e = lambda *s: torch.empty(*s, device=dev, dtype=dtype)
+        self.x0, self.y1, self.xhat1, self.y2, self.xhat2 = e(T, D), e(T, D), e(T, D), e(T, D), e(T, D)
+        self.inv1 = torch.empty(T, device=dev)
+        self.inv2 = torch.empty(T, device=dev)
+        self.act = e(T, F)
+        self.mask = torch.empty(self.lib.dlb_act_cache_bytes(capi.RELU, T * F, self.code), dtype=torch.uint8, device=dev)
+        self.dx2, self.dx1 = e(T, D), e(T, D)
+        self.d_pre = e(T, F)
+        # every small parameter gradient sits in one buffer: one all-reduce
+        self.small_grads = torch.empty(4 * D + F, device=dev)
+        self.dgamma1, self.dbeta1 = self.small_grads[0:D], self.small_grads[D:2 * D]
+        self.dgamma2, self.dbeta2 = self.small_grads[2 * D:3 * D], self.small_grads[3 * D:4 * D]
+        self.dbias1 = self.small_grads[4 * D:]
+        self.table_grad = torch.empty(V, D, device=dev)
+        self.ws_ln = ops.ln_bwd_workspace(T, D, dev)
+        self.ws_act = ops.act_bwd_workspace(capi.RELU, T, F, dev)
+        self.ws_embed = ops.embed_workspace(T, V, D, dev)
+        self.h_result = torch.empty(4 * D + F, dtype=torch.float32).pin_memory()
+        self.distinct_ids = int(np.unique(self.h_ids.numpy()).size)
+
+    # algorithmic HBM bytes of each op for the local tokens (each input byte read once,
+    # each output byte written once)
+    def bytes_per_op(self):
+        T, D, F, V, S, e = self.T, self.D, self.F, self.V, self.S, self.e
+        pos_rows = min(S, T)
+        return {
+            "sort_tokens": 0,
+            "embed_gather_pe": (self.distinct_ids + T) * D * e + pos_rows * D * 4 + T * 4,
+            "ln1_fwd": T * D * 4 * e + T * 4 + 2 * D * 4,
+            "ln2_fwd": T * D * 4 * e + T * 4 + 2 * D * 4,
+            "relu_fwd": T * F * 2 * e + T * F // 8 + F * 4,
+            "relu_bwd": T * F * 2 * e + T * F // 8 + F * 4,
+            "ln2_bwd": T * D * 3 * e + T * 4 + 3 * D * 4,
+            "ln1_bwd": T * D * 4 * e + T * 4 + 3 * D * 4,
+            "embed_scatter": T * D * e + V * D * 4 + T * 4,
+            "allreduce": 0,
+        }
+
+    def step(self, marks=None, copy_inputs=False):
+        lib, capi, st = self.lib, self.capi, torch.cuda.current_stream().cuda_stream
+        p = lambda t: t.data_ptr()
+        T, D, F, V, S, code = self.T, self.D, self.F, self.V, self.S, self.code
+        chk = capi.check
+
+        def mark():
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append(ev)
+
+        if copy_inputs:
+            self.ids.copy_(self.h_ids, non_blocking=True)
+        mark()
+        chk(lib.dlb_embed_sort_tokens(p(self.ids), p(self.ws_embed), self.ws_embed.numel(), T, V, D, st))
+        mark()
+        chk(lib.dlb_embed_gather_fwd(p(self.table), p(self.ids), p(self.pe), S, p(self.x0), T, V, D, code, st))
+        mark()
+        chk(lib.dlb_ln_residual_fwd(p(self.x0), p(self.attn_out), p(self.gamma1), p(self.beta1), p(self.y1),
+                                    p(self.xhat1), p(self.inv1), T, D, 1e-5, code, st))
+        mark()
+        chk(lib.dlb_act_fwd(capi.RELU, p(self.ff_pre), p(self.bias1), p(self.act), p(self.mask), T, F, code, st))
+        mark()
+        chk(lib.dlb_ln_residual_fwd(p(self.y1), p(self.ff_out), p(self.gamma2), p(self.beta2), p(self.y2),
+                                    p(self.xhat2), p(self.inv2), T, D, 1e-5, code, st))
+        mark()
+        chk(lib.dlb_ln_bwd(p(self.dy), None, p(self.xhat2), p(self.inv2), p(self.gamma2), p(self.dx2),
+                           p(self.dgamma2), p(self.dbeta2), p(self.ws_ln), self.ws_ln.numel(), T, D, code, st))
+        mark()
+        chk(lib.dlb_act_bwd(capi.RELU, p(self.d_act), p(self.mask), p(self.d_pre), p(self.dbias1), p(self.ws_act),
+                            self.ws_act.numel(), T, F, code, st))
+        mark()
+        chk(lib.dlb_ln_bwd(p(self.dx2), p(self.d_ff_in), p(self.xhat1), p(self.inv1), p(self.gamma1), p(self.dx1),
+                           p(self.dgamma1), p(self.dbeta1), p(self.ws_ln), self.ws_ln.numel(), T, D, code, st))
+        mark()
+        chk(lib.dlb_embed_scatter_bwd(p(self.dx1), p(self.ids), p(self.table_grad), p(self.ws_embed),
+                                      self.ws_embed.numel(), T, V, D, code, st))
+        mark()
+        if self.dist.active:
+            self.dist.dist.all_reduce(self.small_grads)
+            self.dist.dist.all_reduce(self.table_grad)
+        mark()
+        if copy_inputs:
+            self.h_result.copy_(self.small_grads, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return float(self.h_result[0])
+        return None
+
+
+# --------------------------------------------------------------------------- the chain (reference kernels)
+class ReferenceChain:
+    """The same chain through the reference's own CUDA kernels (fp32 only, default stream)."""
+
+    def __init__(self, tokens, seq, d, f, vocab, seed):
+        from oracle import ref
+        self.ref = ref
+        dev = torch.device("cuda", torch.cuda.current_device())
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)
+        randn = lambda *s: torch.randn(*s, generator=g, device=dev)
+        T, D, F, V = tokens, d, f, vocab
+        self.T, self.S, self.D, self.F, self.V = T, seq, D, F, V
+        self.table = randn(V, D) * 0.02
+        self.pe = ref.pe_table(seq, D).to(dev)
+        self.gamma = torch.rand(D, generator=g, device=dev) + 0.5
+        self.beta = randn(D) * 0.1
+        rng = np.random.Generator(np.random.Philox(key=seed))
+        self.h_ids = torch.from_numpy(zipf_ids(rng, T, V)).pin_memory()
+        self.ids = self.h_ids.to(dev)
+        self.attn_out, self.ff_out, self.dy, self.d_ff_in = randn(T, D), randn(T, D), randn(T, D), randn(T, D)
+        self.ff_pre, self.d_act = randn(T, F), randn(T, F)
+        e = lambda *s: torch.empty(*s, device=dev)
+        self.emb, self.x0, self.res, self.y1, self.xhat1, self.y2, self.xhat2 = (e(T, D) for _ in range(7))
+        self.inv1, self.inv2 = e(T), e(T)
+        self.act, self.relu_cache, self.d_pre = e(T, F), e(T, F), e(T, F)
+        self.dx2, self.dsum, self.dx1, self.dpe = e(T, D), e(T, D), e(T, D), e(T, D)
+        self.small = e(4 * D + F)
+        self.table_grad = e(V, D)
+        self.h_result = torch.empty(4 * D + F).pin_memory()
+
+    def step(self, copy_inputs=False):
+        r, D, F = self.ref, self.D, self.F
+        B = self.T // self.S if self.T >= self.S else 1
+        S = min(self.S, self.T)
+        if copy_inputs:
+            self.ids.copy_(self.h_ids, non_blocking=True)
+        r.lib().ref_embed_fwd(self.table.data_ptr(), self.ids.data_ptr(), self.emb.data_ptr(), self.T, D)
+        r.lib().ref_pe_add(self.emb.data_ptr(), self.pe.data_ptr(), self.x0.data_ptr(), B, S, D)
+        n = self.T * D
+        r.lib().ref_residual_add(self.x0.data_ptr(), self.attn_out.data_ptr(), self.res.data_ptr(), n)
+        r.lib().ref_ln_fwd(self.res.data_ptr(), self.gamma.data_ptr(), self.beta.data_ptr(), self.y1.data_ptr(),
+                           self.xhat1.data_ptr(), self.inv1.data_ptr(), self.T, D, 1e-5)
+        # the bias add of the reference is the last line of its GEMM kernel: nothing extra to time
+        r.lib().ref_act_fwd(0, self.ff_pre.data_ptr(), self.act.data_ptr(), self.relu_cache.data_ptr(), self.T * F)
+        r.lib().ref_residual_add(self.y1.data_ptr(), self.ff_out.data_ptr(), self.res.data_ptr(), n)
+        r.lib().ref_ln_fwd(self.res.data_ptr(), self.gamma.data_ptr(), self.beta.data_ptr(), self.y2.data_ptr(),
+                           self.xhat2.data_ptr(), self.inv2.data_ptr(), self.T, D, 1e-5)
+        s = self.small
+        r.lib().ref_ln_bwd(self.dy.data_ptr(), self.xhat2.data_ptr(), self.inv2.data_ptr(), self.gamma.data_ptr(),
+                           self.dx2.data_ptr(), s[2 * D:].data_ptr(), s[3 * D:].data_ptr(), self.T, D)
+        r.lib().ref_act_bwd(0, self.d_act.data_ptr(), self.relu_cache.data_ptr(), self.d_pre.data_ptr(), self.T * F)
+        r.lib().ref_bias_grad(self.d_pre.data_ptr(), s[4 * D:].data_ptr(), self.T, F)
+        r.lib().ref_residual_add(self.dx2.data_ptr(), self.d_ff_in.data_ptr(), self.dsum.data_ptr(), n)
+        r.lib().ref_ln_bwd(self.dsum.data_ptr(), self.xhat1.data_ptr(), self.inv1.data_ptr(), self.gamma.data_ptr(),
+                           self.dx1.data_ptr(), s[0:].data_ptr(), s[D:].data_ptr(), self.T, D)
+        r.lib().ref_pe_bwd(self.dx1.data_ptr(), self.dpe.data_ptr(), n)
+        code = r.lib().ref_embed_bwd(self.dpe.data_ptr(), self.ids.data_ptr(), self.table_grad.data_ptr(), self.T,
+                                     self.V, D)
+        if code != 0:
+            raise RuntimeError(f"reference kernels failed: CUDA error {code}")
+        if copy_inputs:
+            self.h_result.copy_(self.small, non_blocking=True)
+            torch.cuda.synchronize()
+            return float(self.h_result[0])
+        return None
+
+
+# --------------------------------------------------------------------------- host baseline
+def cpu_baseline(sample_tokens=4096):
+    """The chain through the single-threaded host loops of oracle/host_ref.cpp on a slice of
+    the tokens (fp32 host arrays; the table gradient is produced at full vocabulary size)."""
+    from oracle import cpu
+    lib = cpu.lib()
+    T, D, F, V, S = sample_tokens, D_MODEL, D_FF, VOCAB, SEQ
+    rng = np.random.Generator(np.random.Philox(key=9))
+    f32 = lambda *s: rng.standard_normal(s, dtype=np.float32)
+    table, pe = f32(V, D) * np.float32(0.02), cpu.pe_table(S, D)
+    ids = zipf_ids(rng, T, V)
+    attn, ffo, dy, dffi = f32(T, D), f32(T, D), f32(T, D), f32(T, D)
+    ffpre, dact = f32(T, F), f32(T, F)
+    gamma, beta, bias = np.ones(D, np.float32), np.zeros(D, np.float32), np.zeros(F, np.float32)
+    z = lambda *s: np.zeros(s, np.float32)  # zeros: pages are touched before the clock starts
+    x0, y1, xh1, y2, xh2, dx2, dx1 = (z(T, D) for _ in range(7))
+    inv1, inv2 = z(T), z(T)
+    act, pre, dpre = z(T, F), z(T, F), z(T, F)
+    dg, db, dbias, grad = z(D), z(D), z(F), z(V, D)
+    P = lambda a: ctypes.c_void_p(a.ctypes.data)
+    i64 = ctypes.c_int64
+    t0 = time.perf_counter()
+    lib.orc_embed_gather(P(table), P(ids), P(pe), S, P(x0), T, D)
+    lib.orc_ln_residual_fwd(P(x0), P(attn), P(gamma), P(beta), P(y1), P(xh1), P(inv1), T, D, ctypes.c_float(1e-5))
+    lib.orc_act_fwd(0, P(ffpre), P(bias), P(act), P(pre), i64(T), i64(F))
+    lib.orc_ln_residual_fwd(P(y1), P(ffo), P(gamma), P(beta), P(y2), P(xh2), P(inv2), T, D, ctypes.c_float(1e-5))
+    lib.orc_ln_bwd_dx(P(dy), None, P(xh2), P(inv2), P(gamma), P(dx2), T, D)
+    lib.orc_ln_param_grad(P(dy), None, P(xh2), P(dg), P(db), T, D)
+    lib.orc_act_bwd(0, P(dact), P(pre), P(dpre), i64(T * F))
+    lib.orc_bias_grad(P(dpre), P(dbias), i64(T), i64(F))
+    lib.orc_ln_bwd_dx(P(dx2), P(dffi), P(xh1), P(inv1), P(gamma), P(dx1), T, D)
+    lib.orc_ln_param_grad(P(dx2), P(dffi), P(xh1), P(dg), P(db), T, D)
+    lib.orc_embed_scatter(P(dx1), P(ids), P(grad), T, V, D)
+    dt = time.perf_counter() - t0
+    return {"value": T / dt, "unit": "tokens/s", "cores": 1, "kind": "port",
+            "host_cores_available": os.cpu_count(),
+            "sample": f"{T} of {BATCH * SEQ} tokens through the whole fp32 chain in {dt:.1f} s, "
+                      f"single thread, table gradient at full vocab {V}x{D}"}
+
+
+# --------------------------------------------------------------------------- per-kernel sweep (fp32 large configs)
+def time_op(fn, warmup=3, iters=10):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+    evs[0].record()
+    for i in range(iters):
+        fn()
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    return float(np.mean([evs[i].elapsed_time(evs[i + 1]) for i in range(iters)]))
+
+
+def kernel_sweep(peak):
+    """GB/s of each kernel on the large fp32 configurations (inputs far larger than L2)."""
+    from dl_cuda_b200 import capi, ops
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    randn = lambda *s: torch.randn(*s, generator=g, device=dev)
+    out = []
+
+    def add(name, cfg, nbytes, ms):
+        gbs = nbytes / ms / 1e6
+        out.append({"kernel": name, "config": cfg, "ms": round(ms, 4), "bytes": int(nbytes),
+                    "gbs": round(gbs, 1), "frac_measured": round(gbs / peak, 4),
+                    "frac_nominal": round(gbs / NOMINAL_HBM_GBS, 4)})
+
+    # config 2: LN + residual, 65536 x 1024
+    R, D = 65536, 1024
+    a, b, dy = randn(R, D), randn(R, D), randn(R, D)
+    gamma, beta = torch.rand(D, generator=g, device=dev) + 0.5, randn(D) * 0.1
+    y, xhat, inv = torch.empty_like(a), torch.empty_like(a), torch.empty(R, device=dev)
+    dx, dg, db = torch.empty_like(a), torch.empty(D, device=dev), torch.empty(D, device=dev)
+    ws = ops.ln_bwd_workspace(R, D, dev)
+    ms = time_op(lambda: ops.ln_residual_fwd(a, b, gamma, beta, 1e-5, y=y, xhat=xhat, inv_std=inv))
+    add("ln_residual_fwd", "65536x1024 fp32", R * D * 16 + R * 4 + 2 * D * 4, ms)
+    ms = time_op(lambda: ops.ln_bwd(dy, None, xhat, inv, gamma, dx=dx, dgamma=dg, dbeta=db, workspace=ws))
+    add("ln_bwd", "65536x1024 fp32", R * D * 12 + R * 4 + 3 * D * 4, ms)
+    ms = time_op(lambda: ops.ln_bwd(dy, b, xhat, inv, gamma, dx=dx, dgamma=dg, dbeta=db, workspace=ws))
+    add("ln_bwd_two_grads", "65536x1024 fp32", R * D * 16 + R * 4 + 3 * D * 4, ms)
+    del a, b, dy, y, xhat, dx
+
+    # config 3: embedding + PE, vocab 32000 x 4096, 16 x 2048 Zipf tokens
+    V, D, B, S = 32000, 4096, 16, 2048
+    T = B * S
+    table = randn(V, D) * 0.02
+    ids_h = zipf_ids(np.random.Generator(np.random.Philox(key=1236)), T, V)
+    ids = torch.from_numpy(ids_h).to(dev)
+    U = int(np.unique(ids_h).size)
+    pe = ops.pe_table(S, D).to(dev)
+    outb, dyb = torch.empty(T, D, device=dev), randn(T, D)
+    grad = torch.empty(V, D, device=dev)
+    wse = ops.embed_workspace(T, V, D, dev)
+    ms = time_op(lambda: ops.embed_gather_fwd(table, ids, pe, S, out=outb))
+    add("embed_gather_pe_fwd", f"V32000 D4096 T32768 zipf1.1 ({U} distinct)", (U + T) * D * 4 + S * D * 4 + T * 4, ms)
+    ms = time_op(lambda: ops.embed_sort_tokens(ids, V, D, workspace=wse))
+    add("embed_sort_tokens", "T32768", 0, ms)
+    ms = time_op(lambda: ops.embed_scatter_bwd(dyb, ids, V, wse, grad=grad))
+    add("embed_scatter_bwd", "V32000 D4096 T32768 zipf1.1", T * D * 4 + V * D * 4 + T * 4, ms)
+    del table, outb, dyb, grad
+
+    # config 4: bias + activation, 32768 x 16384 (2 GiB per buffer)
+    R, C = 32768, 16384
+    x, dyy = randn(R, C) * 2.0, randn(R, C)
+    bias = randn(C) * 0.1
+    yb, dxb = torch.empty_like(x), torch.empty_like(x)
+    cache = torch.empty(R * C * 4, dtype=torch.uint8, device=dev)
+    dbias = torch.empty(C, device=dev)
+    wsa = ops.act_bwd_workspace(capi.RELU, R, C, dev)
+    n = R * C
+    for kind, name in ((capi.RELU, "relu"), (capi.SIGMOID, "sigmoid"), (capi.TANH, "tanh")):
+        cache_b = n // 8 if kind == capi.RELU else n * 4
+        ms = time_op(lambda: ops.act_fwd(kind, x, bias, y=yb, cache=cache))
+        add(f"bias_{name}_fwd", "32768x16384 fp32", n * 8 + cache_b + C * 4, ms)
+        ms = time_op(lambda: ops.act_bwd(kind, dyy, cache, dx=dxb, dbias=dbias, want_dbias=True, workspace=wsa))
+        add(f"{name}_bwd_dbias", "32768x16384 fp32", n * 8 + cache_b + C * 4, ms)
+    return out
+
+
+# --------------------------------------------------------------------------- main
+def run_timed(step, dist: Dist, steps, warmup):
+    for _ in range(warmup):
+        step()
+    dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    dist.barrier()
+    return dist.max_float(start.elapsed_time(stop))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["native", "reference"], default="native")
+    ap.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
+    ap.add_argument("--tokens", type=int, default=BATCH * SEQ, help="global token rows (default: batch 8 x seq 4096)")
+    ap.add_argument("--skip-kernels", action="store_true", help="skip the per-kernel fp32 sweep")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the host baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    dist = Dist()
+    if dist.world != args.gpus and dist.world > 1:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {dist.world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+
+    if args.impl == "reference":
+        return main_reference(args, dist)
+
+    dist.init()
+    peak, peak_kind = measured_peak()
+    n = dist.world
+    tokens_local = args.tokens // n
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    chain = Chain(tokens_local, SEQ, D_MODEL, D_FF, VOCAB, dtype, seed=1234 + dist.rank, dist=dist)
+    lib = chain.lib
+
+    # device-resident run: the headline `value`
+    marks_all = []
+
+    def step_marked():
+        marks = []
+        chain.step(marks=marks)
+        marks_all.append(marks)
+
+    for _ in range(args.warmup):
+        chain.step()
+    dist.barrier()
+    launches0 = lib.dlb_launch_count()
+    sampler = ClockSampler(torch.cuda.current_device())
+    with sampler:
+        total_ms = run_timed(step_marked, dist, args.steps, 0)
+    launches = lib.dlb_launch_count() - launches0
+    marks_all = marks_all[-args.steps:]
+    ms_per_step = total_ms / args.steps
+    tokens_per_s = args.tokens / (ms_per_step / 1e3)
+
+    # per-op device time from the events recorded inside the timed region
+    op_ms = {name: 0.0 for name in Chain.OPS}
+    for marks in marks_all:
+        for i, name in enumerate(Chain.OPS):
+            op_ms[name] += marks[i].elapsed_time(marks[i + 1])
+    op_ms = {k: v / len(marks_all) for k, v in op_ms.items()}
+    op_bytes = chain.bytes_per_op()
+    ops_report = []
+    for name in Chain.OPS:
+        gbs = op_bytes[name] / op_ms[name] / 1e6 if op_ms[name] > 0 and op_bytes[name] else None
+        ops_report.append({"op": name, "ms": round(op_ms[name], 4), "bytes": int(op_bytes[name]),
+                           "gbs": None if gbs is None else round(gbs, 1),
+                           "frac": None if gbs is None else round(gbs / peak, 4)})
+    dominant = max((o for o in ops_report if o["gbs"]), key=lambda o: o["ms"])
+
+    # end to end: ids from pinned host memory in, parameter gradients out, every step
+    e2e_ms = run_timed(lambda: chain.step(copy_inputs=True), dist, args.steps, args.warmup) / args.steps
+    e2e = {"value": args.tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": int(chain.h_ids.numel() * 4 * n),
+           "d2h_bytes_per_step": int(chain.h_result.numel() * 4 * n),
+           "what": "per step: token ids copied from pinned host memory, the chain through the C ABI, "
+                   "gamma/beta/bias gradients read back to the host"}
+
+    result = {
+        "metric": "tokens/s", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "impl": "native",
+        "config": {"workload": "transformer-block non-GEMM chain fwd+bwd (embed+PE, LN+residual x2, bias+ReLU, "
+                               "scatter-add), token-sharded",
+                   "batch": BATCH, "seq_len": SEQ, "d_model": D_MODEL, "d_ff": D_FF, "vocab": VOCAB,
+                   "global_tokens": args.tokens, "tokens_per_gpu": tokens_local, "ids": "zipf(1.1)",
+                   "parallelism": f"token rows / {n}", "l2": "inputs larger than L2 (about 10 GB touched per step)"},
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": sampler.summary(),
+        "roofline": {"bound": "hbm", "kernel": dominant["op"], "achieved": dominant["gbs"], "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": dominant["frac"],
+                     "frac_of_nominal_8000": round(dominant["gbs"] / NOMINAL_HBM_GBS, 4), "traffic": None},
+        "chain_ops": ops_report,
+        "chain_bytes_per_step": int(sum(op_bytes.values()) * n),
+        "chain_gbs": round(sum(op_bytes.values()) * n / ms_per_step / 1e6, 1),
+    }
+    del chain
+    torch.cuda.empty_cache()
+    if dist.rank == 0 and n == 1:
+        if not args.skip_kernels:
+            result["kernels_fp32"] = kernel_sweep(peak)
+        if not args.skip_cpu:
+            result["cpu_baseline"] = cpu_baseline()
+    dist.barrier()
+    if dist.rank == 0:
+        print(json.dumps(result))
+    dist.finish()
+
+
+def main_reference(args, dist: Dist):
+    """Reference arm: the reference's unmodified CUDA kernels (it has no CPU implementation and
+    no bf16 or multi-GPU path) on the fp32 version of the same chain, one GPU, rank 0 only."""
+    if dist.rank != 0:
+        return
+    from oracle import ref
+    if not ref.available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref_shim.so was not built "
+                          "(the reference checkout was absent at build time)"}))
+        return
+    torch.cuda.set_device(dist.local_rank)
+    one = Dist()
+    one.active = False
+    chain = ReferenceChain(args.tokens, SEQ, D_MODEL, D_FF, VOCAB, seed=1234)
+    sampler = ClockSampler(torch.cuda.current_device())
+    for _ in range(args.warmup):
+        chain.step()
+    torch.cuda.synchronize()
+    with sampler:
+        total_ms = run_timed(chain.step, one, args.steps, 0)
+    ms = total_ms / args.steps
+    e2e_ms = run_timed(lambda: chain.step(copy_inputs=True), one, args.steps, 1) / args.steps
+    value = args.tokens / (ms / 1e3)
+    print(json.dumps({
+        "impl": "reference", "metric": "tokens/s", "value": value, "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": {"workload": "transformer-block non-GEMM chain fwd+bwd through the reference's own CUDA kernels "
+                               "(fp32: the reference has no bf16; single GPU: it has no multi-GPU path)",
+                   "batch": BATCH, "seq_len": SEQ, "d_model": D_MODEL, "d_ff": D_FF, "vocab": VOCAB,
+                   "global_tokens": args.tokens, "ids": "zipf(1.1)",
+                   "l2": "inputs larger than L2"},
+        "e2e": {"value": args.tokens / (e2e_ms / 1e3), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(chain.h_ids.numel() * 4), "d2h_bytes_per_step": int(chain.h_result.numel() * 4)},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": 0, "kind": "reference",
+                         "sample": "the reference's CUDA kernels built for sm_100 on the same B200 "
+                                   "(the reference has no CPU implementation of this path)"},
+        "clocks": sampler.summary(),
+    }))
+
+
+if __name__ == "__main__":
+    main()

@@ -23,6 +23,7 @@ SIGNATURES = {
     "dlb_status_string": (C.c_char_p, [_i]),
     "dlb_last_error": (C.c_char_p, []),
     "dlb_launch_count": (C.c_uint64, []),
+    "dlb_pipeline_timeouts": (_i, [_p]),
     "dlb_residual_add": (_i, [_p, _p, _p, _i64, _i, _p]),
     "dlb_ln_residual_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _p]),
     "dlb_ln_bwd_workspace_bytes": (_sz, [_i, _i]),
@@ -72,6 +73,13 @@ def lib() -> C.CDLL:
 def check(status: int) -> None:
     if status != OK:
         raise DlbError(status, lib().dlb_last_error().decode() or lib().dlb_status_string(status).decode())
+
+
+def pipeline_timeouts() -> int:
+    """Waits that gave up inside pipelined kernels on the current device (0 = all good)."""
+    out = C.c_uint(0)
+    check(lib().dlb_pipeline_timeouts(C.byref(out)))
+    return int(out.value)
 
 
 def ptr(t) -> int | None:

@@ -1,6 +1,7 @@
 // Library-level pieces of the C ABI: status strings, the per-thread error
 // text, the launch counter and the cached SM count.
 #include "common.cuh"
+#include "tma.cuh"
 
 #include <cstring>
 
@@ -33,7 +34,33 @@ int sm_count() {
   return n;
 }
 
+__device__ unsigned int g_wait_timeouts = 0;
+
+unsigned int *wait_timeouts_counter() {
+  constexpr int kMaxDev = 64;
+  static std::atomic<unsigned int *> cached[kMaxDev];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  unsigned int *p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    void *addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_wait_timeouts) != cudaSuccess) return nullptr;
+    p = static_cast<unsigned int *>(addr);
+    cached[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
+
 }  // namespace dlb
+
+extern "C" int dlb_pipeline_timeouts(unsigned int *h_count) {
+  DLB_REQUIRE(h_count != nullptr, DLB_ERR_INVALID_ARG, "pipeline_timeouts: null pointer");
+  unsigned int *p = dlb::wait_timeouts_counter();
+  DLB_REQUIRE(p != nullptr, DLB_ERR_NO_DEVICE, "pipeline_timeouts: no CUDA device");
+  cudaError_t e = cudaMemcpy(h_count, p, sizeof(unsigned int), cudaMemcpyDeviceToHost);
+  DLB_REQUIRE(e == cudaSuccess, DLB_ERR_CUDA, "pipeline_timeouts: %s", cudaGetErrorString(e));
+  return DLB_OK;
+}
 
 extern "C" int dlb_version(void) { return 100; }
 

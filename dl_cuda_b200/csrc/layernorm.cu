@@ -7,6 +7,7 @@
 // of dgamma/dbeta in the same pass; a second small kernel adds the partials in
 // a fixed order.
 #include "common.cuh"
+#include "ln_bwd_pipe.cuh"
 #include "reduce.cuh"
 
 namespace dlb {
@@ -457,11 +458,18 @@ int ln_bwd_typed(const void *dy_a, const void *dy_b, const void *xhat, const flo
                  int rows, int d, cudaStream_t st) {
   const bool al = aligned16(dy_a) && (dy_b == nullptr || aligned16(dy_b)) && aligned16(xhat) &&
                   aligned16(dx) && aligned16(gamma);
-  const Shape s = pick_shape<T>(d, al);
   int n_partial = 0;
   int rc = -1;
+  // Wide rows and enough of them: the bulk-copy pipeline; otherwise rows in registers.
+  const PipeShape ps = pick_pipe_shape<T>(rows, d, dy_b != nullptr, al && aligned16(partial));
+#define M(CT, KV, RT)                                  \
+  if (ps.ct == CT && ps.kv == KV && ps.rt == RT)       \
+    rc = launch_ln_bwd_pipe<T, CT, KV, RT>(ps, dy_a, dy_b, xhat, inv_std, gamma, dx, partial, &n_partial, rows, d, st);
+  DLB_PIPE_CASES(M)
+#undef M
+  const Shape s = rc == -1 ? pick_shape<T>(d, al) : Shape{};
 #define M(TPR, VPT)                 \
-  if (s.tpr == TPR && s.vpt == VPT) \
+  if (rc == -1 && s.tpr == TPR && s.vpt == VPT) \
     rc = launch_bwd<T, TPR, VPT>(dy_a, dy_b, xhat, inv_std, gamma, dx, partial, &n_partial, rows, d, st);
   if constexpr (sizeof(T) == 4) {
     DLB_LN_CASES_F32(M)

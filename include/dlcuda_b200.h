@@ -60,6 +60,13 @@ DLB_API const char *dlb_last_error(void);
  * load (every stream, every thread).  Used by benchmarks to report launches. */
 DLB_API uint64_t dlb_launch_count(void);
 
+/* The pipelined kernels wait on shared-memory barriers with a bounded number of
+ * polls; a wait that gives up lets the kernel finish (with wrong results) and
+ * bumps a per-device counter instead of hanging the GPU.  This call
+ * synchronises the device and returns that counter: 0 means every result since
+ * load is good.  No counterpart in the reference. */
+DLB_API int dlb_pipeline_timeouts(unsigned int *h_count);
+
 /* ---- residual add -------------------------------------------------------
  * out[i] = a[i] + b[i].  out may alias a or b.
  * Replaces transformerResidualAddKernel (src/transformer.cuh:216-222) and

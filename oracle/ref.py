@@ -23,10 +23,36 @@ def available() -> bool:
     return LIB_PATH.exists()
 
 
+_P, _I, _F = C.c_void_p, C.c_int, C.c_float
+_SIGNATURES = {
+    "ref_residual_add": [_P, _P, _P, _I],
+    "ref_ln_fwd": [_P, _P, _P, _P, _P, _P, _I, _I, _F],
+    "ref_ln_bwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I],
+    "ref_embed_fwd": [_P, _P, _P, _I, _I],
+    "ref_embed_bwd": [_P, _P, _P, _I, _I, _I],
+    "ref_pe_add": [_P, _P, _P, _I, _I, _I],
+    "ref_pe_bwd": [_P, _P, _I],
+    "ref_pe_table": [_P, _I, _I],
+    "ref_act_fwd": [_I, _P, _P, _P, _I],
+    "ref_act_bwd": [_I, _P, _P, _P, _I],
+    "ref_tanh_bwd_element": [_P, _P, _P, _I],
+    "ref_bias_grad": [_P, _P, _I, _I],
+    "ref_bias_add": [_P, _P, _P, _I, _I],
+    "ref_sgd": [_P, _P, _F, _I],
+    "ref_embedding_init": [C.c_uint64, _I, _I, _I, _P, C.c_char_p],
+    "ref_embedding_layer_run": [_P, _P, _P, _I, _I, _I, _P, _P],
+}
+
+
 def lib() -> C.CDLL:
+    """The shim with argument types set, so that 64-bit device addresses are never truncated."""
     global _lib
     if _lib is None:
-        _lib = C.CDLL(str(LIB_PATH))
+        handle = C.CDLL(str(LIB_PATH))
+        for name, args in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = C.c_int, args
+        _lib = handle
     return _lib
 
 
