@@ -113,6 +113,7 @@ template <typename T, int KIND>
 __global__ void __launch_bounds__(kBlock)
 act_fwd_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, int64_t rows,
                int64_t cols, int64_t n, int64_t rows_per_cta) {
+  pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   const int64_t ncv = cols / E;
@@ -179,6 +180,7 @@ template <typename T, int KIND>
 __global__ void __launch_bounds__(kBlock)
 act_bwd_kernel(const T *dy, const void *cache, T *dx, float *__restrict__ partial, int64_t rows,
                int64_t cols, int64_t n, int64_t rows_per_cta) {
+  pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   __shared__ float colacc[kBlock * E];  // [ty][tx*E]
@@ -258,6 +260,7 @@ template <typename T, int KIND>
 __global__ void __launch_bounds__(kBlock)
 act_fwd_scalar_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, int64_t cols,
                       int64_t n) {
+  pdl_prologue();
   using S = Store<T>;
   const int64_t i0 = (static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x) * 8;
   if (i0 >= n) return;
@@ -282,6 +285,7 @@ act_fwd_scalar_kernel(const T *x, const float *__restrict__ bias, T *y, void *ca
 template <typename T, int KIND>
 __global__ void __launch_bounds__(kBlock)
 act_bwd_scalar_kernel(const T *dy, const void *cache, T *dx, int64_t n) {
+  pdl_prologue();
   using S = Store<T>;
   const int64_t i0 = (static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x) * 8;
   if (i0 >= n) return;
@@ -304,6 +308,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock)
 colsum_scalar_kernel(const T *__restrict__ v, float *__restrict__ partial, int64_t rows,
                      int64_t cols, int64_t rows_per_chunk) {
+  pdl_prologue();
   using S = Store<T>;
   const int64_t col = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x;
   if (col >= cols) return;
@@ -345,14 +350,14 @@ int act_fwd_typed(const void *x, const float *bias, void *y, void *cache, int64_
       vr = ceil_div<int64_t>(n, vc);
     }
     const Tiling t = make_tiling(vr, vc / E);
-    act_fwd_kernel<T, KIND><<<t.grid, t.block, 0, st>>>(static_cast<const T *>(x), bias,
+    launch_pdl(act_fwd_kernel<T, KIND>, t.grid, t.block, 0, st, static_cast<const T *>(x), bias,
                                                         static_cast<T *>(y), cache, vr, vc, n,
                                                         t.rows_per_cta);
     DLB_LAUNCH_CHECK("act_fwd");
     return DLB_OK;
   }
   const int64_t threads = ceil_div<int64_t>(n, 8);
-  act_fwd_scalar_kernel<T, KIND><<<static_cast<unsigned>(ceil_div<int64_t>(threads, kBlock)), kBlock, 0, st>>>(
+  launch_pdl(act_fwd_scalar_kernel<T, KIND>, static_cast<unsigned>(ceil_div<int64_t>(threads, kBlock)), kBlock, 0, st, 
       static_cast<const T *>(x), bias, static_cast<T *>(y), cache, cols, n);
   DLB_LAUNCH_CHECK("act_fwd_scalar");
   return DLB_OK;
@@ -370,7 +375,7 @@ int act_bwd_typed(const void *dy, const void *cache, void *dx, float *dbias, flo
       vr = ceil_div<int64_t>(n, vc);
     }
     const Tiling t = make_tiling(vr, vc / E);
-    act_bwd_kernel<T, KIND><<<t.grid, t.block, 0, st>>>(
+    launch_pdl(act_bwd_kernel<T, KIND>, t.grid, t.block, 0, st, 
         static_cast<const T *>(dy), cache, static_cast<T *>(dx), dbias ? partial : nullptr, vr, vc,
         n, t.rows_per_cta);
     DLB_LAUNCH_CHECK("act_bwd");
@@ -381,7 +386,7 @@ int act_bwd_typed(const void *dy, const void *cache, void *dx, float *dbias, flo
   }
   if constexpr (KIND != kActNone) {
     const int64_t threads = ceil_div<int64_t>(n, 8);
-    act_bwd_scalar_kernel<T, KIND><<<static_cast<unsigned>(ceil_div<int64_t>(threads, kBlock)), kBlock, 0, st>>>(
+    launch_pdl(act_bwd_scalar_kernel<T, KIND>, static_cast<unsigned>(ceil_div<int64_t>(threads, kBlock)), kBlock, 0, st, 
         static_cast<const T *>(dy), cache, static_cast<T *>(dx), n);
     DLB_LAUNCH_CHECK("act_bwd_scalar");
   }
@@ -389,7 +394,7 @@ int act_bwd_typed(const void *dy, const void *cache, void *dx, float *dbias, flo
     const void *src = (KIND == kActNone) ? dy : dx;
     const int64_t chunks = ceil_div<int64_t>(rows, kScalarRowsPerChunk);
     dim3 grid(static_cast<unsigned>(ceil_div<int64_t>(cols, kBlock)), static_cast<unsigned>(chunks));
-    colsum_scalar_kernel<T><<<grid, kBlock, 0, st>>>(static_cast<const T *>(src), partial, rows,
+    launch_pdl(colsum_scalar_kernel<T>, grid, kBlock, 0, st, static_cast<const T *>(src), partial, rows,
                                                      cols, kScalarRowsPerChunk);
     DLB_LAUNCH_CHECK("colsum_scalar");
     return colsum_finalize(partial, static_cast<int>(chunks), static_cast<int>(cols), dbias,

@@ -47,6 +47,27 @@ inline bool aligned16(const void *p) {
     }                                  \
   } while (0)
 
+// Launch with programmatic dependent launch allowed: the grid may be scheduled
+// while the previous kernel of the stream drains.  Every kernel of this library
+// starts with pdl_prologue(), which lets its own successor do the same and then
+// waits until all earlier work of the stream has completed and is visible, so
+// only launch latency and block scheduling overlap, never data.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                       Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);  // errors surface in DLB_LAUNCH_CHECK
+}
+
 template <typename T>
 inline T ceil_div(T a, T b) {
   return (a + b - 1) / b;
@@ -54,6 +75,13 @@ inline T ceil_div(T a, T b) {
 
 // -------------------------------------------------------------- device side
 constexpr int kWarp = 32;
+
+// First statement of every kernel: allow the next kernel of the stream to be
+// scheduled early, then wait for everything launched before this kernel.
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 // Storage traits: a 16-byte vector holds kPerVec elements of storage type T.
 template <typename T>

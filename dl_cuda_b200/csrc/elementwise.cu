@@ -17,6 +17,7 @@ constexpr int kUnroll = 4;
 template <typename T, bool kCopy>
 __global__ void __launch_bounds__(kBlock)
 add_kernel(const T *a, const T *b, T *out, int64_t nvec) {
+  pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kBlock;
@@ -53,6 +54,7 @@ add_kernel(const T *a, const T *b, T *out, int64_t nvec) {
 template <typename T, bool kCopy>
 __global__ void __launch_bounds__(kBlock)
 add_scalar_kernel(const T *a, const T *b, T *out, int64_t n) {
+  pdl_prologue();
   using S = Store<T>;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x;
   if (i >= n) return;
@@ -64,6 +66,7 @@ add_scalar_kernel(const T *a, const T *b, T *out, int64_t n) {
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
 pe_add_kernel(const T *in, const float *__restrict__ pe, T *out, int batch, int seq_len, int d) {
+  pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   const int ncv = d / E;
@@ -99,6 +102,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBlock)
 pe_add_scalar_kernel(const T *in, const float *__restrict__ pe, T *out, int64_t total,
                      int64_t period) {
+  pdl_prologue();
   using S = Store<T>;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x;
   if (i >= total) return;
@@ -107,6 +111,7 @@ pe_add_scalar_kernel(const T *in, const float *__restrict__ pe, T *out, int64_t 
 
 __global__ void __launch_bounds__(kBlock)
 sgd_kernel(float *__restrict__ p, const float *__restrict__ g, float lr, int64_t n) {
+  pdl_prologue();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kBlock;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x; i < n; i += stride)
     p[i] -= lr * g[i];
@@ -123,12 +128,12 @@ int add_typed(const void *a, const void *b, void *out, int64_t n, cudaStream_t s
   constexpr int E = Store<T>::kPerVec;
   if (n % E == 0 && aligned16(a) && (kCopy || aligned16(b)) && aligned16(out)) {
     const int64_t nvec = n / E;
-    add_kernel<T, kCopy><<<stream_grid(nvec), kBlock, 0, st>>>(
+    launch_pdl(add_kernel<T, kCopy>, stream_grid(nvec), kBlock, 0, st, 
         static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), nvec);
     DLB_LAUNCH_CHECK("add");
     return DLB_OK;
   }
-  add_scalar_kernel<T, kCopy><<<static_cast<unsigned>(ceil_div<int64_t>(n, kBlock)), kBlock, 0, st>>>(
+  launch_pdl(add_scalar_kernel<T, kCopy>, static_cast<unsigned>(ceil_div<int64_t>(n, kBlock)), kBlock, 0, st, 
       static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), n);
   DLB_LAUNCH_CHECK("add_scalar");
   return DLB_OK;
@@ -144,13 +149,13 @@ int pe_add_typed(const void *in, const float *pe, void *out, int batch, int seq_
   if (d % E == 0 && aligned16(in) && aligned16(out) && aligned16(pe) &&
       ceil_div(seq_len, ty) <= 65535) {
     dim3 grid(ceil_div(d / E, tx), ceil_div(seq_len, ty));
-    pe_add_kernel<T><<<grid, dim3(tx, ty), 0, st>>>(static_cast<const T *>(in), pe,
+    launch_pdl(pe_add_kernel<T>, grid, dim3(tx, ty), 0, st, static_cast<const T *>(in), pe,
                                                     static_cast<T *>(out), batch, seq_len, d);
     DLB_LAUNCH_CHECK("pe_add");
     return DLB_OK;
   }
   const int64_t period = static_cast<int64_t>(seq_len) * d, total = period * batch;
-  pe_add_scalar_kernel<T><<<static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st>>>(
+  launch_pdl(pe_add_scalar_kernel<T>, static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st, 
       static_cast<const T *>(in), pe, static_cast<T *>(out), total, period);
   DLB_LAUNCH_CHECK("pe_add_scalar");
   return DLB_OK;
@@ -211,7 +216,7 @@ extern "C" int dlb_sgd_update(float *params, const float *grads, float lr, int64
   DLB_REQUIRE(n >= 0, DLB_ERR_INVALID_ARG, "sgd_update: n=%lld", static_cast<long long>(n));
   if (n == 0) return DLB_OK;
   DLB_REQUIRE(params && grads, DLB_ERR_INVALID_ARG, "sgd_update: null pointer");
-  sgd_kernel<<<stream_grid(n), kBlock, 0, as_stream(stream)>>>(params, grads, lr, n);
+  launch_pdl(sgd_kernel, stream_grid(n), kBlock, 0, as_stream(stream), params, grads, lr, n);
   DLB_LAUNCH_CHECK("sgd");
   return DLB_OK;
 }

@@ -11,10 +11,12 @@
 //     kSubLen tokens is summed in ascending token order and written once (zero
 //     if no token refers to it).  Long rows are cut into sub-segments of
 //     kSubLen tokens, each summed by its own thread group into a scratch row.
-//  3. combine_long_kernel: adds a long row's scratch rows in sub-segment order.
+//  3. combine_long_kernel: adds a long row's scratch rows: four contiguous quarters of
+//     the sub-segments are summed in order, then the four quarter sums in order.
 // The order of every addition is a function of ids alone, so two runs give the
 // same bits whatever the scheduling.
 #include "common.cuh"
+#include "embed_plan_cluster.cuh"
 
 namespace dlb {
 namespace {
@@ -31,6 +33,7 @@ __global__ void __launch_bounds__(kBlock)
 embed_gather_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids,
                     const float *__restrict__ pe, T *__restrict__ out, int num_tokens, int vocab,
                     int d, int stride_s) {
+  pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   constexpr int U = 4;
@@ -81,6 +84,7 @@ __global__ void __launch_bounds__(kBlock)
 embed_gather_scalar_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids,
                            const float *__restrict__ pe, T *__restrict__ out, int num_tokens,
                            int vocab, int d, int seq_len) {
+  pdl_prologue();
   using S = Store<T>;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x;
   if (i >= static_cast<int64_t>(num_tokens) * d) return;
@@ -100,6 +104,7 @@ constexpr int kDigits = 256;
 __global__ void __launch_bounds__(kBlock)
 sort_hist_kernel(const uint32_t *__restrict__ keys, int n, int shift, int nblocks,
                  int32_t *__restrict__ block_hist) {
+  pdl_prologue();
   __shared__ int hist[kDigits];
   hist[threadIdx.x] = 0;
   __syncthreads();
@@ -155,6 +160,7 @@ __device__ int cta_exclusive_scan_inplace(int32_t *data, int n, int *smem /*[33]
 }
 
 __global__ void __launch_bounds__(1024) scan_inplace_kernel(int32_t *data, int n) {
+  pdl_prologue();
   __shared__ int smem[33];
   cta_exclusive_scan_inplace(data, n, smem);
 }
@@ -166,6 +172,7 @@ __global__ void __launch_bounds__(kBlock)
 sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const int32_t *__restrict__ vals_in,
                     uint32_t *__restrict__ keys_out, int32_t *__restrict__ vals_out, int n,
                     int shift, int nblocks, const int32_t *__restrict__ block_base) {
+  pdl_prologue();
   constexpr int kWarps = kBlock / 32;
   __shared__ int cnt[kWarps][kDigits];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -218,6 +225,7 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const int32_t *__restr
 __global__ void __launch_bounds__(kBlock)
 segment_start_kernel(const uint32_t *__restrict__ sorted_keys, int n, int vocab,
                      int32_t *__restrict__ seg_start) {
+  pdl_prologue();
   const int v = blockIdx.x * kBlock + threadIdx.x;
   if (v > vocab) return;
   int lo = 0, hi = n;
@@ -234,6 +242,7 @@ __global__ void __launch_bounds__(1024)
 plan_long_rows_kernel(const int32_t *__restrict__ seg_start, int vocab,
                       int32_t *__restrict__ long_row, int32_t *__restrict__ long_first,
                       int32_t *__restrict__ meta) {
+  pdl_prologue();
   __shared__ int wsum[2][33];
   const int tid = threadIdx.x;
   const int per = (vocab + 1023) / 1024;
@@ -394,6 +403,7 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
                     const int32_t *__restrict__ long_first, const int32_t *__restrict__ meta,
                     float *__restrict__ grad, float *__restrict__ scratch, int vocab, int d,
                     int sub_groups) {
+  pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   const int tx = blockDim.x, ty = blockDim.y;
@@ -437,24 +447,43 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
   }
 }
 
-// grad[v,:] = scratch rows of v added in sub-segment order (one float4 column
-// vector per thread).
+// grad[v,:] = the scratch rows of long row v.  Four adjacent lanes share one
+// float4 column vector: lane k adds the k-th contiguous quarter of the row's
+// sub-segments in order, then the four quarter sums are added in order.
+constexpr int kCombineSlices = 4;
+
 __global__ void __launch_bounds__(kBlock)
 combine_long_kernel(const float *__restrict__ scratch, const int32_t *__restrict__ long_row,
                     const int32_t *__restrict__ long_first, const int32_t *__restrict__ meta,
                     float *__restrict__ grad, int d) {
+  pdl_prologue();
   const int li = blockIdx.x;
   if (li >= meta[0]) return;
   const int v = long_row[li];
   const int s0 = long_first[li], s1 = long_first[li + 1];
-  for (int c = (blockIdx.y * kBlock + threadIdx.x) * 4; c < d; c += gridDim.y * kBlock * 4) {
+  const int per = (s1 - s0 + kCombineSlices - 1) / kCombineSlices;
+  const int slice = threadIdx.x & (kCombineSlices - 1), cvl = threadIdx.x / kCombineSlices;
+  constexpr int kVecPerCta = kBlock / kCombineSlices;
+  const int b = min(s1, s0 + slice * per), e = min(s1, b + per);
+  for (int cb = blockIdx.y * kVecPerCta; cb * 4 < d; cb += gridDim.y * kVecPerCta) {
+    const int c = (cb + cvl) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-    for (int s = s0; s < s1; s++) {
-      const float4 p = __ldcs(reinterpret_cast<const float4 *>(scratch + static_cast<size_t>(s) * d + c));
-      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    if (c < d) {
+#pragma unroll 8
+      for (int s = b; s < e; s++) {
+        const float4 p = __ldcs(reinterpret_cast<const float4 *>(scratch + static_cast<size_t>(s) * d + c));
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+      }
     }
-    __stcs(reinterpret_cast<float4 *>(grad + static_cast<size_t>(v) * d + c), acc);
+    float4 r = acc;
+#pragma unroll
+    for (int k = 1; k < kCombineSlices; k++) {
+      r.x += __shfl_down_sync(0xffffffffu, acc.x, k);
+      r.y += __shfl_down_sync(0xffffffffu, acc.y, k);
+      r.z += __shfl_down_sync(0xffffffffu, acc.z, k);
+      r.w += __shfl_down_sync(0xffffffffu, acc.w, k);
+    }
+    if (slice == 0 && c < d) __stcs(reinterpret_cast<float4 *>(grad + static_cast<size_t>(v) * d + c), r);
   }
 }
 
@@ -464,21 +493,29 @@ __global__ void __launch_bounds__(kBlock)
 scatter_scalar_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
                       const int32_t *__restrict__ seg_start, float *__restrict__ grad, int vocab,
                       int d) {
+  pdl_prologue();
   using S = Store<T>;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x;
   if (i >= static_cast<int64_t>(vocab) * d) return;
   const int v = static_cast<int>(i / d), c = static_cast<int>(i % d);
   const int b = seg_start[v], e = seg_start[v + 1];
   float total = 0.f;
-  // Same association as the vector path: sub-segments of kSubLen, then their sum.
+  // Same association as the vector path: sub-segments of kSubLen tokens, their sums
+  // added inside four contiguous quarters, then the quarter sums in order.
   if (e - b <= kSubLen) {
     for (int j = b; j < e; j++) total += S::to_float(dy[static_cast<size_t>(perm[j]) * d + c]);
   } else {
-    for (int b2 = b; b2 < e; b2 += kSubLen) {
-      float part = 0.f;
-      const int e2 = min(e, b2 + kSubLen);
-      for (int j = b2; j < e2; j++) part += S::to_float(dy[static_cast<size_t>(perm[j]) * d + c]);
-      total += part;
+    const int pieces = (e - b + kSubLen - 1) / kSubLen;
+    const int per = (pieces + kCombineSlices - 1) / kCombineSlices;
+    for (int q = 0; q < kCombineSlices; q++) {
+      float quarter = 0.f;
+      for (int piece = q * per; piece < pieces && piece < (q + 1) * per; piece++) {
+        float part = 0.f;
+        const int b2 = b + piece * kSubLen, e2 = min(e, b2 + kSubLen);
+        for (int j = b2; j < e2; j++) part += S::to_float(dy[static_cast<size_t>(perm[j]) * d + c]);
+        quarter += part;
+      }
+      total = q == 0 ? quarter : total + quarter;
     }
   }
   grad[i] = total;
@@ -512,13 +549,13 @@ int gather_typed(const void *table, const int32_t *ids, const float *pe, int seq
     dim3 grid(ceil_div(ncv, bs.tx), ceil_div(stride_s, bs.ty));
     DLB_REQUIRE(grid.y <= 65535u, DLB_ERR_UNSUPPORTED,
                 "embed_gather_fwd: seq_len=%d exceeds %d positions", seq_len, 65535 * bs.ty);
-    embed_gather_kernel<T><<<grid, dim3(bs.tx, bs.ty), 0, st>>>(
+    launch_pdl(embed_gather_kernel<T>, grid, dim3(bs.tx, bs.ty), 0, st, 
         static_cast<const T *>(table), ids, pe, static_cast<T *>(out), num_tokens, vocab, d, stride_s);
     DLB_LAUNCH_CHECK("embed_gather");
     return DLB_OK;
   }
   const int64_t total = static_cast<int64_t>(num_tokens) * d;
-  embed_gather_scalar_kernel<T><<<static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st>>>(
+  launch_pdl(embed_gather_scalar_kernel<T>, static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st, 
       static_cast<const T *>(table), ids, pe, static_cast<T *>(out), num_tokens, vocab, d, seq_len);
   DLB_LAUNCH_CHECK("embed_gather_scalar");
   return DLB_OK;
@@ -532,7 +569,7 @@ int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *gr
   const int sub_groups = ceil_div(p.max_sub, bs.ty);
   const int row_groups = ceil_div(vocab, bs.ty);
   dim3 grid(sub_groups + row_groups, ceil_div(ncv, bs.tx * KV));
-  scatter_rows_kernel<T, KV><<<grid, dim3(bs.tx, bs.ty), 0, st>>>(
+  launch_pdl(scatter_rows_kernel<T, KV>, grid, dim3(bs.tx, bs.ty), 0, st, 
       static_cast<const T *>(dy), perm, p.seg_start, p.long_row, p.long_first, p.meta, grad,
       p.scratch, vocab, d, sub_groups);
   DLB_LAUNCH_CHECK("scatter_rows");
@@ -546,7 +583,7 @@ int scatter_typed(const Plan &p, const void *dy, float *grad, int vocab, int d, 
   const bool vec = d % E == 0 && aligned16(dy) && aligned16(grad);
   if (!vec) {
     const int64_t total = static_cast<int64_t>(vocab) * d;
-    scatter_scalar_kernel<T><<<static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st>>>(
+    launch_pdl(scatter_scalar_kernel<T>, static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st, 
         static_cast<const T *>(dy), perm, p.seg_start, grad, vocab, d);
     DLB_LAUNCH_CHECK("scatter_scalar");
     return DLB_OK;
@@ -559,8 +596,8 @@ int scatter_typed(const Plan &p, const void *dy, float *grad, int vocab, int d, 
   else if (need >= 2) rc = launch_scatter<T, 2>(p, dy, perm, grad, vocab, d, bs, st);
   else rc = launch_scatter<T, 1>(p, dy, perm, grad, vocab, d, bs, st);
   if (rc != DLB_OK) return rc;
-  dim3 grid(p.max_long, max(1, min(8, d / (kBlock * 4))));
-  combine_long_kernel<<<grid, kBlock, 0, st>>>(p.scratch, p.long_row, p.long_first, p.meta, grad, d);
+  dim3 grid(p.max_long, max(1, min(16, ceil_div(d / 4, kBlock / kCombineSlices))));
+  launch_pdl(combine_long_kernel, grid, kBlock, 0, st, p.scratch, p.long_row, p.long_first, p.meta, grad, d);
   DLB_LAUNCH_CHECK("combine_long");
   return DLB_OK;
 }
@@ -609,26 +646,42 @@ extern "C" int dlb_embed_sort_tokens(const int32_t *ids, void *workspace, size_t
   DLB_REQUIRE(ids || num_tokens == 0, DLB_ERR_INVALID_ARG, "embed_sort_tokens: null ids");
   cudaStream_t st = as_stream(stream);
   const Plan p = make_plan(workspace, num_tokens, vocab, d);
+  if (num_tokens <= kClusterPlanMaxTokens) {
+    // One launch: an 8-CTA cluster runs every phase of the plan.
+    ClusterPlanArgs a{};
+    a.ids = reinterpret_cast<const uint32_t *>(ids);
+    a.keys[0] = p.keys[0]; a.keys[1] = p.keys[1];
+    a.vals[0] = p.vals[0]; a.vals[1] = p.vals[1];
+    a.seg_start = p.seg_start; a.long_row = p.long_row; a.long_first = p.long_first; a.meta = p.meta;
+    a.num_tokens = num_tokens; a.vocab = vocab; a.passes = p.passes; a.sub_len = kSubLen;
+    cudaError_t e = cudaFuncSetAttribute(embed_plan_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kClusterPlanSmem));
+    DLB_REQUIRE(e == cudaSuccess, DLB_ERR_CUDA, "embed_sort_tokens: shared memory attribute: %s",
+                cudaGetErrorString(e));
+    launch_pdl(embed_plan_cluster_kernel, kClusterCtas, kClusterThreads, kClusterPlanSmem, st, a);
+    DLB_LAUNCH_CHECK("embed_plan_cluster");
+    return DLB_OK;
+  }
   const uint32_t *kin = reinterpret_cast<const uint32_t *>(ids);
   const int32_t *vin = nullptr;
   for (int pass = 0; pass < p.passes && num_tokens > 0; pass++) {
     const int shift = 8 * pass;
     uint32_t *kout = p.keys[(pass + 1) & 1];
     int32_t *vout = p.vals[(pass + 1) & 1];
-    sort_hist_kernel<<<p.nblocks, kBlock, 0, st>>>(kin, num_tokens, shift, p.nblocks, p.block_hist);
+    launch_pdl(sort_hist_kernel, p.nblocks, kBlock, 0, st, kin, num_tokens, shift, p.nblocks, p.block_hist);
     DLB_LAUNCH_CHECK("sort_hist");
-    scan_inplace_kernel<<<1, 1024, 0, st>>>(p.block_hist, kDigits * p.nblocks);
+    launch_pdl(scan_inplace_kernel, 1, 1024, 0, st, p.block_hist, kDigits * p.nblocks);
     DLB_LAUNCH_CHECK("sort_scan");
-    sort_scatter_kernel<<<p.nblocks, kBlock, 0, st>>>(kin, vin, kout, vout, num_tokens, shift,
+    launch_pdl(sort_scatter_kernel, p.nblocks, kBlock, 0, st, kin, vin, kout, vout, num_tokens, shift,
                                                       p.nblocks, p.block_hist);
     DLB_LAUNCH_CHECK("sort_scatter");
     kin = kout;
     vin = vout;
   }
-  segment_start_kernel<<<ceil_div(vocab + 1, kBlock), kBlock, 0, st>>>(
+  launch_pdl(segment_start_kernel, ceil_div(vocab + 1, kBlock), kBlock, 0, st, 
       p.keys[p.passes & 1], num_tokens, vocab, p.seg_start);
   DLB_LAUNCH_CHECK("segment_start");
-  plan_long_rows_kernel<<<1, 1024, 0, st>>>(p.seg_start, vocab, p.long_row, p.long_first, p.meta);
+  launch_pdl(plan_long_rows_kernel, 1, 1024, 0, st, p.seg_start, vocab, p.long_row, p.long_first, p.meta);
   DLB_LAUNCH_CHECK("plan_long_rows");
   return DLB_OK;
 }

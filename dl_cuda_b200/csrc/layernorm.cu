@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(kBlock)
 ln_fwd_kernel(const T *a, const T *b, const float *__restrict__ gamma,
               const float *__restrict__ beta, T *y, T *xhat, float *__restrict__ inv_std,
               int rows, int d, float eps) {
+  pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   constexpr int kRowsPerCta = kBlock / TPR;
@@ -146,6 +147,7 @@ ln_fwd_generic_kernel(const T *a, const T *b,
                       const float *__restrict__ gamma, const float *__restrict__ beta,
                       T *y, T *xhat, float *__restrict__ inv_std, int rows, int d,
                       float eps) {
+  pdl_prologue();
   using S = Store<T>;
   __shared__ float red[kBlock / 32];
   const size_t base = static_cast<size_t>(blockIdx.x) * d;
@@ -183,6 +185,7 @@ __global__ void __launch_bounds__(kBlock)
 ln_bwd_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xhat,
               const float *__restrict__ inv_std, const float *__restrict__ gamma, T *dx,
               float *__restrict__ partial, int rows, int d) {
+  pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   constexpr int kRowsPerCta = kBlock / TPR;
@@ -300,6 +303,7 @@ __global__ void __launch_bounds__(kBlock)
 ln_bwd_dx_generic_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xhat,
                          const float *__restrict__ inv_std,
                          const float *__restrict__ gamma, T *dx, int rows, int d) {
+  pdl_prologue();
   using S = Store<T>;
   __shared__ float red[kBlock / 32];
   const size_t base = static_cast<size_t>(blockIdx.x) * d;
@@ -331,6 +335,7 @@ __global__ void __launch_bounds__(kBlock)
 ln_colsum_generic_kernel(const T *__restrict__ dy_a, const T *__restrict__ dy_b,
                          const T *__restrict__ xhat, float *__restrict__ partial,
                          int rows, int d, int rows_per_chunk) {
+  pdl_prologue();
   using S = Store<T>;
   const int col = blockIdx.x * kBlock + threadIdx.x;
   if (col >= d) return;
@@ -391,7 +396,7 @@ template <typename T, int TPR, int VPT>
 int launch_fwd(const void *a, const void *b, const float *gamma, const float *beta, void *y,
                void *xhat, float *inv_std, int rows, int d, float eps, cudaStream_t st) {
   const int grid = ceil_div(rows, kBlock / TPR);
-  ln_fwd_kernel<T, TPR, VPT><<<grid, kBlock, 0, st>>>(
+  launch_pdl(ln_fwd_kernel<T, TPR, VPT>, grid, kBlock, 0, st, 
       static_cast<const T *>(a), static_cast<const T *>(b), gamma, beta, static_cast<T *>(y),
       static_cast<T *>(xhat), inv_std, rows, d, eps);
   DLB_LAUNCH_CHECK("ln_fwd");
@@ -415,7 +420,7 @@ int launch_bwd(const void *dy_a, const void *dy_b, const void *xhat, const float
     ctas_per_sm = n;
   }
   const int grid = bwd_grid(rows, kRowsPerCta, ctas_per_sm);
-  kern<<<grid, kBlock, kSmem, st>>>(static_cast<const T *>(dy_a), static_cast<const T *>(dy_b),
+  launch_pdl(kern, grid, kBlock, kSmem, st, static_cast<const T *>(dy_a), static_cast<const T *>(dy_b),
                                     static_cast<const T *>(xhat), inv_std, gamma,
                                     static_cast<T *>(dx), partial, rows, d);
   DLB_LAUNCH_CHECK("ln_bwd");
@@ -443,7 +448,7 @@ int ln_fwd_typed(const void *a, const void *b, const float *gamma, const float *
     DLB_LN_CASES_BF16(M)
   }
 #undef M
-  ln_fwd_generic_kernel<T><<<rows, kBlock, 0, st>>>(
+  launch_pdl(ln_fwd_generic_kernel<T>, rows, kBlock, 0, st, 
       static_cast<const T *>(a), static_cast<const T *>(b), gamma, beta, static_cast<T *>(y),
       static_cast<T *>(xhat), inv_std, rows, d, eps);
   DLB_LAUNCH_CHECK("ln_fwd_generic");
@@ -480,11 +485,11 @@ int ln_bwd_typed(const void *dy_a, const void *dy_b, const void *xhat, const flo
   if (rc == -1) {
     n_partial = ceil_div(rows, kGenericRowsPerChunk);
     dim3 grid(ceil_div(d, kBlock), n_partial);
-    ln_colsum_generic_kernel<T><<<grid, kBlock, 0, st>>>(
+    launch_pdl(ln_colsum_generic_kernel<T>, grid, kBlock, 0, st, 
         static_cast<const T *>(dy_a), static_cast<const T *>(dy_b), static_cast<const T *>(xhat),
         partial, rows, d, kGenericRowsPerChunk);
     DLB_LAUNCH_CHECK("ln_colsum_generic");
-    ln_bwd_dx_generic_kernel<T><<<rows, kBlock, 0, st>>>(
+    launch_pdl(ln_bwd_dx_generic_kernel<T>, rows, kBlock, 0, st, 
         static_cast<const T *>(dy_a), static_cast<const T *>(dy_b), static_cast<const T *>(xhat),
         inv_std, gamma, static_cast<T *>(dx), rows, d);
     DLB_LAUNCH_CHECK("ln_bwd_dx_generic");

@@ -77,6 +77,7 @@ ln_bwd_pipe_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xhat,
                    const float *__restrict__ inv_std, const float *__restrict__ gamma, T *dx,
                    float *__restrict__ partial, int rows, int d, PipeLayout L,
                    unsigned int *timeouts) {
+  pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   constexpr int kColWarps = CT / 32;
@@ -372,7 +373,7 @@ int launch_ln_bwd_pipe(const PipeShape &p, const void *dy_a, const void *dy_b, c
   unsigned int *timeouts = wait_timeouts_counter();
   DLB_REQUIRE(timeouts != nullptr, DLB_ERR_CUDA, "ln_bwd: no timeout counter on this device");
   const int grid = min(sm_count() * p.ctas_per_sm, ceil_div(rows, RT));
-  kern<<<grid, CT + 64, p.layout.total, st>>>(
+  launch_pdl(kern, grid, CT + 64, p.layout.total, st, 
       static_cast<const T *>(dy_a), static_cast<const T *>(dy_b), static_cast<const T *>(xhat), inv_std,
       gamma, static_cast<T *>(dx), partial, rows, d, p.layout, timeouts);
   DLB_LAUNCH_CHECK("ln_bwd_pipe");

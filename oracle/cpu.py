@@ -14,6 +14,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "_build" / "liboracle.so"
 SUB_LEN = 32  # tokens per sub-segment of the CUDA scatter-add (kSubLen in csrc/embedding.cu)
+SLICES = 4    # groups of sub-segments added separately (kCombineSlices in csrc/embedding.cu)
 
 _lib = None
 
@@ -114,7 +115,7 @@ def embed_scatter(dy, ids, vocab, mode="sequential"):
         lib().orc_embed_scatter_f64(_p(dy), _p(ids), _p(grad), n, vocab, d)
     elif mode == "segmented":
         grad = np.empty((vocab, d), np.float32)
-        lib().orc_embed_scatter_segmented(_p(dy), _p(ids), _p(grad), n, vocab, d, SUB_LEN)
+        lib().orc_embed_scatter_segmented(_p(dy), _p(ids), _p(grad), n, vocab, d, SUB_LEN, SLICES)
     else:
         grad = np.empty((vocab, d), np.float32)
         lib().orc_embed_scatter(_p(dy), _p(ids), _p(grad), n, vocab, d)

@@ -168,12 +168,13 @@ void orc_embed_scatter(const float *dy, const int32_t *ids, float *grad, int num
 
 // The same sum in the association the CUDA kernel fixes: the tokens of a row in
 // ascending order; a row with more than `sub_len` tokens is cut into pieces of
-// sub_len tokens, each summed from 0.0f, and the pieces are added in order.
+// sub_len tokens, each summed from 0.0f; the piece sums are added in order inside
+// `slices` contiguous groups of pieces, and the group sums are added in order.
 void orc_embed_scatter_segmented(const float *dy, const int32_t *ids, float *grad, int num_tokens,
-                                 int vocab, int d, int sub_len) {
+                                 int vocab, int d, int sub_len, int slices) {
   std::vector<std::vector<int>> rows(static_cast<size_t>(vocab));
   for (int t = 0; t < num_tokens; t++) rows[ids[t]].push_back(t);
-  std::vector<float> part(static_cast<size_t>(d));
+  std::vector<float> part(static_cast<size_t>(d)), group(static_cast<size_t>(d));
   for (int v = 0; v < vocab; v++) {
     float *dst = grad + static_cast<size_t>(v) * d;
     for (int j = 0; j < d; j++) dst[j] = 0.0f;
@@ -182,13 +183,22 @@ void orc_embed_scatter_segmented(const float *dy, const int32_t *ids, float *gra
     if (n <= sub_len) {
       for (int k = 0; k < n; k++)
         for (int j = 0; j < d; j++) dst[j] += dy[static_cast<size_t>(tok[k]) * d + j];
-    } else {
-      for (int b = 0; b < n; b += sub_len) {
+      continue;
+    }
+    const int pieces = (n + sub_len - 1) / sub_len;
+    const int per = (pieces + slices - 1) / slices;
+    for (int q = 0; q < slices; q++) {
+      for (int j = 0; j < d; j++) group[j] = 0.0f;
+      for (int piece = q * per; piece < pieces && piece < (q + 1) * per; piece++) {
         for (int j = 0; j < d; j++) part[j] = 0.0f;
-        for (int k = b; k < n && k < b + sub_len; k++)
+        for (int k = piece * sub_len; k < n && k < (piece + 1) * sub_len; k++)
           for (int j = 0; j < d; j++) part[j] += dy[static_cast<size_t>(tok[k]) * d + j];
-        for (int j = 0; j < d; j++) dst[j] += part[j];
+        for (int j = 0; j < d; j++) group[j] += part[j];
       }
+      if (q == 0)
+        for (int j = 0; j < d; j++) dst[j] = group[j];
+      else
+        for (int j = 0; j < d; j++) dst[j] += group[j];
     }
   }
 }

@@ -106,6 +106,17 @@ def test_scatter_add_edge_patterns(pattern):
     assert rel_err(grad, oracle.embed_scatter(dy, ids, vocab, "f64")) <= 1e-5
 
 
+@pytest.mark.parametrize("vocab,d,n", [(500, 8, 70000), (70000, 16, 66000), (300, 64, 65536), (300, 64, 65537)])
+def test_scatter_add_many_tokens(vocab, d, n):
+    """Above 65536 tokens the plan is built by the multi-kernel radix sort instead of the
+    single cluster launch; both sides of the switch must agree with the oracle."""
+    ids = zipf_ids(rng_for(21, 0), n, vocab)
+    dy = rng_for(21, 1).standard_normal((n, d)).astype(np.float32)
+    grad = scatter(dev(dy), dev(ids), vocab).cpu().numpy()
+    assert bits_equal(grad, oracle.embed_scatter(dy, ids, vocab, "segmented"))
+    assert rel_err(grad, oracle.embed_scatter(dy, ids, vocab, "f64")) <= 1e-5
+
+
 def test_scatter_add_is_deterministic_and_overwrites():
     vocab, d, n = 2000, 512, 16384
     ids = zipf_ids(rng_for(40, 0), n, vocab)
