@@ -167,6 +167,8 @@ class Chain:
 
     def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist):
         from dl_cuda_b200 import capi, ops
+        global allreduce_param_grads
+        from dl_cuda_b200.sharding import allreduce_param_grads
         self.capi, self.ops, self.lib = capi, ops, capi.lib()
         self.T, self.S, self.D, self.F, self.V = tokens, seq, d, f, vocab
         self.dist = dist
@@ -291,8 +293,7 @@ class Chain:
                                       self.ws_embed.numel(), T, V, D, code, st))
         mark()
         if self.dist.active:
-            self.dist.dist.all_reduce(self.small_grads)
-            self.dist.dist.all_reduce(self.table_grad)
+            allreduce_param_grads(self.dist.dist, self.small_grads, self.table_grad)
         mark()
         if copy_inputs:
             self.h_result.copy_(self.small_grads, non_blocking=True)
@@ -529,7 +530,8 @@ def main():
     dist.init()
     peak, peak_kind = measured_peak()
     n = dist.world
-    tokens_local = args.tokens // n
+    from dl_cuda_b200.sharding import shard_rows
+    _, tokens_local = shard_rows(args.tokens, n, dist.rank, SEQ if args.tokens % (SEQ * n) == 0 else 1)
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     chain = Chain(tokens_local, SEQ, D_MODEL, D_FF, VOCAB, dtype, seed=1234 + dist.rank, dist=dist)
     lib = chain.lib
