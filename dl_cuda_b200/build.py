@@ -74,5 +74,24 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB_PATH
 
 
+CPP_TEST_SRC = PKG_DIR.parent / "tests" / "cpp" / "layer_api_test.cu"
+CPP_TEST_BIN = PKG_DIR.parent / "tests" / "cpp" / "layer_api_test"
+
+
+def build_cpp_tests() -> Path:
+    """Compile the C++ program that drives the layer classes of src/*.cuh against the library."""
+    build()
+    deps = [CPP_TEST_SRC, LIB_PATH] + sorted((PKG_DIR / "src").glob("*.cuh"))
+    if _stale(CPP_TEST_BIN, deps):
+        cmd = [_nvcc(), "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2",
+               f"-I{PKG_DIR / 'src'}", f"-I{PKG_DIR.parent / 'include'}", str(CPP_TEST_SRC), "-o", str(CPP_TEST_BIN),
+               f"-L{PKG_DIR}", "-ldlcuda_b200", "-Xlinker", "-rpath,$ORIGIN/../../dl_cuda_b200"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {CPP_TEST_SRC.name}:\n{res.stderr}")
+    return CPP_TEST_BIN
+
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    print(build_cpp_tests())

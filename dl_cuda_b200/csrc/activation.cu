@@ -109,15 +109,16 @@ __device__ __forceinline__ uint32_t load_mask(const uint8_t *mask, size_t off) {
   return (byte >> ((off & 4) ? 4 : 0)) & 0xfu;
 }
 
-template <typename T, int KIND>
-__global__ void __launch_bounds__(kBlock)
-act_fwd_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, int64_t rows,
-               int64_t cols, int64_t n, int64_t rows_per_cta) {
+// I is the element-index type: int when every index fits 31 bits (fewer registers), else int64_t.
+template <typename T, int KIND, typename I>
+__global__ void __launch_bounds__(kBlock, 4)
+act_fwd_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, I rows,
+               I cols, I n, I rows_per_cta) {
   pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
-  const int64_t ncv = cols / E;
-  const int64_t cv = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const I ncv = cols / E;
+  const I cv = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x;
   const bool col_ok = cv < ncv;
   const int ty = blockDim.y;
 
@@ -133,17 +134,17 @@ act_fwd_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, in
     }
   }
 
-  const int64_t r_begin = static_cast<int64_t>(blockIdx.y) * rows_per_cta;
-  const int64_t r_end = min(rows, r_begin + rows_per_cta);
-  for (int64_t r0 = r_begin; r0 < r_end; r0 += static_cast<int64_t>(ty) * kUnroll) {
+  const I r_begin = static_cast<I>(blockIdx.y) * rows_per_cta;
+  const I r_end = (rows < r_begin + rows_per_cta ? rows : r_begin + rows_per_cta);
+  for (I r0 = r_begin; r0 < r_end; r0 += static_cast<I>(ty) * kUnroll) {
     uint4 in[kUnroll];
-    size_t off[kUnroll];
+    I off[kUnroll];
     bool ok[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; u++) {
-      const int64_t r = r0 + u * ty + threadIdx.y;
-      off[u] = static_cast<size_t>(r) * cols + static_cast<size_t>(cv) * E;
-      ok[u] = col_ok && r < r_end && static_cast<int64_t>(off[u]) + E <= n;
+      const I r = r0 + u * ty + threadIdx.y;
+      off[u] = r * cols + cv * E;
+      ok[u] = col_ok && r < r_end && off[u] + E <= n;
       if (ok[u]) in[u] = ld_stream(x + off[u]);
     }
 #pragma unroll
@@ -176,16 +177,16 @@ act_fwd_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, in
 }
 
 // partial (when non-null) is [gridDim.y][cols]: the CTA's column sums of dx.
-template <typename T, int KIND>
-__global__ void __launch_bounds__(kBlock)
-act_bwd_kernel(const T *dy, const void *cache, T *dx, float *__restrict__ partial, int64_t rows,
-               int64_t cols, int64_t n, int64_t rows_per_cta) {
+template <typename T, int KIND, typename I>
+__global__ void __launch_bounds__(kBlock, 4)
+act_bwd_kernel(const T *dy, const void *cache, T *dx, float *__restrict__ partial, I rows,
+               I cols, I n, I rows_per_cta) {
   pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
   __shared__ float colacc[kBlock * E];  // [ty][tx*E]
-  const int64_t ncv = cols / E;
-  const int64_t cv = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const I ncv = cols / E;
+  const I cv = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x;
   const bool col_ok = cv < ncv;
   const int ty = blockDim.y;
 
@@ -193,18 +194,18 @@ act_bwd_kernel(const T *dy, const void *cache, T *dx, float *__restrict__ partia
 #pragma unroll
   for (int e = 0; e < E; e++) acc[e] = 0.f;
 
-  const int64_t r_begin = static_cast<int64_t>(blockIdx.y) * rows_per_cta;
-  const int64_t r_end = min(rows, r_begin + rows_per_cta);
-  for (int64_t r0 = r_begin; r0 < r_end; r0 += static_cast<int64_t>(ty) * kUnroll) {
+  const I r_begin = static_cast<I>(blockIdx.y) * rows_per_cta;
+  const I r_end = (rows < r_begin + rows_per_cta ? rows : r_begin + rows_per_cta);
+  for (I r0 = r_begin; r0 < r_end; r0 += static_cast<I>(ty) * kUnroll) {
     uint4 g[kUnroll], c[kUnroll];
     uint32_t bits[kUnroll];
-    size_t off[kUnroll];
+    I off[kUnroll];
     bool ok[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; u++) {
-      const int64_t r = r0 + u * ty + threadIdx.y;
-      off[u] = static_cast<size_t>(r) * cols + static_cast<size_t>(cv) * E;
-      ok[u] = col_ok && r < r_end && static_cast<int64_t>(off[u]) + E <= n;
+      const I r = r0 + u * ty + threadIdx.y;
+      off[u] = r * cols + cv * E;
+      ok[u] = col_ok && r < r_end && off[u] + E <= n;
       if (ok[u]) {
         g[u] = ld_stream(dy + off[u]);
         if constexpr (KIND == DLB_ACT_RELU) {
@@ -350,9 +351,12 @@ int act_fwd_typed(const void *x, const float *bias, void *y, void *cache, int64_
       vr = ceil_div<int64_t>(n, vc);
     }
     const Tiling t = make_tiling(vr, vc / E);
-    launch_pdl(act_fwd_kernel<T, KIND>, t.grid, t.block, 0, st, static_cast<const T *>(x), bias,
-                                                        static_cast<T *>(y), cache, vr, vc, n,
-                                                        t.rows_per_cta);
+    if (n + vc * 4 * kBlock < INT32_MAX)
+      launch_pdl(act_fwd_kernel<T, KIND, int>, t.grid, t.block, 0, st, static_cast<const T *>(x), bias,
+                 static_cast<T *>(y), cache, vr, vc, n, t.rows_per_cta);
+    else
+      launch_pdl(act_fwd_kernel<T, KIND, int64_t>, t.grid, t.block, 0, st, static_cast<const T *>(x), bias,
+                 static_cast<T *>(y), cache, vr, vc, n, t.rows_per_cta);
     DLB_LAUNCH_CHECK("act_fwd");
     return DLB_OK;
   }
@@ -375,7 +379,12 @@ int act_bwd_typed(const void *dy, const void *cache, void *dx, float *dbias, flo
       vr = ceil_div<int64_t>(n, vc);
     }
     const Tiling t = make_tiling(vr, vc / E);
-    launch_pdl(act_bwd_kernel<T, KIND>, t.grid, t.block, 0, st, 
+    if (n + vc * 4 * kBlock < INT32_MAX)
+      launch_pdl(act_bwd_kernel<T, KIND, int>, t.grid, t.block, 0, st, 
+        static_cast<const T *>(dy), cache, static_cast<T *>(dx), dbias ? partial : nullptr, vr, vc,
+        n, t.rows_per_cta);
+    else
+      launch_pdl(act_bwd_kernel<T, KIND, int64_t>, t.grid, t.block, 0, st, 
         static_cast<const T *>(dy), cache, static_cast<T *>(dx), dbias ? partial : nullptr, vr, vc,
         n, t.rows_per_cta);
     DLB_LAUNCH_CHECK("act_bwd");

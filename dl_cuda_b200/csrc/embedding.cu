@@ -340,11 +340,10 @@ Plan make_plan(void *workspace, int num_tokens, int vocab, int d) {
   return p;
 }
 
-// Sum of dy rows perm[b..e) over this thread's KV column vectors, in order.
-template <typename T, int KV>
-__device__ __forceinline__ void sum_tokens(const T *__restrict__ dy, const int32_t *__restrict__ perm,
-                                           int b, int e, int d, int cv0, int tx, int ncv,
-                                           float (&acc)[KV][Store<T>::kPerVec]) {
+// Sum of the dy rows tok(b) .. tok(e-1) over this thread's KV column vectors, in order.
+template <typename T, int KV, typename Tok>
+__device__ __forceinline__ void sum_tokens(const T *__restrict__ dy, Tok tok, int b, int e, int d, int cv0,
+                                           int tx, int ncv, float (&acc)[KV][Store<T>::kPerVec]) {
   using S = Store<T>;
   constexpr int E = S::kPerVec;
 #pragma unroll
@@ -353,8 +352,8 @@ __device__ __forceinline__ void sum_tokens(const T *__restrict__ dy, const int32
     for (int q = 0; q < E; q++) acc[k][q] = 0.f;
   int j = b;
   for (; j + 2 <= e; j += 2) {
-    const size_t r0 = static_cast<size_t>(__ldg(perm + j)) * d;
-    const size_t r1 = static_cast<size_t>(__ldg(perm + j + 1)) * d;
+    const size_t r0 = static_cast<size_t>(tok(j)) * d;
+    const size_t r1 = static_cast<size_t>(tok(j + 1)) * d;
     uint4 v0[KV], v1[KV];
 #pragma unroll
     for (int k = 0; k < KV; k++) {
@@ -379,7 +378,7 @@ __device__ __forceinline__ void sum_tokens(const T *__restrict__ dy, const int32
     }
   }
   if (j < e) {
-    const size_t r0 = static_cast<size_t>(__ldg(perm + j)) * d;
+    const size_t r0 = static_cast<size_t>(tok(j)) * d;
 #pragma unroll
     for (int k = 0; k < KV; k++) {
       const int cv = cv0 + k * tx;
@@ -393,9 +392,34 @@ __device__ __forceinline__ void sum_tokens(const T *__restrict__ dy, const int32
   }
 }
 
+template <typename T, int KV>
+__device__ __forceinline__ void store_row(float *dst, int cv0, int tx, int ncv,
+                                          const float (&acc)[KV][Store<T>::kPerVec]) {
+  constexpr int E = Store<T>::kPerVec;
+#pragma unroll
+  for (int k = 0; k < KV; k++) {
+    const int cv = cv0 + k * tx;
+    if (cv < ncv) {
+#pragma unroll
+      for (int q = 0; q < E / 4; q++) {
+        const uint4 o = make_uint4(__float_as_uint(acc[k][4 * q]), __float_as_uint(acc[k][4 * q + 1]),
+                                   __float_as_uint(acc[k][4 * q + 2]), __float_as_uint(acc[k][4 * q + 3]));
+        st_stream(dst + static_cast<size_t>(cv) * E + 4 * q, o);
+      }
+    }
+  }
+}
+
 // blockDim = (tx, ty).  grid.x = sub_groups + row_groups; grid.y tiles columns
 // when a row has more than tx*KV vectors.  The sub-segment groups come first so
-// that the heaviest work starts first.
+// that the heaviest work starts first.  A row group is kScatterRowsPerCta (or ty,
+// if larger) consecutive table rows: the CTA fetches their segment bounds and the
+// token list they share (consecutive rows are consecutive in the sorted list)
+// into shared memory once, then each thread row walks its rows, so the only
+// dependent global access left per row is the dy load itself.
+constexpr int kScatterRowsPerCta = 16;
+constexpr int kScatterPermCap = 1024;
+
 template <typename T, int KV>
 __global__ void __launch_bounds__(kBlock)
 scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
@@ -406,11 +430,12 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
   pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
+  __shared__ int s_seg[kBlock + 1];
+  __shared__ int s_perm[kScatterPermCap];
   const int tx = blockDim.x, ty = blockDim.y;
   const int ncv = d / E;
   const int cv0 = blockIdx.y * (tx * KV) + threadIdx.x;
   float acc[KV][E];
-  float *dst;
   if (static_cast<int>(blockIdx.x) < sub_groups) {
     const int idx = blockIdx.x * ty + threadIdx.y;
     const int n_long = meta[0], n_sub = meta[1];
@@ -423,27 +448,29 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
     const int v = long_row[lo];
     const int b = seg_start[v] + (idx - long_first[lo]) * kSubLen;
     const int e = min(seg_start[v + 1], b + kSubLen);
-    sum_tokens<T, KV>(dy, perm, b, e, d, cv0, tx, ncv, acc);
-    dst = scratch + static_cast<size_t>(idx) * d;
-  } else {
-    const int v = (blockIdx.x - sub_groups) * ty + threadIdx.y;
-    if (v >= vocab) return;
-    const int b = seg_start[v], e = seg_start[v + 1];
-    if (e - b > kSubLen) return;  // long row: written by combine_long_kernel
-    sum_tokens<T, KV>(dy, perm, b, e, d, cv0, tx, ncv, acc);
-    dst = grad + static_cast<size_t>(v) * d;
+    sum_tokens<T, KV>(dy, [&](int j) { return __ldg(perm + j); }, b, e, d, cv0, tx, ncv, acc);
+    store_row<T, KV>(scratch + static_cast<size_t>(idx) * d, cv0, tx, ncv, acc);
+    return;
   }
-#pragma unroll
-  for (int k = 0; k < KV; k++) {
-    const int cv = cv0 + k * tx;
-    if (cv < ncv) {
-#pragma unroll
-      for (int q = 0; q < E / 4; q++) {
-        const uint4 o = make_uint4(__float_as_uint(acc[k][4 * q]), __float_as_uint(acc[k][4 * q + 1]),
-                                   __float_as_uint(acc[k][4 * q + 2]), __float_as_uint(acc[k][4 * q + 3]));
-        st_stream(dst + static_cast<size_t>(cv) * E + 4 * q, o);
-      }
-    }
+  const int rows_cta = ty > kScatterRowsPerCta ? ty : kScatterRowsPerCta;
+  const int v_first = (blockIdx.x - sub_groups) * rows_cta;
+  const int nrows = min(rows_cta, vocab - v_first);
+  const int tid = threadIdx.y * tx + threadIdx.x;
+  for (int i = tid; i <= nrows; i += kBlock) s_seg[i] = __ldg(seg_start + v_first + i);
+  __syncthreads();
+  const int p0 = s_seg[0], np = s_seg[nrows] - p0;
+  const bool staged = np <= kScatterPermCap;
+  if (staged)
+    for (int i = tid; i < np; i += kBlock) s_perm[i] = __ldg(perm + p0 + i);
+  __syncthreads();
+  for (int rl = threadIdx.y; rl < nrows; rl += ty) {
+    const int b = s_seg[rl], e = s_seg[rl + 1];
+    if (e - b > kSubLen) continue;  // long row: written by combine_long_kernel
+    if (staged)
+      sum_tokens<T, KV>(dy, [&](int j) { return s_perm[j - p0]; }, b, e, d, cv0, tx, ncv, acc);
+    else
+      sum_tokens<T, KV>(dy, [&](int j) { return __ldg(perm + j); }, b, e, d, cv0, tx, ncv, acc);
+    store_row<T, KV>(grad + static_cast<size_t>(v_first + rl) * d, cv0, tx, ncv, acc);
   }
 }
 
@@ -567,7 +594,7 @@ int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *gr
   constexpr int E = Store<T>::kPerVec;
   const int ncv = d / E;
   const int sub_groups = ceil_div(p.max_sub, bs.ty);
-  const int row_groups = ceil_div(vocab, bs.ty);
+  const int row_groups = ceil_div(vocab, bs.ty > kScatterRowsPerCta ? bs.ty : kScatterRowsPerCta);
   dim3 grid(sub_groups + row_groups, ceil_div(ncv, bs.tx * KV));
   launch_pdl(scatter_rows_kernel<T, KV>, grid, dim3(bs.tx, bs.ty), 0, st, 
       static_cast<const T *>(dy), perm, p.seg_start, p.long_row, p.long_first, p.meta, grad,
