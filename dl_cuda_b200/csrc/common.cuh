@@ -11,6 +11,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 
 #include "../../include/dlcuda_b200.h"
 
@@ -66,6 +67,18 @@ inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);  // errors surface in DLB_LAUNCH_CHECK
+}
+
+// Plain stream-ordered launch (no programmatic overlap with the previous kernel).
+template <typename... KArgs, typename... Args>
+inline void launch_plain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                         Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 template <typename T>
@@ -141,6 +154,16 @@ __device__ __forceinline__ uint4 ld_stream(const void *p) {
 __device__ __forceinline__ void st_stream(void *p, const uint4 &v) {
   __stcs(reinterpret_cast<uint4 *>(p), v);
 }
+// 32-byte streaming store (sm_100 256-bit global access): one lane writes a whole
+// 32-byte sector, where two 16-byte stores with a 32-byte lane stride would each
+// write half of it.  p must be 32-byte aligned.
+__device__ __forceinline__ void st_stream32(float *p, const float (&f)[8]) {
+  asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(f[0]), "f"(f[1]),
+               "f"(f[2]), "f"(f[3]), "f"(f[4]), "f"(f[5]), "f"(f[6]), "f"(f[7])
+               : "memory");
+}
+inline bool aligned32(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
+
 // Read-only, cached 16-byte access for operands that are reused across rows.
 __device__ __forceinline__ uint4 ld_keep(const void *p) {
   return __ldg(reinterpret_cast<const uint4 *>(p));

@@ -69,7 +69,11 @@ __device__ __forceinline__ int cta_exclusive_scan(int v, int n, int *tmp, int *t
 
 __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterThreads)
 embed_plan_cluster_kernel(ClusterPlanArgs a) {
-  pdl_prologue();
+  // Launched plainly and without an early trigger: this kernel neither overlaps its
+  // predecessor nor lets its successor be scheduled before it has finished.  (With
+  // programmatic dependent launch around this cluster kernel, the kernel after it
+  // was seen reading the plan before it was complete.)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   cg::cluster_group cluster = cg::this_cluster();
   // Dynamic shared memory (68 KB, above the static limit), same layout in every CTA.
   extern __shared__ int smem_i[];

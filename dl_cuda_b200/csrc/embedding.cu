@@ -11,8 +11,8 @@
 //     kSubLen tokens is summed in ascending token order and written once (zero
 //     if no token refers to it).  Long rows are cut into sub-segments of
 //     kSubLen tokens, each summed by its own thread group into a scratch row.
-//  3. combine_long_kernel: adds a long row's scratch rows: four contiguous quarters of
-//     the sub-segments are summed in order, then the four quarter sums in order.
+//  3. combine_long_kernel: adds a long row's scratch rows: 8 contiguous slices of
+//     the sub-segments are summed in order, then the 8 slice sums in order.
 // The order of every addition is a function of ids alone, so two runs give the
 // same bits whatever the scheduling.
 #include "common.cuh"
@@ -350,34 +350,33 @@ __device__ __forceinline__ void sum_tokens(const T *__restrict__ dy, Tok tok, in
   for (int k = 0; k < KV; k++)
 #pragma unroll
     for (int q = 0; q < E; q++) acc[k][q] = 0.f;
+  // UNR token rows in flight per step; the additions stay in token order.
+  constexpr int UNR = KV >= 4 ? 2 : 4;
   int j = b;
-  for (; j + 2 <= e; j += 2) {
-    const size_t r0 = static_cast<size_t>(tok(j)) * d;
-    const size_t r1 = static_cast<size_t>(tok(j + 1)) * d;
-    uint4 v0[KV], v1[KV];
+  for (; j + UNR <= e; j += UNR) {
+    uint4 v[UNR][KV];
 #pragma unroll
-    for (int k = 0; k < KV; k++) {
-      const int cv = cv0 + k * tx;
-      if (cv < ncv) {
-        v0[k] = ld_stream(dy + r0 + static_cast<size_t>(cv) * E);
-        v1[k] = ld_stream(dy + r1 + static_cast<size_t>(cv) * E);
+    for (int u = 0; u < UNR; u++) {
+      const size_t r = static_cast<size_t>(tok(j + u)) * d;
+#pragma unroll
+      for (int k = 0; k < KV; k++) {
+        const int cv = cv0 + k * tx;
+        if (cv < ncv) v[u][k] = ld_stream(dy + r + static_cast<size_t>(cv) * E);
       }
     }
 #pragma unroll
-    for (int k = 0; k < KV; k++) {
-      if (cv0 + k * tx < ncv) {
-        float f0[E], f1[E];
-        S::unpack(v0[k], f0);
-        S::unpack(v1[k], f1);
+    for (int u = 0; u < UNR; u++)
 #pragma unroll
-        for (int q = 0; q < E; q++) {
-          acc[k][q] += f0[q];
-          acc[k][q] += f1[q];
+      for (int k = 0; k < KV; k++) {
+        if (cv0 + k * tx < ncv) {
+          float f[E];
+          S::unpack(v[u][k], f);
+#pragma unroll
+          for (int q = 0; q < E; q++) acc[k][q] += f[q];
         }
       }
-    }
   }
-  if (j < e) {
+  for (; j < e; j++) {
     const size_t r0 = static_cast<size_t>(tok(j)) * d;
 #pragma unroll
     for (int k = 0; k < KV; k++) {
@@ -400,11 +399,16 @@ __device__ __forceinline__ void store_row(float *dst, int cv0, int tx, int ncv,
   for (int k = 0; k < KV; k++) {
     const int cv = cv0 + k * tx;
     if (cv < ncv) {
+      if constexpr (E == 8) {
+        // dst rows are 32-byte aligned (checked on the host: base and d*4 are)
+        st_stream32(dst + static_cast<size_t>(cv) * E, acc[k]);
+      } else {
 #pragma unroll
-      for (int q = 0; q < E / 4; q++) {
-        const uint4 o = make_uint4(__float_as_uint(acc[k][4 * q]), __float_as_uint(acc[k][4 * q + 1]),
-                                   __float_as_uint(acc[k][4 * q + 2]), __float_as_uint(acc[k][4 * q + 3]));
-        st_stream(dst + static_cast<size_t>(cv) * E + 4 * q, o);
+        for (int q = 0; q < E / 4; q++) {
+          const uint4 o = make_uint4(__float_as_uint(acc[k][4 * q]), __float_as_uint(acc[k][4 * q + 1]),
+                                     __float_as_uint(acc[k][4 * q + 2]), __float_as_uint(acc[k][4 * q + 3]));
+          st_stream(dst + static_cast<size_t>(cv) * E + 4 * q, o);
+        }
       }
     }
   }
@@ -437,19 +441,19 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
   const int cv0 = blockIdx.y * (tx * KV) + threadIdx.x;
   float acc[KV][E];
   if (static_cast<int>(blockIdx.x) < sub_groups) {
-    const int idx = blockIdx.x * ty + threadIdx.y;
     const int n_long = meta[0], n_sub = meta[1];
-    if (idx >= n_sub) return;
-    int lo = 0, hi = n_long;  // last long row whose first sub-segment is <= idx
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (long_first[mid] <= idx) lo = mid; else hi = mid;
+    for (int idx = blockIdx.x * ty + threadIdx.y; idx < n_sub; idx += sub_groups * ty) {
+      int lo = 0, hi = n_long;  // last long row whose first sub-segment is <= idx
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (long_first[mid] <= idx) lo = mid; else hi = mid;
+      }
+      const int v = long_row[lo];
+      const int b = seg_start[v] + (idx - long_first[lo]) * kSubLen;
+      const int e = min(seg_start[v + 1], b + kSubLen);
+      sum_tokens<T, KV>(dy, [&](int j) { return __ldg(perm + j); }, b, e, d, cv0, tx, ncv, acc);
+      store_row<T, KV>(scratch + static_cast<size_t>(idx) * d, cv0, tx, ncv, acc);
     }
-    const int v = long_row[lo];
-    const int b = seg_start[v] + (idx - long_first[lo]) * kSubLen;
-    const int e = min(seg_start[v + 1], b + kSubLen);
-    sum_tokens<T, KV>(dy, [&](int j) { return __ldg(perm + j); }, b, e, d, cv0, tx, ncv, acc);
-    store_row<T, KV>(scratch + static_cast<size_t>(idx) * d, cv0, tx, ncv, acc);
     return;
   }
   const int rows_cta = ty > kScatterRowsPerCta ? ty : kScatterRowsPerCta;
@@ -463,9 +467,53 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
   if (staged)
     for (int i = tid; i < np; i += kBlock) s_perm[i] = __ldg(perm + p0 + i);
   __syncthreads();
+  // Rows with no token or one token (nearly all of them): U rows at a time, every
+  // load of the U rows issued before the first store, so that U*KV 16-byte loads per
+  // thread are in flight.  A row's sum is still 0.0f + dy (the same bits as the
+  // general path below).
+  constexpr int U = KV >= 4 ? 2 : 4;
+  for (int rl0 = threadIdx.y; rl0 < nrows; rl0 += ty * U) {
+    uint4 v[U][KV];
+    int state[U];  // -1: not mine or handled below, 0: empty row, 1: one token
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int rl = rl0 + u * ty;
+      state[u] = -1;
+      if (rl < nrows) {
+        const int b = s_seg[rl], cnt = s_seg[rl + 1] - b;
+        if (cnt <= 1) state[u] = cnt;
+        if (cnt == 1) {
+          const int t = staged ? s_perm[b - p0] : __ldg(perm + b);
+          const T *src = dy + static_cast<size_t>(t) * d;
+#pragma unroll
+          for (int k = 0; k < KV; k++) {
+            const int cv = cv0 + k * tx;
+            if (cv < ncv) v[u][k] = ld_stream(src + static_cast<size_t>(cv) * E);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      if (state[u] < 0) continue;
+#pragma unroll
+      for (int k = 0; k < KV; k++) {
+#pragma unroll
+        for (int q = 0; q < E; q++) acc[k][q] = 0.f;
+        if (state[u] == 1 && cv0 + k * tx < ncv) {
+          float f[E];
+          S::unpack(v[u][k], f);
+#pragma unroll
+          for (int q = 0; q < E; q++) acc[k][q] += f[q];
+        }
+      }
+      store_row<T, KV>(grad + static_cast<size_t>(v_first + rl0 + u * ty) * d, cv0, tx, ncv, acc);
+    }
+  }
+  // Rows with 2..kSubLen tokens.
   for (int rl = threadIdx.y; rl < nrows; rl += ty) {
     const int b = s_seg[rl], e = s_seg[rl + 1];
-    if (e - b > kSubLen) continue;  // long row: written by combine_long_kernel
+    if (e - b < 2 || e - b > kSubLen) continue;  // long rows are written by combine_long_kernel
     if (staged)
       sum_tokens<T, KV>(dy, [&](int j) { return s_perm[j - p0]; }, b, e, d, cv0, tx, ncv, acc);
     else
@@ -474,26 +522,29 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
   }
 }
 
-// grad[v,:] = the scratch rows of long row v.  Four adjacent lanes share one
-// float4 column vector: lane k adds the k-th contiguous quarter of the row's
-// sub-segments in order, then the four quarter sums are added in order.
-constexpr int kCombineSlices = 4;
+// grad[v,:] = the scratch rows of long row v.  A work item is (long row, block of
+// 32 float4 column vectors); CTAs loop over the items.  Each of the CTA's
+// kCombineSlices warps adds one contiguous slice of the row's sub-segments in
+// order (512 contiguous bytes per sub-segment), then the slice sums are added in
+// warp order through shared memory.
+constexpr int kCombineSlices = 8;
+static_assert(kCombineSlices * 32 == kBlock, "one warp per slice");
 
 __global__ void __launch_bounds__(kBlock)
 combine_long_kernel(const float *__restrict__ scratch, const int32_t *__restrict__ long_row,
                     const int32_t *__restrict__ long_first, const int32_t *__restrict__ meta,
                     float *__restrict__ grad, int d) {
   pdl_prologue();
-  const int li = blockIdx.x;
-  if (li >= meta[0]) return;
-  const int v = long_row[li];
-  const int s0 = long_first[li], s1 = long_first[li + 1];
-  const int per = (s1 - s0 + kCombineSlices - 1) / kCombineSlices;
-  const int slice = threadIdx.x & (kCombineSlices - 1), cvl = threadIdx.x / kCombineSlices;
-  constexpr int kVecPerCta = kBlock / kCombineSlices;
-  const int b = min(s1, s0 + slice * per), e = min(s1, b + per);
-  for (int cb = blockIdx.y * kVecPerCta; cb * 4 < d; cb += gridDim.y * kVecPerCta) {
-    const int c = (cb + cvl) * 4;
+  __shared__ float4 part[kCombineSlices][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = d / 4;
+  const int ncb = (nvec + 31) / 32;  // column blocks per row
+  const int items = meta[0] * ncb;
+  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    const int li = item / ncb, c = ((item % ncb) * 32 + lane) * 4;
+    const int s0 = long_first[li], s1 = long_first[li + 1];
+    const int per = (s1 - s0 + kCombineSlices - 1) / kCombineSlices;
+    const int b = min(s1, s0 + warp * per), e = min(s1, b + per);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < d) {
 #pragma unroll 8
@@ -502,15 +553,18 @@ combine_long_kernel(const float *__restrict__ scratch, const int32_t *__restrict
         acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
       }
     }
-    float4 r = acc;
+    __syncthreads();  // part[] of the previous item has been read
+    part[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && c < d) {
+      float4 r = part[0][lane];
 #pragma unroll
-    for (int k = 1; k < kCombineSlices; k++) {
-      r.x += __shfl_down_sync(0xffffffffu, acc.x, k);
-      r.y += __shfl_down_sync(0xffffffffu, acc.y, k);
-      r.z += __shfl_down_sync(0xffffffffu, acc.z, k);
-      r.w += __shfl_down_sync(0xffffffffu, acc.w, k);
+      for (int k = 1; k < kCombineSlices; k++) {
+        const float4 p = part[k][lane];
+        r.x += p.x; r.y += p.y; r.z += p.z; r.w += p.w;
+      }
+      __stcs(reinterpret_cast<float4 *>(grad + static_cast<size_t>(long_row[li]) * d + c), r);
     }
-    if (slice == 0 && c < d) __stcs(reinterpret_cast<float4 *>(grad + static_cast<size_t>(v) * d + c), r);
   }
 }
 
@@ -528,7 +582,7 @@ scatter_scalar_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm
   const int b = seg_start[v], e = seg_start[v + 1];
   float total = 0.f;
   // Same association as the vector path: sub-segments of kSubLen tokens, their sums
-  // added inside four contiguous quarters, then the quarter sums in order.
+  // added inside kCombineSlices contiguous slices, then the slice sums in order.
   if (e - b <= kSubLen) {
     for (int j = b; j < e; j++) total += S::to_float(dy[static_cast<size_t>(perm[j]) * d + c]);
   } else {
@@ -593,7 +647,8 @@ int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *gr
                    BlockShape bs, cudaStream_t st) {
   constexpr int E = Store<T>::kPerVec;
   const int ncv = d / E;
-  const int sub_groups = ceil_div(p.max_sub, bs.ty);
+  // Sub-segment groups loop over the sub-segments, so a few hundred CTAs cover any count.
+  const int sub_groups = min(ceil_div(p.max_sub, bs.ty), 4 * sm_count());
   const int row_groups = ceil_div(vocab, bs.ty > kScatterRowsPerCta ? bs.ty : kScatterRowsPerCta);
   dim3 grid(sub_groups + row_groups, ceil_div(ncv, bs.tx * KV));
   launch_pdl(scatter_rows_kernel<T, KV>, grid, dim3(bs.tx, bs.ty), 0, st, 
@@ -607,7 +662,8 @@ template <typename T>
 int scatter_typed(const Plan &p, const void *dy, float *grad, int vocab, int d, cudaStream_t st) {
   constexpr int E = Store<T>::kPerVec;
   const int32_t *perm = p.vals[p.passes & 1];
-  const bool vec = d % E == 0 && aligned16(dy) && aligned16(grad);
+  // bf16 input: rows of grad and scratch are written 32 bytes at a time (d % 8 == 0 makes row starts 32-byte aligned).
+  const bool vec = d % E == 0 && aligned16(dy) && (E == 8 ? aligned32(grad) : aligned16(grad));
   if (!vec) {
     const int64_t total = static_cast<int64_t>(vocab) * d;
     launch_pdl(scatter_scalar_kernel<T>, static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st, 
@@ -623,7 +679,7 @@ int scatter_typed(const Plan &p, const void *dy, float *grad, int vocab, int d, 
   else if (need >= 2) rc = launch_scatter<T, 2>(p, dy, perm, grad, vocab, d, bs, st);
   else rc = launch_scatter<T, 1>(p, dy, perm, grad, vocab, d, bs, st);
   if (rc != DLB_OK) return rc;
-  dim3 grid(p.max_long, max(1, min(16, ceil_div(d / 4, kBlock / kCombineSlices))));
+  const int grid = 2 * sm_count();
   launch_pdl(combine_long_kernel, grid, kBlock, 0, st, p.scratch, p.long_row, p.long_first, p.meta, grad, d);
   DLB_LAUNCH_CHECK("combine_long");
   return DLB_OK;
@@ -685,7 +741,8 @@ extern "C" int dlb_embed_sort_tokens(const int32_t *ids, void *workspace, size_t
                                          static_cast<int>(kClusterPlanSmem));
     DLB_REQUIRE(e == cudaSuccess, DLB_ERR_CUDA, "embed_sort_tokens: shared memory attribute: %s",
                 cudaGetErrorString(e));
-    launch_pdl(embed_plan_cluster_kernel, kClusterCtas, kClusterThreads, kClusterPlanSmem, st, a);
+    // Plain launch: this kernel must not overlap its neighbours (see the kernel's first lines).
+    launch_plain(embed_plan_cluster_kernel, kClusterCtas, kClusterThreads, kClusterPlanSmem, st, a);
     DLB_LAUNCH_CHECK("embed_plan_cluster");
     return DLB_OK;
   }

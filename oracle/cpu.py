@@ -14,7 +14,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "_build" / "liboracle.so"
 SUB_LEN = 32  # tokens per sub-segment of the CUDA scatter-add (kSubLen in csrc/embedding.cu)
-SLICES = 4    # groups of sub-segments added separately (kCombineSlices in csrc/embedding.cu)
+SLICES = 8    # groups of sub-segments added separately (kCombineSlices in csrc/embedding.cu)
 
 _lib = None
 

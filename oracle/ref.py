@@ -17,6 +17,9 @@ HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "_ref" / "libref_shim.so"
 
 _lib = None
+# Reference layers with weights built in this process so far: the reference seeds the n-th one
+# with global_seed + 9973*n (src/layers.cuh:15-19) and the counter cannot be reset.
+layers_built = 0
 
 
 def available() -> bool:
@@ -173,6 +176,8 @@ def sgd(p, g, lr):
 
 def embedding_init(seed, vocab, d, num_tokens, checkpoint_path=None):
     """cuRAND-initialised table of a reference EmbeddingLayer built after set_global_init_seed(seed)."""
+    global layers_built
+    layers_built += 1
     t = np.empty((vocab, d), np.float32)
     path = None if checkpoint_path is None else str(checkpoint_path).encode()
     code = lib().ref_embedding_init(C.c_uint64(seed), vocab, d, num_tokens, C.c_void_p(t.ctypes.data), path)
@@ -182,6 +187,8 @@ def embedding_init(seed, vocab, d, num_tokens, checkpoint_path=None):
 
 def embedding_layer_run(table, ids, dout):
     """The reference EmbeddingLayer class end to end on host arrays: (out, grad)."""
+    global layers_built
+    layers_built += 1
     table = np.ascontiguousarray(table, np.float32)
     ids = np.ascontiguousarray(ids, np.int32)
     dout = np.ascontiguousarray(dout, np.float32)

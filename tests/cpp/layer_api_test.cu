@@ -1,7 +1,7 @@
 // Exercises the C++ layer classes (dl_cuda_b200/src/*.cuh) the way the reference's
 // own tests/gpu_correctness_tests.cu drives its classes.  Usage:
 //   layer_api_test known_answer | roundtrip | chain
-//   layer_api_test checkpoint <path> <seed> <vocab> <dim> <tokens>
+//   layer_api_test checkpoint <path> <seed> <vocab> <dim> <tokens> <layers built before>
 // Exit code 0 = pass.
 #include <cmath>
 #include <cstdio>
@@ -67,8 +67,11 @@ int known_answer() {
   return same(got, want) && same(grad, grad_want) ? 0 : 1;
 }
 
-int checkpoint(const char *path, unsigned long long seed, int vocab, int dim, int tokens) {
+// The n-th layer built in a process draws its weights from seed + 9973*n, so a process that has
+// already built `built_before` layers is imitated by consuming that many seeds first.
+int checkpoint(const char *path, unsigned long long seed, int vocab, int dim, int tokens, int built_before) {
   set_global_init_seed(seed);
+  for (int i = 0; i < built_before; i++) (void)next_init_seed();
   EmbeddingLayer layer(vocab, dim, tokens);
   Sequential model;
   model.add(&layer);
@@ -154,8 +157,8 @@ int main(int argc, char **argv) {
   if (mode == "known_answer") rc = known_answer();
   else if (mode == "roundtrip") rc = roundtrip();
   else if (mode == "chain") rc = chain();
-  else if (mode == "checkpoint" && argc == 7)
-    rc = checkpoint(argv[2], strtoull(argv[3], nullptr, 10), atoi(argv[4]), atoi(argv[5]), atoi(argv[6]));
+  else if (mode == "checkpoint" && argc == 8)
+    rc = checkpoint(argv[2], strtoull(argv[3], nullptr, 10), atoi(argv[4]), atoi(argv[5]), atoi(argv[6]), atoi(argv[7]));
   CUDA_CHECK(cudaDeviceSynchronize());
   printf("%s: %s\n", mode.c_str(), rc == 0 ? "PASS" : "FAIL");
   return rc;

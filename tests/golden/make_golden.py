@@ -98,7 +98,7 @@ def main():
     ids = np.array([1, 3, 1, 4], np.int32)
     dout = np.repeat(np.arange(1, 5, dtype=np.float32)[:, None], 3, axis=1)
     o, gr = ref.embedding_layer_run(table, ids, dout)
-    init = ref.embedding_init(3, 5, 3, 4)
+    init = ref.embedding_init(3, 5, 3, 4)  # the second layer this process builds: seed 3 + 9973*2
     np.savez_compressed(out / "embedding_layer_known_answer.npz", table=table, ids=ids, dout=dout, out=o, grad=gr,
                         curand_table_seed3=init)
     sgd_p = rng(41).standard_normal(257).astype(np.float32)

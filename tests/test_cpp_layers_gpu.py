@@ -28,18 +28,20 @@ def test_layer_classes(mode):
 
 def test_checkpoint_bytes_and_curand_init_match_the_reference(tmp_path):
     mine = tmp_path / "mine.bin"
-    run("checkpoint", mine, 3, 5, 3, 4)
+    run("checkpoint", mine, 3, 5, 3, 4, 1)
     data = mine.read_bytes()
     assert data[:4] == b"DLCU" and len(data) == 4 + 4 + 4 + 4 + 15 * 4
     header = np.frombuffer(data[4:16], np.int32)
     assert list(header) == [1, 1, 15]
     table = np.frombuffer(data[16:], np.float32).reshape(5, 3)
-    # the cuRAND-initialised table the reference's EmbeddingLayer holds after set_global_init_seed(3)
+    # the cuRAND-initialised table of the SECOND reference layer built after set_global_init_seed(3)
+    # (make_golden.py builds one layer before it)
     golden = np.load(ROOT / "tests" / "golden" / "embedding_layer_known_answer.npz")["curand_table_seed3"]
     assert np.array_equal(table.view(np.uint32), golden.view(np.uint32))
     if refshim.available():
         theirs = tmp_path / "theirs.bin"
+        built_before = refshim.layers_built
         refshim.embedding_init(12345, 65, 64, 2048, theirs)
         mine2 = tmp_path / "mine2.bin"
-        run("checkpoint", mine2, 12345, 65, 64, 2048)
+        run("checkpoint", mine2, 12345, 65, 64, 2048, built_before)
         assert mine2.read_bytes() == theirs.read_bytes()

@@ -176,3 +176,20 @@ def test_residual_add_bit_exact():
         assert bits_equal(got, oracle.residual_add(a, b))
         if refshim.available():
             assert bits_equal(got, refshim.residual_add(dev(a), dev(b)).cpu().numpy())
+
+
+def test_plan_and_scatter_back_to_back_without_host_syncs():
+    """Plan build, scatter-add and the next batch's upload queued back to back on one stream,
+    several batches in a row, with nothing but stream order between them."""
+    vocab, d, n = 300, 64, 65536
+    want = None
+    for rep in range(6):
+        ids = zipf_ids(rng_for(21, 0), n, vocab)
+        dy = rng_for(21, 1).standard_normal((n, d)).astype(np.float32)
+        tids, tdy = dev(ids), dev(dy)
+        ws = ops.embed_sort_tokens(tids, vocab, d)
+        grad = ops.embed_scatter_bwd(tdy, tids, vocab, ws)
+        got = grad.cpu().numpy()
+        if want is None:
+            want = oracle.embed_scatter(dy, ids, vocab, "segmented")
+        assert bits_equal(got, want), f"batch {rep}"
