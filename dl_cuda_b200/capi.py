@@ -28,6 +28,8 @@ SIGNATURES = {
     "dlb_ln_residual_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _p]),
     "dlb_ln_bwd_workspace_bytes": (_sz, [_i, _i]),
     "dlb_ln_bwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _p]),
+    "dlb_ln_bwd_noalloc_max_bytes": (_sz, []),
+    "dlb_ln_bwd_noalloc": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "dlb_pe_build_table_host": (_i, [_p, _i, _i]),
     "dlb_pe_add_fwd": (_i, [_p, _p, _p, _i, _i, _i, _i, _p]),
     "dlb_pe_add_bwd": (_i, [_p, _p, _i64, _i, _p]),

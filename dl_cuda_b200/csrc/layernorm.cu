@@ -559,3 +559,52 @@ extern "C" int dlb_ln_bwd(const void *dy_a, const void *dy_b, const void *xhat,
   set_error("ln_bwd: unknown dtype %d", dtype);
   return DLB_ERR_INVALID_ARG;
 }
+
+// ---------------------------------------------------------------------------
+// Layer-norm backward for callers that cannot allocate device memory.
+//
+// Some hosts of this library are handed buffers by someone else and must not
+// call cudaMalloc themselves: a plugin that runs inside another framework's
+// memory pool, code on a latency-critical path where an allocation may stall or
+// fail, a process whose memory budget is fixed at start-up.  dlb_ln_bwd() needs
+// a workspace from its caller; this variant brings its own.  The workspace is a
+// fixed array in the library's device image, so every GPU that loads the
+// library holds kNoAllocScratchBytes for the life of the process.
+constexpr size_t kNoAllocScratchBytes = 16u << 20;  // 16 MiB
+static __device__ __align__(256) unsigned char g_ln_bwd_scratch[kNoAllocScratchBytes];
+
+namespace {
+// g_ln_bwd_scratch is a host-side stand-in for the array, not an address a
+// kernel can use: the device address is asked for once per device, with that
+// device current, and cached.
+void *noalloc_scratch_address() {
+  constexpr int kMaxDev = 64;
+  static std::atomic<void *> cached[kMaxDev];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  void *p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    if (cudaGetSymbolAddress(&p, g_ln_bwd_scratch) != cudaSuccess || p == nullptr) return nullptr;
+    cached[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
+}  // namespace
+
+extern "C" size_t dlb_ln_bwd_noalloc_max_bytes(void) { return kNoAllocScratchBytes; }
+
+extern "C" int dlb_ln_bwd_noalloc(const void *dy_a, const void *dy_b, const void *xhat,
+                                  const float *inv_std, const float *gamma, void *dx, float *dgamma,
+                                  float *dbeta, int rows, int d, int dtype, void *stream) {
+  DLB_REQUIRE(rows >= 0 && d > 0, DLB_ERR_INVALID_ARG, "ln_bwd_noalloc: rows=%d d=%d", rows, d);
+  const size_t need = dlb_ln_bwd_workspace_bytes(rows, d);
+  DLB_REQUIRE(need <= kNoAllocScratchBytes, DLB_ERR_UNSUPPORTED,
+              "ln_bwd_noalloc: rows=%d d=%d needs %zu bytes of scratch, the built-in array holds %zu "
+              "(use dlb_ln_bwd with a caller-provided workspace)",
+              rows, d, need, kNoAllocScratchBytes);
+  void *scratch = noalloc_scratch_address();
+  DLB_REQUIRE(scratch != nullptr, DLB_ERR_CUDA, "ln_bwd_noalloc: cudaGetSymbolAddress failed: %s",
+              cudaGetErrorString(cudaGetLastError()));
+  return dlb_ln_bwd(dy_a, dy_b, xhat, inv_std, gamma, dx, dgamma, dbeta, scratch, kNoAllocScratchBytes,
+                    rows, d, dtype, stream);
+}

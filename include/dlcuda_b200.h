@@ -104,6 +104,28 @@ DLB_API int dlb_ln_bwd(const void *dy_a, const void *dy_b, const void *xhat,
                        size_t workspace_bytes, int rows, int d, int dtype,
                        void *stream);
 
+/* Layer-norm backward for callers that cannot allocate: same arguments and
+ * results as dlb_ln_bwd, minus the workspace.  It is meant for hosts that are
+ * handed their buffers by someone else and must not call cudaMalloc themselves
+ * (a plugin inside another framework's memory pool, a latency-critical path, a
+ * process with a memory budget fixed at start-up).  The scratch is a 16 MiB
+ * array inside the library's device image (dlb_ln_bwd_noalloc_max_bytes()):
+ * every GPU that loads the library holds it until the process exits.  Shapes
+ * whose dlb_ln_bwd_workspace_bytes(rows, d) exceeds it (d > 2048 for up to
+ * 262144 rows) are refused with DLB_ERR_UNSUPPORTED.  The call itself makes no
+ * allocation of any kind.  The first call on a device looks up the array's
+ * device address (cudaGetSymbolAddress) and caches it: make that first call
+ * before any stream capture.  All calls share the one array and it keeps the
+ * last call's contents; nothing in it has to start at zero (every partial row
+ * is written before it is read), but two calls that overlap on the GPU (two
+ * streams, two host threads) race on it -- order them.
+ * This entry point has no counterpart in the reference. */
+DLB_API size_t dlb_ln_bwd_noalloc_max_bytes(void);
+DLB_API int dlb_ln_bwd_noalloc(const void *dy_a, const void *dy_b, const void *xhat,
+                               const float *inv_std, const float *gamma, void *dx,
+                               float *dgamma, float *dbeta, int rows, int d,
+                               int dtype, void *stream);
+
 /* ---- sinusoidal positional encoding --------------------------------------
  * h_table[pos*d + i] = (i even ? sinf : cosf)(pos / powf(10000, 2*(i/2)/d)),
  * built on the HOST with the C library's float functions, exactly as
