@@ -491,6 +491,61 @@ def kernel_sweep(peak):
     return out
 
 
+# --------------------------------------------------------------------------- small cases for ncu
+def profile_case(name):
+    """One kernel on a case sized for an ncu capture (inputs above L2, well under 2 GB held),
+    three calls.  `python bench.py --case NAME`; NAME is one of PROFILE_CASES."""
+    from dl_cuda_b200 import capi, ops
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    randn = lambda *s: torch.randn(*s, generator=g, device=dev)
+    kind, storage = name.rsplit("_", 1)
+    dt = torch.bfloat16 if storage == "bf16" else torch.float32
+    if kind in ("ln_fwd", "ln_bwd", "ln_bwd2"):
+        R, D = (16384, 4096) if storage == "bf16" else (32768, 1024)
+        a, b, dy = randn(R, D).to(dt), randn(R, D).to(dt), randn(R, D).to(dt)
+        gamma, beta = torch.rand(D, generator=g, device=dev) + 0.5, randn(D) * 0.1
+        y, xhat, inv = torch.empty_like(a), torch.empty_like(a), torch.empty(R, device=dev)
+        dx, dg, db = torch.empty_like(a), torch.empty(D, device=dev), torch.empty(D, device=dev)
+        ws = ops.ln_bwd_workspace(R, D, dev)
+        ops.ln_residual_fwd(a, b, gamma, beta, 1e-5, y=y, xhat=xhat, inv_std=inv)
+        for _ in range(3):
+            if kind == "ln_fwd":
+                ops.ln_residual_fwd(a, b, gamma, beta, 1e-5, y=y, xhat=xhat, inv_std=inv)
+            else:
+                ops.ln_bwd(dy, b if kind == "ln_bwd2" else None, xhat, inv, gamma, dx=dx, dgamma=dg, dbeta=db,
+                           workspace=ws)
+    elif kind in ("relu", "tanh"):
+        R, C = 8192, 16384
+        k = capi.RELU if kind == "relu" else capi.TANH
+        x, dy, bias = (randn(R, C) * 2).to(dt), randn(R, C).to(dt), randn(C) * 0.1
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        cache, dbias = ops.act_cache(k, x), torch.empty(C, device=dev)
+        ws = ops.act_bwd_workspace(k, R, C, dev)
+        for _ in range(3):
+            ops.act_fwd(k, x, bias, y=y, cache=cache)
+            ops.act_bwd(k, dy, cache, dx=dx, dbias=dbias, want_dbias=True, workspace=ws)
+    elif kind == "embed":
+        V, D, T, S = 32000, 4096, 32768, 2048
+        table = (randn(V, D) * 0.02).to(dt)
+        ids = torch.from_numpy(zipf_ids(np.random.Generator(np.random.Philox(key=5)), T, V)).to(dev)
+        pe, out, dy = ops.pe_table(S, D).to(dev), torch.empty(T, D, device=dev, dtype=dt), randn(T, D).to(dt)
+        grad, ws = torch.empty(V, D, device=dev), ops.embed_workspace(T, V, D, dev)
+        for _ in range(3):
+            ops.embed_gather_fwd(table, ids, pe, S, out=out)
+            ops.embed_sort_tokens(ids, V, D, workspace=ws)
+            ops.embed_scatter_bwd(dy, ids, V, ws, grad=grad)
+    else:
+        raise SystemExit(f"unknown case {name}; choose from {PROFILE_CASES}")
+    torch.cuda.synchronize()
+    print(json.dumps({"case": name, "launches": int(capi.lib().dlb_launch_count()),
+                      "pipeline_timeouts": capi.pipeline_timeouts()}))
+
+
+PROFILE_CASES = [f"{k}_{s}" for k in ("ln_fwd", "ln_bwd", "ln_bwd2", "relu", "tanh", "embed") for s in ("fp32", "bf16")]
+
+
 # --------------------------------------------------------------------------- main
 def run_timed(step, dist: Dist, steps, warmup):
     for _ in range(warmup):
@@ -515,8 +570,11 @@ def main():
     ap.add_argument("--tokens", type=int, default=BATCH * SEQ, help="global token rows (default: batch 8 x seq 4096)")
     ap.add_argument("--skip-kernels", action="store_true", help="skip the per-kernel fp32 sweep")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the host baseline")
+    ap.add_argument("--case", default=None, help="run one small kernel case (for ncu) and exit: " + ", ".join(PROFILE_CASES))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.case:
+        return profile_case(args.case)
 
     dist = Dist()
     if dist.world != args.gpus and dist.world > 1:
