@@ -351,7 +351,7 @@ __device__ __forceinline__ void sum_tokens(const T *__restrict__ dy, Tok tok, in
 #pragma unroll
     for (int q = 0; q < E; q++) acc[k][q] = 0.f;
   // UNR token rows in flight per step; the additions stay in token order.
-  constexpr int UNR = KV >= 4 ? 2 : 4;
+  constexpr int UNR = KV >= 2 ? 2 : 4;
   int j = b;
   for (; j + UNR <= e; j += UNR) {
     uint4 v[UNR][KV];
@@ -679,7 +679,7 @@ int scatter_typed(const Plan &p, const void *dy, float *grad, int vocab, int d, 
   else if (need >= 2) rc = launch_scatter<T, 2>(p, dy, perm, grad, vocab, d, bs, st);
   else rc = launch_scatter<T, 1>(p, dy, perm, grad, vocab, d, bs, st);
   if (rc != DLB_OK) return rc;
-  const int grid = 2 * sm_count();
+  const int grid = 8 * sm_count();  // 8 CTAs fit an SM; each loops over (long row, column block) items
   launch_pdl(combine_long_kernel, grid, kBlock, 0, st, p.scratch, p.long_row, p.long_first, p.meta, grad, d);
   DLB_LAUNCH_CHECK("combine_long");
   return DLB_OK;
