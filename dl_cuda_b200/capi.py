@@ -37,6 +37,10 @@ SIGNATURES = {
     "dlb_embed_workspace_bytes": (_sz, [_i, _i, _i]),
     "dlb_embed_sort_tokens": (_i, [_p, _p, _sz, _i, _i, _i, _p]),
     "dlb_embed_scatter_bwd": (_i, [_p, _p, _p, _p, _sz, _i, _i, _i, _i, _p]),
+    "dlb_embed_compact_workspace_bytes": (_sz, [_i]),
+    "dlb_embed_compact_plan": (_i, [_p, _i, _p, _i, _p, _sz, _i, _i, _p]),
+    "dlb_embed_scatter_bwd_compact": (_i, [_p, _p, _sz, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "dlb_embed_expand_rows": (_i, [_p, _p, _p, _i, _i, _i, _p]),
     "dlb_act_cache_bytes": (_sz, [_i, _i64, _i]),
     "dlb_act_fwd": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _i, _p]),
     "dlb_act_bwd_workspace_bytes": (_sz, [_i, _i64, _i64]),

@@ -430,11 +430,12 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
                     const int32_t *__restrict__ seg_start, const int32_t *__restrict__ long_row,
                     const int32_t *__restrict__ long_first, const int32_t *__restrict__ meta,
                     float *__restrict__ grad, float *__restrict__ scratch, int vocab, int d,
-                    int sub_groups) {
+                    int sub_groups, const int32_t *__restrict__ row_begin,
+                    const int32_t *__restrict__ row_end) {
   pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
-  __shared__ int s_seg[kBlock + 1];
+  __shared__ int s_b[kBlock], s_e[kBlock];
   __shared__ int s_perm[kScatterPermCap];
   const int tx = blockDim.x, ty = blockDim.y;
   const int ncv = d / E;
@@ -458,12 +459,19 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
   }
   const int rows_cta = ty > kScatterRowsPerCta ? ty : kScatterRowsPerCta;
   const int v_first = (blockIdx.x - sub_groups) * rows_cta;
+  // Output row r takes the sorted tokens [begin, end).  Dense mode: r is the table row and the
+  // range is seg_start[r], seg_start[r+1].  Compact mode (row_begin given): r is a slot of the
+  // compacted row list, `vocab` is the number of slots, and the ranges come from row_begin/end.
   const int nrows = min(rows_cta, vocab - v_first);
   const int tid = threadIdx.y * tx + threadIdx.x;
-  for (int i = tid; i <= nrows; i += kBlock) s_seg[i] = __ldg(seg_start + v_first + i);
+  const bool compact = row_begin != nullptr;
+  for (int i = tid; i < nrows; i += kBlock) {
+    s_b[i] = compact ? __ldg(row_begin + v_first + i) : __ldg(seg_start + v_first + i);
+    s_e[i] = compact ? __ldg(row_end + v_first + i) : __ldg(seg_start + v_first + i + 1);
+  }
   __syncthreads();
-  const int p0 = s_seg[0], np = s_seg[nrows] - p0;
-  const bool staged = np <= kScatterPermCap;
+  const int p0 = s_b[0], np = s_e[nrows - 1] - p0;
+  const bool staged = !compact && np <= kScatterPermCap;
   if (staged)
     for (int i = tid; i < np; i += kBlock) s_perm[i] = __ldg(perm + p0 + i);
   __syncthreads();
@@ -480,7 +488,7 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
       const int rl = rl0 + u * ty;
       state[u] = -1;
       if (rl < nrows) {
-        const int b = s_seg[rl], cnt = s_seg[rl + 1] - b;
+        const int b = s_b[rl], cnt = s_e[rl] - b;
         if (cnt <= 1) state[u] = cnt;
         if (cnt == 1) {
           const int t = staged ? s_perm[b - p0] : __ldg(perm + b);
@@ -512,7 +520,7 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
   }
   // Rows with 2..kSubLen tokens.
   for (int rl = threadIdx.y; rl < nrows; rl += ty) {
-    const int b = s_seg[rl], e = s_seg[rl + 1];
+    const int b = s_b[rl], e = s_e[rl];
     if (e - b < 2 || e - b > kSubLen) continue;  // long rows are written by combine_long_kernel
     if (staged)
       sum_tokens<T, KV>(dy, [&](int j) { return s_perm[j - p0]; }, b, e, d, cv0, tx, ncv, acc);
@@ -533,7 +541,7 @@ static_assert(kCombineSlices * 32 == kBlock, "one warp per slice");
 __global__ void __launch_bounds__(kBlock)
 combine_long_kernel(const float *__restrict__ scratch, const int32_t *__restrict__ long_row,
                     const int32_t *__restrict__ long_first, const int32_t *__restrict__ meta,
-                    float *__restrict__ grad, int d) {
+                    float *__restrict__ grad, int d, const int32_t *__restrict__ slot_map) {
   pdl_prologue();
   __shared__ float4 part[kCombineSlices][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -563,7 +571,9 @@ combine_long_kernel(const float *__restrict__ scratch, const int32_t *__restrict
         const float4 p = part[k][lane];
         r.x += p.x; r.y += p.y; r.z += p.z; r.w += p.w;
       }
-      __stcs(reinterpret_cast<float4 *>(grad + static_cast<size_t>(long_row[li]) * d + c), r);
+      const int v = long_row[li];
+      const int out_row = slot_map != nullptr ? slot_map[v] : v;  // compact mode: the row's slot
+      __stcs(reinterpret_cast<float4 *>(grad + static_cast<size_t>(out_row) * d + c), r);
     }
   }
 }
@@ -642,45 +652,140 @@ int gather_typed(const void *table, const int32_t *ids, const float *pe, int seq
   return DLB_OK;
 }
 
+// Where the rows of a multi-GPU (compacted) scatter go: the table rows some rank refers to
+// ("used" rows) are numbered 0..used-1 in ascending id; everything lives in one workspace.
+struct Compact {
+  int32_t *header;     // [4]   {used rows, -, -, -}
+  int32_t *slot_map;   // [V]   slot of a table row, -1 if no rank refers to it
+  int32_t *used_rows;  // [V]   table row of a slot (first `used` entries)
+  int32_t *row_begin;  // [V]   this rank's sorted-token range of a slot
+  int32_t *row_end;    // [V]
+  size_t bytes;
+};
+
+Compact make_compact(void *workspace, int vocab) {
+  Compact c{};
+  char *base = static_cast<char *>(workspace);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    char *ptr = base ? base + off : nullptr;
+    off += align_up(bytes);
+    return reinterpret_cast<int32_t *>(ptr);
+  };
+  const size_t per = sizeof(int32_t) * static_cast<size_t>(vocab);
+  c.header = take(sizeof(int32_t) * 4);
+  c.slot_map = take(per);
+  c.used_rows = take(per);
+  c.row_begin = take(per);
+  c.row_end = take(per);
+  c.bytes = off;
+  return c;
+}
+
+// One CTA: walks the table rows in order, 1024 at a time; a row is used if the GLOBAL plan
+// (the tokens of every rank) has a token for it.  Emits the slot numbering and, per slot, the
+// LOCAL plan's token range.
+__global__ void __launch_bounds__(1024)
+compact_rows_kernel(const int32_t *__restrict__ seg_global, const int32_t *__restrict__ seg_local, int vocab,
+                    Compact c) {
+  pdl_prologue();
+  __shared__ int tmp[33];
+  int base = 0;
+  for (int v0 = 0; v0 < vocab; v0 += 1024) {
+    const int v = v0 + threadIdx.x;
+    const int used = (v < vocab && seg_global[v + 1] > seg_global[v]) ? 1 : 0;
+    int total;
+    const int off = cta_exclusive_scan(used, 1024, tmp, &total);
+    if (v < vocab) {
+      c.slot_map[v] = used ? base + off : -1;
+      if (used) {
+        c.used_rows[base + off] = v;
+        c.row_begin[base + off] = seg_local[v];
+        c.row_end[base + off] = seg_local[v + 1];
+      }
+    }
+    base += total;
+  }
+  if (threadIdx.x == 0) c.header[0] = base;
+}
+
+// grad[v,:] = 0 for rows no rank refers to (what & 1); grad[v,:] = compact[slot_map[v],:] for the
+// others (what & 2).  blockDim = (tx, ty): ty rows per step, tx float4 column vectors.
+__global__ void __launch_bounds__(kBlock)
+expand_rows_kernel(const float *__restrict__ compact, const int32_t *__restrict__ slot_map,
+                   float *__restrict__ grad, int vocab, int d, int what, int rows_per_cta) {
+  pdl_prologue();
+  const int nvec = d / 4;
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int r1 = min(vocab, r0 + rows_per_cta);
+  for (int v = r0 + threadIdx.y; v < r1; v += blockDim.y) {
+    const int slot = __ldg(slot_map + v);
+    if (slot < 0 ? !(what & 1) : !(what & 2)) continue;
+    float4 *dst = reinterpret_cast<float4 *>(grad + static_cast<size_t>(v) * d);
+    const float4 *src = reinterpret_cast<const float4 *>(compact + static_cast<size_t>(max(slot, 0)) * d);
+    for (int c0 = threadIdx.x; c0 < nvec; c0 += 4 * blockDim.x) {
+      float4 val[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int c = c0 + u * blockDim.x;
+        val[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (slot >= 0 && c < nvec) val[u] = __ldcs(src + c);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int c = c0 + u * blockDim.x;
+        if (c < nvec) __stcs(dst + c, val[u]);
+      }
+    }
+  }
+}
+
 template <typename T, int KV>
-int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *grad, int vocab, int d,
-                   BlockShape bs, cudaStream_t st) {
+int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *grad, int out_rows, int d,
+                   BlockShape bs, const Compact *compact, cudaStream_t st) {
   constexpr int E = Store<T>::kPerVec;
   const int ncv = d / E;
   // Sub-segment groups loop over the sub-segments, so a few hundred CTAs cover any count.
   const int sub_groups = min(ceil_div(p.max_sub, bs.ty), 4 * sm_count());
-  const int row_groups = ceil_div(vocab, bs.ty > kScatterRowsPerCta ? bs.ty : kScatterRowsPerCta);
+  const int row_groups = ceil_div(out_rows, bs.ty > kScatterRowsPerCta ? bs.ty : kScatterRowsPerCta);
   dim3 grid(sub_groups + row_groups, ceil_div(ncv, bs.tx * KV));
-  launch_pdl(scatter_rows_kernel<T, KV>, grid, dim3(bs.tx, bs.ty), 0, st, 
-      static_cast<const T *>(dy), perm, p.seg_start, p.long_row, p.long_first, p.meta, grad,
-      p.scratch, vocab, d, sub_groups);
+  launch_pdl(scatter_rows_kernel<T, KV>, grid, dim3(bs.tx, bs.ty), 0, st,
+             static_cast<const T *>(dy), perm, p.seg_start, p.long_row, p.long_first, p.meta, grad, p.scratch,
+             out_rows, d, sub_groups, compact ? compact->row_begin : nullptr,
+             compact ? compact->row_end : nullptr);
   DLB_LAUNCH_CHECK("scatter_rows");
   return DLB_OK;
 }
 
+// out_rows: table rows (dense) or used rows (compact: `grad` is then the [used, d] buffer).
 template <typename T>
-int scatter_typed(const Plan &p, const void *dy, float *grad, int vocab, int d, cudaStream_t st) {
+int scatter_typed(const Plan &p, const void *dy, float *grad, int out_rows, int d, const Compact *compact,
+                  cudaStream_t st) {
   constexpr int E = Store<T>::kPerVec;
   const int32_t *perm = p.vals[p.passes & 1];
   // bf16 input: rows of grad and scratch are written 32 bytes at a time (d % 8 == 0 makes row starts 32-byte aligned).
   const bool vec = d % E == 0 && aligned16(dy) && (E == 8 ? aligned32(grad) : aligned16(grad));
   if (!vec) {
-    const int64_t total = static_cast<int64_t>(vocab) * d;
-    launch_pdl(scatter_scalar_kernel<T>, static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st, 
-        static_cast<const T *>(dy), perm, p.seg_start, grad, vocab, d);
+    DLB_REQUIRE(compact == nullptr, DLB_ERR_UNSUPPORTED,
+                "embed_scatter_bwd_compact: d must be a multiple of %d and the buffers 32-byte aligned", E);
+    const int64_t total = static_cast<int64_t>(out_rows) * d;
+    launch_pdl(scatter_scalar_kernel<T>, static_cast<unsigned>(ceil_div<int64_t>(total, kBlock)), kBlock, 0, st,
+               static_cast<const T *>(dy), perm, p.seg_start, grad, out_rows, d);
     DLB_LAUNCH_CHECK("scatter_scalar");
     return DLB_OK;
   }
+  if (out_rows == 0) return DLB_OK;
   const int ncv = d / E;
   const BlockShape bs = shape_for(ncv);
   const int need = ceil_div(ncv, bs.tx);
   int rc;
-  if (need >= 4) rc = launch_scatter<T, 4>(p, dy, perm, grad, vocab, d, bs, st);
-  else if (need >= 2) rc = launch_scatter<T, 2>(p, dy, perm, grad, vocab, d, bs, st);
-  else rc = launch_scatter<T, 1>(p, dy, perm, grad, vocab, d, bs, st);
+  if (need >= 4) rc = launch_scatter<T, 4>(p, dy, perm, grad, out_rows, d, bs, compact, st);
+  else if (need >= 2) rc = launch_scatter<T, 2>(p, dy, perm, grad, out_rows, d, bs, compact, st);
+  else rc = launch_scatter<T, 1>(p, dy, perm, grad, out_rows, d, bs, compact, st);
   if (rc != DLB_OK) return rc;
   const int grid = 8 * sm_count();  // 8 CTAs fit an SM; each loops over (long row, column block) items
-  launch_pdl(combine_long_kernel, grid, kBlock, 0, st, p.scratch, p.long_row, p.long_first, p.meta, grad, d);
+  launch_pdl(combine_long_kernel, grid, kBlock, 0, st, p.scratch, p.long_row, p.long_first, p.meta, grad, d,
+             compact ? compact->slot_map : nullptr);
   DLB_LAUNCH_CHECK("combine_long");
   return DLB_OK;
 }
@@ -783,9 +888,68 @@ extern "C" int dlb_embed_scatter_bwd(const void *dy, const int32_t *ids, float *
               dlb_embed_workspace_bytes(num_tokens, vocab, d));
   DLB_REQUIRE(dy || num_tokens == 0, DLB_ERR_INVALID_ARG, "embed_scatter_bwd: null dy");
   const Plan p = make_plan(workspace, num_tokens, vocab, d);
-  if (dtype == DLB_F32) return scatter_typed<float>(p, dy, grad, vocab, d, as_stream(stream));
+  if (dtype == DLB_F32) return scatter_typed<float>(p, dy, grad, vocab, d, nullptr, as_stream(stream));
   if (dtype == DLB_BF16)
-    return scatter_typed<__nv_bfloat16>(p, dy, grad, vocab, d, as_stream(stream));
+    return scatter_typed<__nv_bfloat16>(p, dy, grad, vocab, d, nullptr, as_stream(stream));
   set_error("embed_scatter_bwd: unknown dtype %d", dtype);
   return DLB_ERR_INVALID_ARG;
+}
+
+// ---- multi-GPU: compacted table gradient ------------------------------------------------------
+
+extern "C" size_t dlb_embed_compact_workspace_bytes(int vocab) {
+  if (vocab <= 0) return 0;
+  return make_compact(nullptr, vocab).bytes;
+}
+
+extern "C" int dlb_embed_compact_plan(const void *global_plan, int global_tokens, const void *local_plan,
+                                      int local_tokens, void *compact_ws, size_t compact_bytes, int vocab,
+                                      int d, void *stream) {
+  DLB_REQUIRE(embed_args_ok(global_tokens, vocab, d) && embed_args_ok(local_tokens, vocab, d),
+              DLB_ERR_INVALID_ARG, "embed_compact_plan: bad shape");
+  DLB_REQUIRE(global_plan && local_plan && compact_ws && (reinterpret_cast<uintptr_t>(compact_ws) & 255u) == 0 &&
+                  compact_bytes >= dlb_embed_compact_workspace_bytes(vocab),
+              DLB_ERR_WORKSPACE, "embed_compact_plan: plans and a 256-byte aligned workspace of %zu bytes required",
+              dlb_embed_compact_workspace_bytes(vocab));
+  const Plan pg = make_plan(const_cast<void *>(global_plan), global_tokens, vocab, d);
+  const Plan pl = make_plan(const_cast<void *>(local_plan), local_tokens, vocab, d);
+  const Compact c = make_compact(compact_ws, vocab);
+  launch_pdl(compact_rows_kernel, 1, 1024, 0, as_stream(stream), pg.seg_start, pl.seg_start, vocab, c);
+  DLB_LAUNCH_CHECK("compact_rows");
+  return DLB_OK;
+}
+
+extern "C" int dlb_embed_scatter_bwd_compact(const void *dy, void *local_plan, size_t local_plan_bytes,
+                                             const void *compact_ws, float *compact_rows, int used_rows,
+                                             int local_tokens, int vocab, int d, int dtype, void *stream) {
+  DLB_REQUIRE(embed_args_ok(local_tokens, vocab, d) && used_rows >= 0 && used_rows <= vocab, DLB_ERR_INVALID_ARG,
+              "embed_scatter_bwd_compact: tokens=%d vocab=%d d=%d used_rows=%d", local_tokens, vocab, d, used_rows);
+  DLB_REQUIRE(local_plan && compact_ws && local_plan_bytes >= dlb_embed_workspace_bytes(local_tokens, vocab, d),
+              DLB_ERR_WORKSPACE, "embed_scatter_bwd_compact: plan workspaces required");
+  DLB_REQUIRE((compact_rows && (dy || local_tokens == 0)) || used_rows == 0, DLB_ERR_INVALID_ARG,
+              "embed_scatter_bwd_compact: null pointer");
+  const Plan p = make_plan(local_plan, local_tokens, vocab, d);
+  const Compact c = make_compact(const_cast<void *>(compact_ws), vocab);
+  if (dtype == DLB_F32) return scatter_typed<float>(p, dy, compact_rows, used_rows, d, &c, as_stream(stream));
+  if (dtype == DLB_BF16)
+    return scatter_typed<__nv_bfloat16>(p, dy, compact_rows, used_rows, d, &c, as_stream(stream));
+  set_error("embed_scatter_bwd_compact: unknown dtype %d", dtype);
+  return DLB_ERR_INVALID_ARG;
+}
+
+extern "C" int dlb_embed_expand_rows(const float *compact_rows, const void *compact_ws, float *grad, int vocab,
+                                     int d, int what, void *stream) {
+  DLB_REQUIRE(vocab > 0 && d > 0 && d % 4 == 0 && (what & 3) != 0 && (what & ~3) == 0, DLB_ERR_INVALID_ARG,
+              "embed_expand_rows: vocab=%d d=%d (a multiple of 4) what=%d (1 zero, 2 copy, 3 both)", vocab, d, what);
+  DLB_REQUIRE(compact_ws && grad && aligned16(grad) && (!(what & 2) || (compact_rows && aligned16(compact_rows))),
+              DLB_ERR_INVALID_ARG, "embed_expand_rows: null or unaligned pointer");
+  const Compact c = make_compact(const_cast<void *>(compact_ws), vocab);
+  int tx = 1;
+  while (tx < kBlock && tx < d / 4) tx *= 2;
+  const int ty = kBlock / tx;
+  const int rows_per_cta = ty > 8 ? ty : 8;
+  launch_pdl(expand_rows_kernel, ceil_div(vocab, rows_per_cta), dim3(tx, ty), 0, as_stream(stream), compact_rows,
+             c.slot_map, grad, vocab, d, what, rows_per_cta);
+  DLB_LAUNCH_CHECK("expand_rows");
+  return DLB_OK;
 }

@@ -120,6 +120,35 @@ def embed_scatter_bwd(dy, ids, vocab, workspace, grad=None):
     return grad
 
 
+def embed_compact_workspace(vocab, device):
+    return _workspace(capi.lib().dlb_embed_compact_workspace_bytes(vocab), device)
+
+
+def embed_compact_plan(global_plan, global_tokens, local_plan, local_tokens, vocab, d, compact_ws=None, stream=None):
+    """Numbers the table rows any rank uses; compact_ws[:4].view(int32)[0] is their count (device)."""
+    compact_ws = embed_compact_workspace(vocab, global_plan.device) if compact_ws is None else compact_ws
+    check(capi.lib().dlb_embed_compact_plan(ptr(global_plan), global_tokens, ptr(local_plan), local_tokens,
+                                            ptr(compact_ws), compact_ws.numel(), vocab, d,
+                                            current_stream() if stream is None else stream))
+    return compact_ws
+
+
+def embed_scatter_bwd_compact(dy, local_plan, compact_ws, compact_rows, used_rows, vocab, stream=None):
+    _need_cuda(dy, local_plan, compact_ws, compact_rows)
+    n, d = dy.shape
+    check(capi.lib().dlb_embed_scatter_bwd_compact(ptr(dy), ptr(local_plan), local_plan.numel(), ptr(compact_ws),
+                                                   ptr(compact_rows), used_rows, n, vocab, d, dtype_of(dy),
+                                                   current_stream() if stream is None else stream))
+    return compact_rows
+
+
+def embed_expand_rows(compact_rows, compact_ws, grad, what=3, stream=None):
+    vocab, d = grad.shape
+    check(capi.lib().dlb_embed_expand_rows(ptr(compact_rows), ptr(compact_ws), ptr(grad), vocab, d, what,
+                                           current_stream() if stream is None else stream))
+    return grad
+
+
 def act_cache(kind, x):
     return _workspace(capi.lib().dlb_act_cache_bytes(kind, x.numel(), dtype_of(x)), x.device)
 

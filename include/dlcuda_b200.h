@@ -172,6 +172,36 @@ DLB_API int dlb_embed_scatter_bwd(const void *dy, const int32_t *ids,
                                   size_t workspace_bytes, int num_tokens,
                                   int vocab, int d, int dtype, void *stream);
 
+/* Multi-GPU form of the table gradient (token rows sharded over ranks; the reference has
+ * no multi-GPU path, so these have no counterpart there -- they serve the all-reduce of
+ * what src/embedding.cuh:82-92 produces).  Instead of all-reducing the dense [vocab, d]
+ * gradient, every rank numbers the table rows that ANY rank refers to ("used" rows, in
+ * ascending id -- the same numbering on every rank), scatter-adds its own tokens into a
+ * compact [used, d] buffer (zeros for rows only other ranks use), all-reduces that, and
+ * expands it into the dense gradient:
+ *   dlb_embed_sort_tokens on the gathered ids of all ranks  -> global plan
+ *   dlb_embed_sort_tokens on this rank's ids                -> local plan
+ *   dlb_embed_compact_plan(global, local)                   -> compact workspace; its
+ *       first int32 (device memory) is the number of used rows
+ *   dlb_embed_scatter_bwd_compact(dy, local plan, compact)  -> compact_rows [used, d]
+ *   all-reduce compact_rows[0 .. used*d)
+ *   dlb_embed_expand_rows(compact_rows, compact, grad, what): what&1 zero the rows no
+ *       rank uses, what&2 copy the used rows (the zeroing needs only the compact plan,
+ *       so it can run beside the all-reduce).
+ * used_rows passed to the scatter must be the value read from the compact workspace. */
+DLB_API size_t dlb_embed_compact_workspace_bytes(int vocab);
+DLB_API int dlb_embed_compact_plan(const void *global_plan, int global_tokens,
+                                   const void *local_plan, int local_tokens,
+                                   void *compact_ws, size_t compact_bytes, int vocab,
+                                   int d, void *stream);
+DLB_API int dlb_embed_scatter_bwd_compact(const void *dy, void *local_plan,
+                                          size_t local_plan_bytes, const void *compact_ws,
+                                          float *compact_rows, int used_rows,
+                                          int local_tokens, int vocab, int d, int dtype,
+                                          void *stream);
+DLB_API int dlb_embed_expand_rows(const float *compact_rows, const void *compact_ws,
+                                  float *grad, int vocab, int d, int what, void *stream);
+
 /* ---- bias + activation epilogues -------------------------------------------
  * Forward: pre = x + (bias ? bias[col] : 0); y = act(pre) over [rows,cols].
  *   RELU    y = pre>0 ? pre : 0           cache = 1 bit per element (pre>0)

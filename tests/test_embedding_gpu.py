@@ -193,3 +193,41 @@ def test_plan_and_scatter_back_to_back_without_host_syncs():
         if want is None:
             want = oracle.embed_scatter(dy, ids, vocab, "segmented")
         assert bits_equal(got, want), f"batch {rep}"
+
+
+@pytest.mark.parametrize("vocab,d,n,ranks,storage", [(2000, 256, 4096, 2, "fp32"), (32000, 512, 8192, 4, "bf16"),
+                                                     (50, 64, 3000, 3, "fp32"), (300, 4096, 640, 8, "bf16")])
+def test_compacted_multi_rank_gradient(vocab, d, n, ranks, storage):
+    """The multi-GPU form of the table gradient with the ranks emulated on one GPU: each rank
+    scatter-adds its token shard into the compact [used, d] buffer, the buffers are summed
+    (the all-reduce), and the expansion must equal the single-rank dense gradient."""
+    dt = torch.bfloat16 if storage == "bf16" else torch.float32
+    ids = zipf_ids(rng_for(61, 0), n, vocab)
+    dy = dev(rng_for(61, 1).standard_normal((n, d)).astype(np.float32), dt)
+    tids = dev(ids)
+    dense = scatter(dy, tids, vocab)
+    global_plan = ops.embed_sort_tokens(tids, vocab, d)
+    used_host = int(np.unique(ids).size)
+    total = None
+    per = n // ranks
+    compact_ws = None
+    for r in range(ranks):
+        lo, hi = r * per, (n if r == ranks - 1 else (r + 1) * per)
+        ids_r, dy_r = tids[lo:hi].contiguous(), dy[lo:hi].contiguous()
+        local_plan = ops.embed_sort_tokens(ids_r, vocab, d)
+        compact_ws = ops.embed_compact_plan(global_plan, n, local_plan, hi - lo, vocab, d)
+        used = int(compact_ws[:4].view(torch.int32)[0].item())
+        assert used == used_host
+        rows = torch.full((used, d), 9.0, device="cuda")  # stale contents must vanish
+        ops.embed_scatter_bwd_compact(dy_r, local_plan, compact_ws, rows, used, vocab)
+        total = rows if total is None else total + rows
+    grad = torch.full((vocab, d), 5.0, device="cuda")
+    ops.embed_expand_rows(total, compact_ws, grad, what=1)   # zero the unused rows (can overlap the all-reduce)
+    ops.embed_expand_rows(total, compact_ws, grad, what=2)   # then copy the reduced rows
+    assert rel_err(grad.cpu().numpy(), dense.cpu().numpy()) <= 1e-5
+    unused = np.setdiff1d(np.arange(vocab), ids)
+    if unused.size:
+        assert float(grad[torch.from_numpy(unused).cuda()].abs().sum()) == 0.0
+    both = torch.full((vocab, d), 5.0, device="cuda")
+    ops.embed_expand_rows(total, compact_ws, both, what=3)
+    assert torch.equal(both, grad)
