@@ -223,6 +223,14 @@ class Chain:
         self.h_result = torch.empty(4 * D + F, dtype=torch.float32).pin_memory()
         self.side = torch.cuda.Stream()
         self.plan_ready = torch.cuda.Event()
+        self.zero_done = torch.cuda.Event()
+        if dist.active:
+            Tg = T * dist.world
+            self.ids_all = torch.empty(Tg, dtype=torch.int32, device=dev)
+            self.ws_global = ops.embed_workspace(Tg, V, D, dev)
+            self.ws_compact = ops.embed_compact_workspace(V, dev)
+            self.compact_rows = torch.empty(min(V, Tg), D, device=dev)
+            self.h_used = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.distinct_ids = int(np.unique(self.h_ids.numpy()).size)
 
     # algorithmic HBM bytes of each op for the local tokens (each input byte read once,
@@ -239,7 +247,8 @@ class Chain:
             "relu_bwd": T * F * 2 * e + T * F // 8 + F * 4,
             "ln2_bwd": T * D * 3 * e + T * 4 + 3 * D * 4,
             "ln1_bwd": T * D * 4 * e + T * 4 + 3 * D * 4,
-            "embed_scatter": T * D * e + V * D * 4 + T * 4,
+            # N > 1: only the rows used by some rank are written (the dense expansion is timed with the all-reduce)
+            "embed_scatter": T * D * e + (int(self.h_used[0]) if self.dist.active else V) * D * 4 + T * 4,
             "allreduce": 0,
         }
 
@@ -258,15 +267,24 @@ class Chain:
         if copy_inputs:
             self.ids.copy_(self.h_ids, non_blocking=True)
         mark()
+        # The sorted-segment plan depends on the ids alone and is needed only by the last kernel of
+        # backward: in the headline pass it is built on a side stream, beside the forward kernels.
+        plan_stream = self.side if marks is None else torch.cuda.current_stream()
+        pst = plan_stream.cuda_stream
+        if self.dist.active:
+            # every rank needs every rank's ids to number the table rows used anywhere
+            self.dist.dist.all_gather_into_tensor(self.ids_all, self.ids)
         if marks is None:
-            # The sorted-segment plan depends on the ids alone and is needed only by the last
-            # kernel of backward: build it on a side stream, beside the forward kernels.
             self.side.wait_stream(torch.cuda.current_stream())
-            chk(lib.dlb_embed_sort_tokens(p(self.ids), p(self.ws_embed), self.ws_embed.numel(), T, V, D,
-                                          self.side.cuda_stream))
-            self.plan_ready.record(self.side)
-        else:
-            chk(lib.dlb_embed_sort_tokens(p(self.ids), p(self.ws_embed), self.ws_embed.numel(), T, V, D, st))
+        chk(lib.dlb_embed_sort_tokens(p(self.ids), p(self.ws_embed), self.ws_embed.numel(), T, V, D, pst))
+        if self.dist.active:
+            Tg = self.ids_all.numel()
+            chk(lib.dlb_embed_sort_tokens(p(self.ids_all), p(self.ws_global), self.ws_global.numel(), Tg, V, D, pst))
+            chk(lib.dlb_embed_compact_plan(p(self.ws_global), Tg, p(self.ws_embed), T, p(self.ws_compact),
+                                           self.ws_compact.numel(), V, D, pst))
+            with torch.cuda.stream(plan_stream):
+                self.h_used.copy_(self.ws_compact[:4].view(torch.int32)[:1], non_blocking=True)
+        self.plan_ready.record(plan_stream)
         mark()
         chk(lib.dlb_embed_gather_fwd(p(self.table), p(self.ids), p(self.pe), S, p(self.x0), T, V, D, code, st))
         mark()
@@ -289,11 +307,24 @@ class Chain:
         mark()
         if marks is None:
             torch.cuda.current_stream().wait_event(self.plan_ready)
-        chk(lib.dlb_embed_scatter_bwd(p(self.dx1), p(self.ids), p(self.table_grad), p(self.ws_embed),
-                                      self.ws_embed.numel(), T, V, D, code, st))
-        mark()
-        if self.dist.active:
-            allreduce_param_grads(self.dist.dist, self.small_grads, self.table_grad)
+        if not self.dist.active:
+            chk(lib.dlb_embed_scatter_bwd(p(self.dx1), p(self.ids), p(self.table_grad), p(self.ws_embed),
+                                          self.ws_embed.numel(), T, V, D, code, st))
+            mark()
+        else:
+            # Compacted form: only the rows some rank uses are summed, all-reduced and expanded.
+            self.plan_ready.synchronize()  # the row count is a host argument of the calls below
+            used = int(self.h_used[0])
+            chk(lib.dlb_embed_scatter_bwd_compact(p(self.dx1), p(self.ws_embed), self.ws_embed.numel(),
+                                                  p(self.ws_compact), p(self.compact_rows), used, T, V, D, code, st))
+            mark()
+            # zero the unused rows of the dense gradient beside the all-reduce
+            self.side.wait_stream(torch.cuda.current_stream())
+            chk(lib.dlb_embed_expand_rows(None, p(self.ws_compact), p(self.table_grad), V, D, 1, self.side.cuda_stream))
+            self.zero_done.record(self.side)
+            allreduce_param_grads(self.dist.dist, self.small_grads, self.compact_rows[:used])
+            torch.cuda.current_stream().wait_event(self.zero_done)
+            chk(lib.dlb_embed_expand_rows(p(self.compact_rows), p(self.ws_compact), p(self.table_grad), V, D, 2, st))
         mark()
         if copy_inputs:
             self.h_result.copy_(self.small_grads, non_blocking=True)
@@ -491,6 +522,25 @@ def kernel_sweep(peak):
     return out
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch from the ncu captures
+# summarised under profiles/, taken on a quarter-size case (8192 or 16384 rows) and scaled by rows:
+# traffic of these streaming kernels grows in proportion to the rows.  Bytes per token row.
+NCU_TRAFFIC_PER_ROW = {
+    "relu_fwd": (268.517632e6 + 231.812096e6) / 8192,   # profiles/act_relu_kernels_bf16_8192x16384.txt
+    "relu_bwd": (285.612288e6 + 232.156160e6) / 8192,
+    "ln1_fwd": (268.487168e6 + 217.069312e6) / 16384,   # profiles/ln_fwd_kernel_bf16_16384x4096.txt
+    "ln2_fwd": (268.487168e6 + 217.069312e6) / 16384,
+    "ln2_bwd": (268.619264e6 + 98.678528e6) / 16384,    # profiles/ln_bwd_pipe_kernel_bf16_16384x4096.txt
+}
+NCU_TRAFFIC_NOTE = ("ncu dram__bytes_read+write of a quarter-size capture (profiles/*.txt) scaled by rows; writes still "
+                    "in L2 when the kernel ends are not counted by ncu, so it can read below the algorithmic bytes")
+
+
+def ncu_traffic(op, rows):
+    per_row = NCU_TRAFFIC_PER_ROW.get(op)
+    return None if per_row is None else int(per_row * rows)
+
+
 # --------------------------------------------------------------------------- small cases for ncu
 def profile_case(name):
     """One kernel on a case sized for an ncu capture (inputs above L2, well under 2 GB held),
@@ -652,7 +702,9 @@ def main():
         "e2e": e2e, "gpu_launches": int(launches), "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "kernel": dominant["op"], "achieved": dominant["gbs"], "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": dominant["frac"],
-                     "frac_of_nominal_8000": round(dominant["gbs"] / NOMINAL_HBM_GBS, 4), "traffic": None},
+                     "frac_of_nominal_8000": round(dominant["gbs"] / NOMINAL_HBM_GBS, 4),
+                     "algorithmic_bytes": dominant["bytes"],
+                     "traffic": ncu_traffic(dominant["op"], tokens_local), "traffic_source": NCU_TRAFFIC_NOTE},
         "chain_ops": ops_report, "chain_ops_ms_per_step": round(marked_ms, 4),
         "chain_ops_note": "per-op times come from a second pass of the same K steps with a CUDA event after "
                           "every op (ops serialised on one stream); the headline pass has no events and "
