@@ -70,7 +70,9 @@ struct Tiling {
   int64_t rows_per_cta;
 };
 
-Tiling make_tiling(int64_t rows, int64_t ncv) {
+// ctas_per_sm: how many CTAs per SM the grid aims at (more, smaller CTAs stream better; with a bias
+// gradient every CTA row adds a partial row to reduce, so backward aims lower).
+Tiling make_tiling(int64_t rows, int64_t ncv, int ctas_per_sm) {
   Tiling t;
   int tx = 2;  // never 1: fp32 ReLU pairs adjacent lanes to build one mask byte
   while (tx < kBlock && tx < ncv) tx *= 2;
@@ -79,7 +81,7 @@ Tiling make_tiling(int64_t rows, int64_t ncv) {
   const int64_t gx = ceil_div<int64_t>(ncv, tx);
   const int64_t step = static_cast<int64_t>(ty) * kUnroll;
   const int64_t max_gy = ceil_div<int64_t>(rows, step);
-  int64_t gy = ceil_div<int64_t>(static_cast<int64_t>(sm_count()) * 16, gx);
+  int64_t gy = ceil_div<int64_t>(static_cast<int64_t>(sm_count()) * ctas_per_sm, gx);
   if (gy > max_gy) gy = max_gy;
   if (gy > 65535) gy = 65535;
   if (gy < 1) gy = 1;
@@ -325,7 +327,7 @@ constexpr int64_t kFlatCols = 4096;  // virtual row width for tensors without bi
 
 int64_t partial_rows_bound(int64_t rows) {
   // Vector path: gy <= sm*16/gx <= sm*16; scalar path: rows/256.  Bound both.
-  const int64_t a = static_cast<int64_t>(sm_count()) * 16;
+  const int64_t a = static_cast<int64_t>(sm_count()) * 64;
   const int64_t b = ceil_div<int64_t>(rows, kScalarRowsPerChunk);
   return a > b ? a : b;
 }
@@ -350,7 +352,7 @@ int act_fwd_typed(const void *x, const float *bias, void *y, void *cache, int64_
       vc = kFlatCols;
       vr = ceil_div<int64_t>(n, vc);
     }
-    const Tiling t = make_tiling(vr, vc / E);
+    const Tiling t = make_tiling(vr, vc / E, 64);
     if (n + vc * 4 * kBlock < INT32_MAX)
       launch_pdl(act_fwd_kernel<T, KIND, int>, t.grid, t.block, 0, st, static_cast<const T *>(x), bias,
                  static_cast<T *>(y), cache, vr, vc, n, t.rows_per_cta);
@@ -378,7 +380,7 @@ int act_bwd_typed(const void *dy, const void *cache, void *dx, float *dbias, flo
       vc = kFlatCols;
       vr = ceil_div<int64_t>(n, vc);
     }
-    const Tiling t = make_tiling(vr, vc / E);
+    const Tiling t = make_tiling(vr, vc / E, dbias != nullptr ? 32 : 64);
     if (n + vc * 4 * kBlock < INT32_MAX)
       launch_pdl(act_bwd_kernel<T, KIND, int>, t.grid, t.block, 0, st, 
         static_cast<const T *>(dy), cache, static_cast<T *>(dx), dbias ? partial : nullptr, vr, vc,
