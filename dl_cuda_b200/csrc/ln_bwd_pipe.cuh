@@ -23,8 +23,6 @@
 // partial row [2*d]; colsum_finalize adds the partial rows in CTA order.
 #pragma once
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -325,15 +323,6 @@ PipeShape pick_pipe_shape(int rows, int d, bool two_grads, bool aligned) {
   if (kv == 1 && rt < 2) rt = 2;
   int max_stages = kPipeMaxStages;
   int ctas = (kv <= 2 || sizeof(T) == 4) ? 2 : 1;  // all but the widest bf16 variant fit two CTAs per SM in registers
-  if (const char *env = getenv("DLB_LN_BWD_PIPE")) {  // tuning aid: "off" or "rt,stages,ctas"
-    if (env[0] == 'o') return p;
-    int ert = 0, est = 0, ecta = 0;
-    if (sscanf(env, "%d,%d,%d", &ert, &est, &ecta) == 3) {
-      if (ert >= (kv == 1 ? 2 : 1) && ert <= rt_max && (ert & (ert - 1)) == 0) rt = ert;
-      if (est >= 2 && est <= kPipeMaxStages) max_stages = est;
-      if (ecta == 1 || (ecta == 2 && (kv <= 2 || sizeof(T) == 4))) ctas = ecta;
-    }
-  }
   PipeLayout &L = p.layout;
   L.op_bytes = static_cast<unsigned>(static_cast<size_t>(rt) * d * sizeof(T));
   L.stage_bytes = L.op_bytes * (two_grads ? 3 : 2);
