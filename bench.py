@@ -402,7 +402,7 @@ class ReferenceChain:
 
 
 # --------------------------------------------------------------------------- host baseline
-def cpu_baseline(sample_tokens=4096):
+def cpu_baseline(sample_tokens=16384):
     """The chain through the single-threaded host loops of oracle/host_ref.cpp on a slice of
     the tokens (fp32 host arrays; the table gradient is produced at full vocabulary size)."""
     from oracle import cpu
@@ -469,6 +469,29 @@ def kernel_sweep(peak):
         out.append({"kernel": name, "config": cfg, "ms": round(ms, 4), "bytes": int(nbytes),
                     "gbs": round(gbs, 1), "frac_measured": round(gbs / peak, 4),
                     "frac_nominal": round(gbs / NOMINAL_HBM_GBS, 4)})
+
+    # config 1: char-LM shapes (batch 32 x seq 64, d_model 64, vocab 65, FFN 2048 x 256): launch-latency
+    # bound (every tensor fits L2), so the time per call is what matters; GB/s only for information
+    T1, D1, V1, S1, F1 = 2048, 64, 65, 64, 256
+    a1, b1, dy1 = randn(T1, D1), randn(T1, D1), randn(T1, D1)
+    g1, be1 = torch.ones(D1, device=dev), torch.zeros(D1, device=dev)
+    y1, xh1, inv1 = torch.empty_like(a1), torch.empty_like(a1), torch.empty(T1, device=dev)
+    dx1, dg1, db1 = torch.empty_like(a1), torch.empty(D1, device=dev), torch.empty(D1, device=dev)
+    ws1 = ops.ln_bwd_workspace(T1, D1, dev)
+    tab1 = randn(V1, D1) * 0.02
+    ids1 = torch.randint(0, V1, (T1,), generator=g, device=dev, dtype=torch.int32)
+    pe1, out1, grad1 = ops.pe_table(S1, D1).to(dev), torch.empty(T1, D1, device=dev), torch.empty(V1, D1, device=dev)
+    wse1 = ops.embed_workspace(T1, V1, D1, dev)
+    x1, dyf1 = randn(T1, F1), randn(T1, F1)
+    yf1, dxf1, c1 = torch.empty_like(x1), torch.empty_like(x1), ops.act_cache(capi.RELU, x1)
+    cfg1 = "char-LM shapes 2048x64 / V65 / 2048x256 fp32"
+    add("ln_residual_fwd", cfg1, T1 * D1 * 16, time_op(lambda: ops.ln_residual_fwd(a1, b1, g1, be1, 1e-5, y=y1, xhat=xh1, inv_std=inv1), iters=50))
+    add("ln_bwd", cfg1, T1 * D1 * 12, time_op(lambda: ops.ln_bwd(dy1, None, xh1, inv1, g1, dx=dx1, dgamma=dg1, dbeta=db1, workspace=ws1), iters=50))
+    add("embed_gather_pe_fwd", cfg1, T1 * D1 * 8, time_op(lambda: ops.embed_gather_fwd(tab1, ids1, pe1, S1, out=out1), iters=50))
+    add("embed_sort_tokens", cfg1, 0, time_op(lambda: ops.embed_sort_tokens(ids1, V1, D1, workspace=wse1), iters=50))
+    add("embed_scatter_bwd", cfg1, T1 * D1 * 4 + V1 * D1 * 4, time_op(lambda: ops.embed_scatter_bwd(dy1, ids1, V1, wse1, grad=grad1), iters=50))
+    add("relu_fwd", cfg1, T1 * F1 * 8, time_op(lambda: ops.act_fwd(capi.RELU, x1, None, y=yf1, cache=c1), iters=50))
+    add("relu_bwd", cfg1, T1 * F1 * 8, time_op(lambda: ops.act_bwd(capi.RELU, dyf1, c1, dx=dxf1), iters=50))
 
     # config 2: LN + residual, 65536 x 1024
     R, D = 65536, 1024
