@@ -542,6 +542,28 @@ def kernel_sweep(peak):
         add(f"bias_{name}_fwd", "32768x16384 fp32", n * 8 + cache_b + C * 4, ms)
         ms = time_op(lambda: ops.act_bwd(kind, dyy, cache, dx=dxb, dbias=dbias, want_dbias=True, workspace=wsa))
         add(f"{name}_bwd_dbias", "32768x16384 fp32", n * 8 + cache_b + C * 4, ms)
+    del x, dyy, yb, dxb, cache
+
+    # beyond the named path (what comes next): GELU epilogue and the optimizer path on the parameters of
+    # the chain (embedding table 32000x4096 plus the small groups), one launch for all groups
+    R, C = 8192, 16384
+    x, dyy, bias = randn(R, C) * 2.0, randn(R, C), randn(C) * 0.1
+    yb, dxb, cache = torch.empty_like(x), torch.empty_like(x), torch.empty(R * C * 4, dtype=torch.uint8, device=dev)
+    n = R * C
+    ms = time_op(lambda: ops.act_fwd(capi.GELU, x, bias, y=yb, cache=cache))
+    add("bias_gelu_fwd", "8192x16384 fp32", n * 12 + C * 4, ms)
+    ms = time_op(lambda: ops.act_bwd(capi.GELU, dyy, cache, dx=dxb))
+    add("gelu_bwd", "8192x16384 fp32", n * 12, ms)
+    del x, dyy, yb, dxb, cache
+    sizes = [32000 * 4096, 4096, 4096, 4096, 4096, 16384]
+    ps, gs = [randn(k) for k in sizes], [randn(k) for k in sizes]
+    ms_, vs_ = [torch.zeros(k, device=dev) for k in sizes], [torch.zeros(k, device=dev) for k in sizes]
+    total = sum(sizes)
+    ms = time_op(lambda: ops.optim_step(capi.OPT_ADAMW, ps, gs, ms_, vs_, lr=1e-3, step=2))
+    add("adamw_step_all_groups", "131M params in 6 groups fp32", total * 28, ms)
+    res, wsn = torch.empty(3, device=dev), torch.empty(8192, dtype=torch.uint8, device=dev)
+    ms = time_op(lambda: ops.grad_norm_clip(gs, 1e9, result=res, workspace=wsn))
+    add("grad_norm", "131M gradients in 6 groups fp32", total * 4, ms)
     return out
 
 

@@ -200,3 +200,36 @@ def sgd_update(params, grads, lr):
     _need_cuda(params, grads)
     check(capi.lib().dlb_sgd_update(ptr(params), ptr(grads), lr, params.numel(), current_stream()))
     return params
+
+
+def _ptr_array(tensors):
+    import ctypes
+    arr = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() if t is not None else None for t in tensors])
+    return arr
+
+
+def optim_step(kind, params, grads, m=None, v=None, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01,
+               step=1):
+    """One optimizer step over lists of fp32 tensors (parameter groups), in place."""
+    import ctypes
+    n = len(params)
+    sizes = (ctypes.c_int * n)(*[p.numel() for p in params])
+    inv1 = 1.0 / (1.0 - beta1 ** step) if kind in (capi.OPT_ADAM, capi.OPT_ADAMW) else 1.0
+    inv2 = 1.0 / (1.0 - beta2 ** step) if kind in (capi.OPT_ADAM, capi.OPT_ADAMW) else 1.0
+    check(capi.lib().dlb_optim_step(kind, n, _ptr_array(params), _ptr_array(grads),
+                                    _ptr_array(m) if m is not None else None,
+                                    _ptr_array(v) if v is not None else None, sizes, lr, beta1, beta2, eps,
+                                    weight_decay, inv1, inv2, current_stream()))
+
+
+def grad_norm_clip(grads, max_norm=0.0, result=None, workspace=None):
+    """Returns the device tensor {sum of squares, norm, applied scale}; clips in place when max_norm > 0."""
+    import ctypes
+    n = len(grads)
+    device = grads[0].device if n else torch.device("cuda")
+    sizes = (ctypes.c_int * n)(*[g.numel() for g in grads])
+    result = torch.empty(3, dtype=torch.float32, device=device) if result is None else result
+    workspace = _workspace(capi.lib().dlb_grad_norm_workspace_bytes(), device) if workspace is None else workspace
+    check(capi.lib().dlb_grad_norm_clip(n, _ptr_array(grads), sizes, max_norm, ptr(workspace), workspace.numel(),
+                                        ptr(result), current_stream()))
+    return result

@@ -241,6 +241,42 @@ DLB_API int dlb_bias_grad(const void *dy, float *dbias, void *workspace,
 DLB_API int dlb_sgd_update(float *params, const float *grads, float lr,
                            int64_t n, void *stream);
 
+/* ---- optimizer steps and gradient clipping over a list of parameter groups ----
+ * The h_* arrays are HOST arrays of n_groups device pointers / sizes (the
+ * reference's ParamGroup list, src/sequential.cuh:19-23); one launch covers up
+ * to 64 groups.
+ *   DLB_OPT_SGD      p -= lr*g                                   (h_m, h_v unused)
+ *   DLB_OPT_ADAM     m = b1*m+(1-b1)*g; v = b2*v+(1-b2)*g*g;
+ *                    p -= lr * (m*inv_bc1) / (sqrtf(v*inv_bc2)+eps)
+ *   DLB_OPT_ADAMW    ... p -= lr * (m_hat/(sqrtf(v_hat)+eps) + weight_decay*p)
+ *   DLB_OPT_RMSPROP  s = b1*s+(1-b1)*g*g (s in h_m, decay in beta1);
+ *                    p -= lr*g/(sqrtf(s)+eps)
+ * inv_bias_correction{1,2} = 1/(1-beta^t) are computed by the caller, as the
+ * reference's optimizer classes do.
+ * Replaces sgdUpdateKernel (src/layers.cuh:84-90), updateRMSprop / updateAdam /
+ * updateAdamW (src/optimizers.cuh:6-48) and the per-group launch loops of
+ * src/optimizer.cuh:28-33, 78-92, 139-153, 187-195. */
+typedef enum dlb_opt { DLB_OPT_SGD = 0, DLB_OPT_ADAM = 1, DLB_OPT_ADAMW = 2, DLB_OPT_RMSPROP = 3 } dlb_opt;
+DLB_API int dlb_optim_step(int kind, int n_groups, float *const *h_params,
+                           float *const *h_grads, float *const *h_m, float *const *h_v,
+                           const int *h_sizes, float lr, float beta1, float beta2,
+                           float eps, float weight_decay, float inv_bias_correction1,
+                           float inv_bias_correction2, void *stream);
+
+/* Global gradient norm and clipping without a host round trip:
+ *   d_result[0] = sum of g*g over every group (fixed order, reproducible),
+ *   d_result[1] = its square root, d_result[2] = the scale applied,
+ * and, when max_norm > 0 and the norm exceeds it, every gradient is multiplied
+ * by max_norm/(norm + 1e-6f) in place.  d_result is DEVICE memory (3 floats);
+ * the caller reads d_result[1] back only if it wants the number.
+ * Replaces the per-group thrust::transform_reduce + host sum and
+ * clipGradsKernel of Sequential::clip_grad_norm (src/optimizer.cuh:205-233,
+ * src/optimizers.cuh:50-55). */
+DLB_API size_t dlb_grad_norm_workspace_bytes(void);
+DLB_API int dlb_grad_norm_clip(int n_groups, float *const *h_grads, const int *h_sizes,
+                               float max_norm, void *workspace, size_t workspace_bytes,
+                               float *d_result, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

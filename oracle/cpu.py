@@ -157,3 +157,21 @@ def sgd_update(p, g, lr):
     g = _f(g)
     lib().orc_sgd_update(_p(p), _p(g), C.c_float(lr), C.c_int64(p.size))
     return p
+
+
+def optim_step(kind, p, g, m, v, lr, beta1, beta2, eps, weight_decay, step):
+    """kind: 1 adam, 2 adamw, 3 rmsprop.  Returns updated copies (p, m, v)."""
+    p, g, m = _f(p).copy(), _f(g), _f(m).copy()
+    v = _f(v).copy() if v is not None else np.zeros_like(p)
+    inv1 = np.float32(1.0 / (1.0 - beta1 ** step)) if kind != 3 else np.float32(1)
+    inv2 = np.float32(1.0 / (1.0 - beta2 ** step)) if kind != 3 else np.float32(1)
+    lib().orc_optim_step(kind, _p(p), _p(g), _p(m), _p(v), C.c_int64(p.size), C.c_float(lr), C.c_float(beta1),
+                         C.c_float(beta2), C.c_float(eps), C.c_float(weight_decay), C.c_float(inv1), C.c_float(inv2))
+    return p, m, v
+
+
+def sq_norm(g):
+    g = _f(g)
+    fn = lib().orc_sq_norm_f64
+    fn.restype = C.c_double
+    return float(fn(_p(g), C.c_int64(g.size)))

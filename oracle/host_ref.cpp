@@ -290,3 +290,36 @@ void orc_sgd_update(float *p, const float *g, float lr, int64_t n) {
 }
 
 }  // extern "C"
+
+extern "C" {
+
+// updateAdam / updateAdamW (src/optimizers.cuh:16-48), updateRMSprop (:6-14): one element at a
+// time, in place.  kind: 1 adam, 2 adamw, 3 rmsprop (state in m, decay in beta1).  The products
+// that nvcc may or may not fuse are left to the compiler here; tests compare within 1e-6.
+void orc_optim_step(int kind, float *p, const float *g, float *m, float *v, int64_t n, float lr, float beta1,
+                    float beta2, float eps, float weight_decay, float inv_bc1, float inv_bc2) {
+  for (int64_t i = 0; i < n; i++) {
+    if (kind == 3) {
+      m[i] = beta1 * m[i] + (1 - beta1) * g[i] * g[i];
+      p[i] -= lr * g[i] / (sqrtf(m[i]) + eps);
+      continue;
+    }
+    m[i] = beta1 * m[i] + (1.0f - beta1) * g[i];
+    v[i] = beta2 * v[i] + (1.0f - beta2) * g[i] * g[i];
+    const float m_hat = m[i] * inv_bc1;
+    const float v_hat = v[i] * inv_bc2;
+    if (kind == 1)
+      p[i] -= lr * m_hat / (sqrtf(v_hat) + eps);
+    else
+      p[i] -= lr * (m_hat / (sqrtf(v_hat) + eps) + weight_decay * p[i]);
+  }
+}
+
+// Sum of squares as Sequential::clip_grad_norm forms it (src/optimizer.cuh:213-221), in double.
+double orc_sq_norm_f64(const float *g, int64_t n) {
+  double s = 0.0;
+  for (int64_t i = 0; i < n; i++) s += static_cast<double>(g[i]) * static_cast<double>(g[i]);
+  return s;
+}
+
+}  // extern "C"

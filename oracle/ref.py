@@ -42,6 +42,8 @@ _SIGNATURES = {
     "ref_bias_grad": [_P, _P, _I, _I],
     "ref_bias_add": [_P, _P, _P, _I, _I],
     "ref_sgd": [_P, _P, _F, _I],
+    "ref_optim_step": [_I, _P, _P, _P, _P, _I, _F, _F, _F, _F, _F, _F, _F],
+    "ref_clip_grad_norm": [_P, _I, _F, _P],
     "ref_embedding_init": [C.c_uint64, _I, _I, _I, _P, C.c_char_p],
     "ref_embedding_layer_run": [_P, _P, _P, _I, _I, _I, _P, _P],
 }
@@ -200,3 +202,17 @@ def embedding_layer_run(table, ids, dout):
                                          C.c_void_p(out.ctypes.data), C.c_void_p(grad.ctypes.data))
     _ok(code, "embedding_layer_run")
     return out, grad
+
+
+def optim_step(kind, p, g, m, v, lr, beta1, beta2, eps, weight_decay, step):
+    """In place on device tensors; kind 1 adam, 2 adamw, 3 rmsprop."""
+    inv1 = 1.0 / (1.0 - beta1 ** step) if kind != 3 else 1.0
+    inv2 = 1.0 / (1.0 - beta2 ** step) if kind != 3 else 1.0
+    _ok(lib().ref_optim_step(kind, _p(p), _p(g), _p(m), _p(v), _i32(p.numel()), lr, beta1, beta2, eps, weight_decay,
+                             inv1, inv2), "optim_step")
+
+
+def clip_grad_norm(g, max_norm):
+    out = C.c_float(0)
+    _ok(lib().ref_clip_grad_norm(_p(g), _i32(g.numel()), max_norm, C.byref(out)), "clip_grad_norm")
+    return float(out.value)

@@ -190,3 +190,28 @@ SHIM_API int ref_embedding_layer_run(const float *h_table, const int *h_ids, con
   cudaFree(d_out);
   return static_cast<int>(e);
 }
+
+#include "optimizer.cuh"
+
+// src/optimizers.cuh:6-48 launched as the optimizer classes do (src/optimizer.cuh:78-92, 139-153,
+// 187-195).  kind: 1 adam, 2 adamw, 3 rmsprop (state in m, decay in beta1).
+SHIM_API int ref_optim_step(int kind, float *p, float *g, float *m, float *v, int n, float lr, float beta1,
+                            float beta2, float eps, float weight_decay, float inv_bc1, float inv_bc2) {
+  if (kind == 1) updateAdam<<<blocks_for(n), 256>>>(g, m, v, p, lr, beta1, beta2, eps, inv_bc1, inv_bc2, n);
+  else if (kind == 2)
+    updateAdamW<<<blocks_for(n), 256>>>(g, m, v, p, lr, beta1, beta2, eps, weight_decay, inv_bc1, inv_bc2, n);
+  else updateRMSprop<<<blocks_for(n), 256>>>(g, m, p, lr, beta1, eps, n);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The norm and clipping of Sequential::clip_grad_norm (src/optimizer.cuh:205-233) for one gradient
+// buffer: thrust reduction, host sqrt, clipGradsKernel.  Returns the norm through *h_norm.
+SHIM_API int ref_clip_grad_norm(float *g, int n, float max_norm, float *h_norm) {
+  thrust::device_ptr<float> begin(g);
+  const float sq = thrust::transform_reduce(thrust::device, begin, begin + n, SquareOp(), 0.0f,
+                                            cuda::std::plus<float>());
+  const float norm = sqrtf(sq);
+  if (norm > max_norm) clipGradsKernel<<<blocks_for(n), 256>>>(g, max_norm / (norm + 1e-6f), n);
+  *h_norm = norm;
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,6 +1,6 @@
 // Exercises the C++ layer classes (dl_cuda_b200/src/*.cuh) the way the reference's
 // own tests/gpu_correctness_tests.cu drives its classes.  Usage:
-//   layer_api_test known_answer | roundtrip | chain
+//   layer_api_test known_answer | roundtrip | chain | optimizer
 //   layer_api_test checkpoint <path> <seed> <vocab> <dim> <tokens> <layers built before>
 // Exit code 0 = pass.
 #include <cmath>
@@ -12,6 +12,7 @@
 
 #include "activation.cuh"
 #include "embedding.cuh"
+#include "optimizer.cuh"
 #include "positional_encoding.cuh"
 #include "sequential.cuh"
 
@@ -144,6 +145,48 @@ int chain() {
   return 0;
 }
 
+// Sequential::set_optimizer / clip_grad_norm / update_weights with AdamW over two embedding layers,
+// against the same arithmetic on the host (src/optimizers.cuh:32-48, src/optimizer.cuh:205-233).
+int optimizer() {
+  set_global_init_seed(11);
+  EmbeddingLayer e1(9, 8, 4), e2(5, 16, 4);
+  Sequential model;
+  model.add(&e1);
+  model.add(&e2);
+  AdamWOptimizer opt(0.9f, 0.999f, 1e-8f, 0.01f);
+  model.set_optimizer(&opt);
+  std::vector<ParamGroup> groups = {e1.get_param_groups()[0], e2.get_param_groups()[0]};
+  std::vector<std::vector<float>> p, g;
+  double sq = 0.0;
+  for (size_t k = 0; k < groups.size(); k++) {
+    p.push_back(download(groups[k].params, groups[k].size));
+    std::vector<float> grad(groups[k].size);
+    for (int i = 0; i < groups[k].size; i++) grad[i] = 0.5f * static_cast<float>((i * 7 + 3 * (int)k) % 11 - 5);
+    for (float v : grad) sq += static_cast<double>(v) * v;
+    upload(groups[k].grads, grad);
+    g.push_back(grad);
+  }
+  const float max_norm = 1.0f;
+  const float norm = model.clip_grad_norm(max_norm);
+  if (fabs(norm - sqrt(sq)) > 1e-4 * sqrt(sq)) return 1;
+  const float coeff = max_norm / (norm + 1e-6f);
+  const float lr = 0.01f;
+  model.update_weights(lr);
+  const float inv1 = 1.0f / (1.0f - powf(0.9f, 1.0f)), inv2 = 1.0f / (1.0f - powf(0.999f, 1.0f));
+  for (size_t k = 0; k < groups.size(); k++) {
+    const std::vector<float> got = download(groups[k].params, groups[k].size);
+    const std::vector<float> got_g = download(groups[k].grads, groups[k].size);
+    for (int i = 0; i < groups[k].size; i++) {
+      const float gi = g[k][i] * coeff;
+      if (fabsf(got_g[i] - gi) > 1e-6f * fabsf(gi) + 1e-12f) return 1;
+      const float m = 0.1f * gi, v = 0.001f * gi * gi;
+      const float want = p[k][i] - lr * (m * inv1 / (sqrtf(v * inv2) + 1e-8f) + 0.01f * p[k][i]);
+      if (fabsf(got[i] - want) > 1e-5f * fmaxf(1.0f, fabsf(want))) return 1;
+    }
+  }
+  return 0;
+}
+
 }  // namespace
 
 int main(int argc, char **argv) {
@@ -157,6 +200,7 @@ int main(int argc, char **argv) {
   if (mode == "known_answer") rc = known_answer();
   else if (mode == "roundtrip") rc = roundtrip();
   else if (mode == "chain") rc = chain();
+  else if (mode == "optimizer") rc = optimizer();
   else if (mode == "checkpoint" && argc == 8)
     rc = checkpoint(argv[2], strtoull(argv[3], nullptr, 10), atoi(argv[4]), atoi(argv[5]), atoi(argv[6]), atoi(argv[7]));
   CUDA_CHECK(cudaDeviceSynchronize());

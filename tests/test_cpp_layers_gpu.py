@@ -21,7 +21,7 @@ def run(*args):
     assert res.returncode == 0, res.stdout + res.stderr
 
 
-@pytest.mark.parametrize("mode", ["known_answer", "roundtrip", "chain"])
+@pytest.mark.parametrize("mode", ["known_answer", "roundtrip", "chain", "optimizer"])
 def test_layer_classes(mode):
     run(mode)
 
