@@ -78,17 +78,26 @@ CPP_TEST_SRC = PKG_DIR.parent / "tests" / "cpp" / "layer_api_test.cu"
 CPP_TEST_BIN = PKG_DIR.parent / "tests" / "cpp" / "layer_api_test"
 
 
+CPP_MODELS_SRC = PKG_DIR.parent / "tests" / "cpp" / "layer_models.cu"
+CPP_MODELS_LIB = PKG_DIR.parent / "tests" / "cpp" / "libnative_models.so"
+
+
 def build_cpp_tests() -> Path:
-    """Compile the C++ program that drives the layer classes of src/*.cuh against the library."""
+    """Compile the C++ test programs that drive the layer classes of src/*.cuh against the library:
+    the known-answer binary and the shared library of small models (tests/cpp/layer_models.cu)."""
     build()
-    deps = [CPP_TEST_SRC, LIB_PATH] + sorted((PKG_DIR / "src").glob("*.cuh"))
-    if _stale(CPP_TEST_BIN, deps):
-        cmd = [_nvcc(), "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2",
-               f"-I{PKG_DIR / 'src'}", f"-I{PKG_DIR.parent / 'include'}", str(CPP_TEST_SRC), "-o", str(CPP_TEST_BIN),
-               f"-L{PKG_DIR}", "-ldlcuda_b200", "-Xlinker", "-rpath,$ORIGIN/../../dl_cuda_b200"]
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if res.returncode != 0:
-            raise RuntimeError(f"nvcc failed on {CPP_TEST_SRC.name}:\n{res.stderr}")
+    common = ["-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2",
+              f"-I{PKG_DIR / 'src'}", f"-I{PKG_DIR.parent / 'include'}"]
+    link = [f"-L{PKG_DIR}", "-ldlcuda_b200", "-Xlinker", "-rpath,$ORIGIN/../../dl_cuda_b200", "-lcurand"]
+    headers = sorted((PKG_DIR / "src").glob("*.cuh"))
+    jobs = [(CPP_TEST_SRC, CPP_TEST_BIN, []),
+            (CPP_MODELS_SRC, CPP_MODELS_LIB, ["-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden"])]
+    for src, out, extra in jobs:
+        if _stale(out, [src, LIB_PATH] + headers):
+            cmd = [_nvcc(), *common, *extra, str(src), "-o", str(out), *link]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"nvcc failed on {src.name}:\n{res.stderr}")
     return CPP_TEST_BIN
 
 

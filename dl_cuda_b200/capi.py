@@ -14,6 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libdlcuda_b200.so"
 F32, BF16 = 0, 1
 RELU, SIGMOID, TANH, GELU = 0, 1, 2, 3
 OPT_SGD, OPT_ADAM, OPT_ADAMW, OPT_RMSPROP = 0, 1, 2, 3
+LOSS_SQUARED, LOSS_ABSOLUTE, LOSS_BCE, LOSS_CCE = 0, 1, 2, 3
 OK, ERR_INVALID_ARG, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_CUDA, ERR_NO_DEVICE = range(6)
 
 _p, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
@@ -52,6 +53,14 @@ SIGNATURES = {
     "dlb_optim_step": (_i, [_i, _i, _p, _p, _p, _p, _p, _f, _f, _f, _f, _f, _f, _f, _p]),
     "dlb_grad_norm_workspace_bytes": (_sz, []),
     "dlb_grad_norm_clip": (_i, [_i, _p, _p, _f, _p, _sz, _p, _p]),
+    "dlb_gemm_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i, _i,
+                          _i64, _i64, _i64, _i64, _i64, _i64, _f, _i, _p]),
+    "dlb_softmax_fwd": (_i, [_p, _p, _i64, _i, _i, _p]),
+    "dlb_softmax_bwd": (_i, [_p, _p, _p, _i64, _i, _f, _p]),
+    "dlb_loss_fwd": (_i, [_i, _p, _p, _p, _i64, _i, _p]),
+    "dlb_loss_bwd": (_i, [_i, _p, _p, _p, _i64, _i, _p]),
+    "dlb_ce_from_ids_fwd": (_i, [_p, _p, _p, _i, _i, _f, _p]),
+    "dlb_ce_from_ids_bwd": (_i, [_p, _p, _p, _i, _i, _f, _p]),
 }
 
 

@@ -233,3 +233,71 @@ def grad_norm_clip(grads, max_norm=0.0, result=None, workspace=None):
     check(capi.lib().dlb_grad_norm_clip(n, _ptr_array(grads), sizes, max_norm, ptr(workspace), workspace.numel(),
                                         ptr(result), current_stream()))
     return result
+
+
+# --- pass-through dense ops (fp32) --------------------------------------------------
+def gemm(a, b, bias=None, out=None, alpha=1.0, accumulate=False):
+    """out (+)= alpha * a @ b + bias for fp32 tensors [M,K]·[K,N] or batched [Z,M,K]·[Z,K,N].
+
+    ``a`` and ``b`` may be any strided views (transposes included); ``out`` is
+    made contiguous if not given.
+    """
+    batched = a.dim() == 3
+    a3 = a if batched else a.unsqueeze(0)
+    b3 = b if batched else b.unsqueeze(0)
+    z, m, k = a3.shape
+    n = b3.shape[2]
+    assert b3.shape[0] == z and b3.shape[1] == k and a.dtype == torch.float32 and b.dtype == torch.float32
+    if out is None:
+        assert not accumulate
+        out = torch.empty((z, m, n) if batched else (m, n), dtype=torch.float32, device=a.device)
+    o3 = out if batched else out.unsqueeze(0)
+    assert o3.stride(2) == 1 or n == 1
+    check(capi.lib().dlb_gemm_f32(ptr(a3), ptr(b3), ptr(bias) if bias is not None else None, ptr(o3), m, n, k,
+                                  a3.stride(1), a3.stride(2), b3.stride(1), b3.stride(2), o3.stride(1), z, 1,
+                                  a3.stride(0), 0, b3.stride(0), 0, o3.stride(0), 0, alpha, int(accumulate),
+                                  current_stream()))
+    return out
+
+
+def softmax_fwd(x, out=None, causal_period=0):
+    """Row softmax over the last dimension of a contiguous fp32 tensor."""
+    out = torch.empty_like(x) if out is None else out
+    width = x.shape[-1]
+    check(capi.lib().dlb_softmax_fwd(ptr(x), ptr(out), x.numel() // width, width, causal_period, current_stream()))
+    return out
+
+
+def softmax_bwd(dy, s, dx=None, scale=1.0):
+    dx = torch.empty_like(dy) if dx is None else dx
+    width = dy.shape[-1]
+    check(capi.lib().dlb_softmax_bwd(ptr(dy), ptr(s), ptr(dx), dy.numel() // width, width, scale, current_stream()))
+    return dx
+
+
+def loss_fwd(kind, y, y_pred, classes=1):
+    n = y.numel() // classes if kind == capi.LOSS_CCE else y.numel()
+    err = torch.empty(n, dtype=torch.float32, device=y.device)
+    check(capi.lib().dlb_loss_fwd(kind, ptr(y), ptr(y_pred), ptr(err), n, classes, current_stream()))
+    return err
+
+
+def loss_bwd(kind, y, y_pred, classes=1):
+    n = y.numel() // classes if kind == capi.LOSS_CCE else y.numel()
+    grad = torch.empty_like(y_pred)
+    check(capi.lib().dlb_loss_bwd(kind, ptr(y), ptr(y_pred), ptr(grad), n, classes, current_stream()))
+    return grad
+
+
+def ce_from_ids_fwd(target_ids, y_pred, eps=1e-10):
+    n, classes = y_pred.shape
+    err = torch.empty(n, dtype=torch.float32, device=y_pred.device)
+    check(capi.lib().dlb_ce_from_ids_fwd(ptr(target_ids), ptr(y_pred), ptr(err), n, classes, eps, current_stream()))
+    return err
+
+
+def ce_from_ids_bwd(target_ids, y_pred, eps=1e-10):
+    n, classes = y_pred.shape
+    grad = torch.empty_like(y_pred)
+    check(capi.lib().dlb_ce_from_ids_bwd(ptr(target_ids), ptr(y_pred), ptr(grad), n, classes, eps, current_stream()))
+    return grad

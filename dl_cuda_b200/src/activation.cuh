@@ -46,3 +46,29 @@ class GELUActivation : public DlbActivation<DLB_ACT_GELU> {
 public:
   explicit GELUActivation(int size) : DlbActivation(size) {}
 };
+
+// Row softmax over [num_rows, row_width] (src/activation.cuh:167-201 of dl-cuda);
+// the layer keeps its own copy of the probabilities for backward.
+class SoftmaxActivation : public Operation {
+public:
+  SoftmaxActivation(int num_rows, int row_width)
+      : rows_(num_rows), width_(row_width), probs_(static_cast<size_t>(num_rows) * row_width) {}
+
+  int input_size() const override { return rows_ * width_; }
+  int output_size() const override { return rows_ * width_; }
+
+  void forward(float *d_input, float *d_output) override {
+    // softmax into the layer's cache, then hand the caller a copy: backward must
+    // not depend on what the caller does with d_output afterwards
+    DLB_CHECK(dlb_softmax_fwd(d_input, probs_.get(), rows_, width_, 0, nullptr));
+    CUDA_CHECK(cudaMemcpyAsync(d_output, probs_.get(), sizeof(float) * rows_ * width_, cudaMemcpyDeviceToDevice, 0));
+  }
+
+  void backward(float *d_output_grad, float *d_input_grad) override {
+    DLB_CHECK(dlb_softmax_bwd(d_output_grad, probs_.get(), d_input_grad, rows_, width_, 1.0f, nullptr));
+  }
+
+private:
+  int rows_, width_;
+  DeviceBuffer<float> probs_;
+};

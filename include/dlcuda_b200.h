@@ -277,6 +277,68 @@ DLB_API int dlb_grad_norm_clip(int n_groups, float *const *h_grads, const int *h
                                float max_norm, void *workspace, size_t workspace_bytes,
                                float *d_result, void *stream);
 
+/* ---- pass-through dense ops (fp32 only, correctness implementations) ----------
+ * The matrix products, row softmax and loss kernels that the reference's
+ * TransformerLayer / LinearLayer / SoftmaxActivation / loss helpers run between
+ * the bandwidth-bound kernels above.  They are here so that a model built on
+ * the reference's layer API runs end to end on this library; they use the fp32
+ * pipes (no tensor cores) and keep the reference's per-element arithmetic: one
+ * fused multiply-add per k in ascending k from 0, then alpha, bias, accumulate.
+ *
+ * dlb_gemm_f32: for every batch z (zo = z / batch_inner, zi = z % batch_inner)
+ *   C[i*ldc + j] (+)= alpha * sum_kk A[i*a_row + kk*a_col] * B[kk*b_row + j*b_col] + bias[j]
+ * with A, B, C offset by zo*x_outer + zi*x_inner elements; bias may be NULL;
+ * accumulate != 0 adds the result to what C holds.  The strides let one launch
+ * serve X*W (linearLayerKernel, src/layers.cuh:23-36), dY*W^T
+ * (linearBackwardInputKernel :38-52, matMulBTKernel src/transformer.cuh:84-95),
+ * X^T*dY (linearBackwardWeightKernel :54-68, matMulATKernel :97-108), and the
+ * per-(batch, head) products of attnScoresKernel / attnApplyKernel (:8-19,
+ * :47-58) over all heads at once, addressing heads inside [tokens, d_model]
+ * by stride instead of through reshapeToHeadsKernel / reshapeFromHeadsKernel
+ * (:110-134). */
+DLB_API int dlb_gemm_f32(const float *a, const float *b, const float *bias, float *c,
+                         int m, int n, int k, int64_t a_row, int64_t a_col,
+                         int64_t b_row, int64_t b_col, int64_t ldc, int batch,
+                         int batch_inner, int64_t a_outer, int64_t a_inner,
+                         int64_t b_outer, int64_t b_inner, int64_t c_outer,
+                         int64_t c_inner, float alpha, int accumulate, void *stream);
+
+/* Row softmax, out may alias in.  causal_period > 0 keeps only the first
+ * (row % causal_period) + 1 entries of each row and writes exact zeros after
+ * them (applyCausalMaskKernel + softmaxForwardKernel, src/transformer.cuh:21-45);
+ * 0 is the plain softmax of softmaxForwardGeneralKernel (src/activation.cuh:121-143). */
+DLB_API int dlb_softmax_fwd(const float *in, float *out, int64_t rows, int width,
+                            int causal_period, void *stream);
+/* dx = s * (dy - sum_j dy_j*s_j) * scale; dx may alias dy.  Replaces
+ * softmaxBackwardKernel + scaleBufferKernel (src/transformer.cuh:60-82, :209-214)
+ * and softmaxBackwardGeneralKernel (src/activation.cuh:145-165). */
+DLB_API int dlb_softmax_bwd(const float *dy, const float *s, float *dx, int64_t rows,
+                            int width, float scale, void *stream);
+
+/* Per-sample losses and their gradients, src/loss.cuh:18-109 (computeLoss /
+ * computeLossBackward :146-202): error[n], grad[n] (grad[n*classes] for the
+ * categorical loss), clamp epsilon 1e-10 as in the reference. */
+typedef enum dlb_loss {
+  DLB_LOSS_SQUARED = 0,
+  DLB_LOSS_ABSOLUTE = 1,
+  DLB_LOSS_BCE = 2,
+  DLB_LOSS_CCE = 3
+} dlb_loss;
+DLB_API int dlb_loss_fwd(int kind, const float *y, const float *y_pred, float *error,
+                         int64_t n, int classes, void *stream);
+DLB_API int dlb_loss_bwd(int kind, const float *y, const float *y_pred, float *grad,
+                         int64_t n, int classes, void *stream);
+/* Cross entropy against integer targets: error[i] = -logf(max(p[i,target[i]], eps)),
+ * grad[i,c] = c == target[i] ? -1/(max(p,eps)*n) : 0.  Replaces
+ * categoricalCrossEntropyFromIdsKernel / ...BackwardFromIdsKernel
+ * (src/loss.cuh:111-144, wrappers :204-221). */
+DLB_API int dlb_ce_from_ids_fwd(const int32_t *target_ids, const float *y_pred,
+                                float *error, int n, int classes, float epsilon,
+                                void *stream);
+DLB_API int dlb_ce_from_ids_bwd(const int32_t *target_ids, const float *y_pred,
+                                float *grad, int n, int classes, float epsilon,
+                                void *stream);
+
 #ifdef __cplusplus
 }
 #endif

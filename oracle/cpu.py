@@ -175,3 +175,50 @@ def sq_norm(g):
     fn = lib().orc_sq_norm_f64
     fn.restype = C.c_double
     return float(fn(_p(g), C.c_int64(g.size)))
+
+
+# --- pass-through dense ops ------------------------------------------------------------
+def gemm(a, b, bias=None, alpha=1.0, c=None):
+    """alpha * a @ b + bias (+ c) for 2-D fp32 arrays of any strides, in the reference's summation order."""
+    assert a.dtype == np.float32 and b.dtype == np.float32
+    m, k = a.shape
+    n = b.shape[1]
+    out = np.zeros((m, n), np.float32) if c is None else _f(c).copy()
+    es = 4
+    bias = None if bias is None else _f(bias)
+    lib().orc_gemm(C.c_void_p(a.ctypes.data), C.c_void_p(b.ctypes.data), _p(bias), _p(out), m, n, k,
+                   C.c_int64(a.strides[0] // es), C.c_int64(a.strides[1] // es), C.c_int64(b.strides[0] // es),
+                   C.c_int64(b.strides[1] // es), C.c_int64(n), C.c_float(alpha), int(c is not None))
+    return out
+
+
+def softmax_fwd(x, causal_period=0):
+    x = _f(x)
+    out = np.empty_like(x)
+    lib().orc_softmax_fwd(_p(x), _p(out), C.c_int64(x.size // x.shape[-1]), x.shape[-1], causal_period)
+    return out
+
+
+def softmax_bwd(dy, s, scale=1.0):
+    dy, s = _f(dy), _f(s)
+    dx = np.empty_like(dy)
+    lib().orc_softmax_bwd(_p(dy), _p(s), _p(dx), C.c_int64(dy.size // dy.shape[-1]), dy.shape[-1], C.c_float(scale))
+    return dx
+
+
+def loss(kind, y, y_pred, classes=1):
+    """Returns (error[n], grad) for kind 0 squared, 1 absolute, 2 binary CE, 3 categorical CE."""
+    y, y_pred = _f(y), _f(y_pred)
+    n = y.size // classes if kind == 3 else y.size
+    err, grad = np.empty(n, np.float32), np.empty_like(y_pred)
+    lib().orc_loss(kind, _p(y), _p(y_pred), _p(err), _p(grad), C.c_int64(n), classes)
+    return err, grad
+
+
+def ce_from_ids(target, y_pred, eps=1e-10):
+    y_pred = _f(y_pred)
+    target = np.ascontiguousarray(target, np.int32)
+    n, classes = y_pred.shape
+    err, grad = np.empty(n, np.float32), np.empty_like(y_pred)
+    lib().orc_ce_from_ids(_p(target), _p(y_pred), _p(err), _p(grad), n, classes, C.c_float(eps))
+    return err, grad

@@ -323,3 +323,111 @@ double orc_sq_norm_f64(const float *g, int64_t n) {
 }
 
 }  // extern "C"
+
+extern "C" {
+
+// The reference's matrix products all have one shape per output element: a sum
+// over k in ascending order that nvcc contracts into one fused multiply-add per
+// step, starting from 0.0f (linearLayerKernel src/layers.cuh:23-36,
+// linearBackwardInputKernel :38-52, linearBackwardWeightKernel :54-68,
+// attnScoresKernel / attnApplyKernel / matMulBTKernel / matMulATKernel
+// src/transformer.cuh:8-19, 47-58, 84-108).  Strides select the variant:
+//   A(i,kk) = a[i*a_row + kk*a_col],  B(kk,j) = b[kk*b_row + j*b_col].
+// Then sum*alpha (attnScoresKernel's inv_scale), + bias[j] (linearLayerKernel),
+// and optionally c += (transformerResidualAddKernel after the Q/K/V input
+// gradients, src/transformer.cuh:663-677).
+void orc_gemm(const float *a, const float *b, const float *bias, float *c, int m, int n, int k, int64_t a_row,
+              int64_t a_col, int64_t b_row, int64_t b_col, int64_t ldc, float alpha, int accumulate) {
+  for (int i = 0; i < m; i++)
+    for (int j = 0; j < n; j++) {
+      float sum = 0.0f;
+      for (int kk = 0; kk < k; kk++) sum = fmaf(a[i * a_row + kk * a_col], b[kk * b_row + j * b_col], sum);
+      float v = sum * alpha;
+      if (bias) v = v + bias[j];
+      if (accumulate) v = c[i * ldc + j] + v;
+      c[i * ldc + j] = v;
+    }
+}
+
+// applyCausalMaskKernel + softmaxForwardKernel (src/transformer.cuh:21-45) and
+// softmaxForwardGeneralKernel (src/activation.cuh:121-143): row max, expf, sequential sum,
+// multiply by 1/sum.  causal_period > 0 overwrites entries past (row % period) with -1e9f first.
+void orc_softmax_fwd(const float *in, float *out, int64_t rows, int width, int causal_period) {
+  std::vector<float> row(width);
+  for (int64_t r = 0; r < rows; r++) {
+    for (int j = 0; j < width; j++) {
+      row[j] = in[r * width + j];
+      if (causal_period > 0 && j > r % causal_period) row[j] = -1e9f;
+    }
+    float mx = row[0];
+    for (int j = 1; j < width; j++) mx = fmaxf(mx, row[j]);
+    float sum = 0.0f;
+    for (int j = 0; j < width; j++) {
+      row[j] = expf(row[j] - mx);
+      sum += row[j];
+    }
+    const float inv = 1.0f / sum;
+    for (int j = 0; j < width; j++) out[r * width + j] = row[j] * inv;
+  }
+}
+
+// softmaxBackwardKernel + scaleBufferKernel (src/transformer.cuh:60-82, 209-214),
+// softmaxBackwardGeneralKernel (src/activation.cuh:145-165) with scale = 1.
+void orc_softmax_bwd(const float *dy, const float *s, float *dx, int64_t rows, int width, float scale) {
+  for (int64_t r = 0; r < rows; r++) {
+    const float *g = dy + r * width, *p = s + r * width;
+    float dot = 0.0f;
+    for (int j = 0; j < width; j++) dot = fmaf(g[j], p[j], dot);
+    for (int j = 0; j < width; j++) dx[r * width + j] = (p[j] * (g[j] - dot)) * scale;
+  }
+}
+
+static float orc_clamp_prob(float p) {
+  const float eps = 1e-10f;
+  if (p < eps) return eps;
+  if (p > 1.0f - eps) return 1.0f - eps;
+  return p;
+}
+
+// src/loss.cuh:18-109.  kind 0 squared, 1 absolute, 2 binary CE, 3 categorical CE.
+void orc_loss(int kind, const float *y, const float *yp, float *err, float *grad, int64_t n, int classes) {
+  const float eps = 1e-10f;
+  const float fn = static_cast<float>(n);
+  for (int64_t i = 0; i < n; i++) {
+    if (kind == 0) {
+      const float diff = y[i] - yp[i];
+      err[i] = diff * diff;
+      grad[i] = 2.0f * (yp[i] - y[i]) / fn;
+    } else if (kind == 1) {
+      err[i] = fabsf(y[i] - yp[i]);
+      const float diff = yp[i] - y[i];
+      grad[i] = ((diff > 0.0f) ? 1.0f : ((diff < 0.0f) ? -1.0f : 0.0f)) / fn;
+    } else if (kind == 2) {
+      const float p = orc_clamp_prob(yp[i]);
+      err[i] = -y[i] * logf(p) - (1.0f - y[i]) * logf(1.0f - p);
+      grad[i] = (-y[i] / p + (1.0f - y[i]) / (1.0f - p)) / fn;
+    } else {
+      float loss = 0.0f;
+      for (int c = 0; c < classes; c++) {
+        const int64_t at = i * classes + c;
+        loss -= y[at] * logf(yp[at] + eps);
+        grad[at] = -y[at] / (yp[at] + eps) / fn;
+      }
+      err[i] = loss;
+    }
+  }
+}
+
+// categoricalCrossEntropyFromIdsKernel / ...BackwardFromIdsKernel, src/loss.cuh:111-144.
+void orc_ce_from_ids(const int32_t *target, const float *yp, float *err, float *grad, int n, int classes,
+                     float eps) {
+  for (int i = 0; i < n; i++) {
+    for (int c = 0; c < classes; c++) grad[static_cast<int64_t>(i) * classes + c] = 0.0f;
+    float p = yp[static_cast<int64_t>(i) * classes + target[i]];
+    if (p < eps) p = eps;
+    err[i] = -logf(p);
+    grad[static_cast<int64_t>(i) * classes + target[i]] = -1.0f / (p * static_cast<float>(n));
+  }
+}
+
+}  // extern "C"
