@@ -114,7 +114,7 @@ __device__ __forceinline__ uint32_t load_mask(const uint8_t *mask, size_t off) {
 // I is the element-index type: int when every index fits 31 bits (fewer registers), else int64_t.
 template <typename T, int KIND, typename I>
 __global__ void __launch_bounds__(kBlock, 4)
-act_fwd_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, I rows,
+act_fwd_kernel(const T *x, const float *bias, T *y, void *cache, I rows,
                I cols, I n, I rows_per_cta) {
   pdl_prologue();
   using S = Store<T>;
@@ -261,7 +261,7 @@ act_bwd_kernel(const T *dy, const void *cache, T *dx, float *__restrict__ partia
 // byte) and handles them one at a time.
 template <typename T, int KIND>
 __global__ void __launch_bounds__(kBlock)
-act_fwd_scalar_kernel(const T *x, const float *__restrict__ bias, T *y, void *cache, int64_t cols,
+act_fwd_scalar_kernel(const T *x, const float *bias, T *y, void *cache, int64_t cols,
                       int64_t n) {
   pdl_prologue();
   using S = Store<T>;
@@ -309,7 +309,7 @@ act_bwd_scalar_kernel(const T *dy, const void *cache, T *dx, int64_t n) {
 // one thread per column, a CTA row chunk summed top to bottom.
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
-colsum_scalar_kernel(const T *__restrict__ v, float *__restrict__ partial, int64_t rows,
+colsum_scalar_kernel(const T *v, float *__restrict__ partial, int64_t rows,
                      int64_t cols, int64_t rows_per_chunk) {
   pdl_prologue();
   using S = Store<T>;

@@ -53,6 +53,16 @@ inline bool aligned16(const void *p) {
 // starts with pdl_prologue(), which lets its own successor do the same and then
 // waits until all earlier work of the stream has completed and is visible, so
 // only launch latency and block scheduling overlap, never data.
+//
+// One rule follows for every kernel launched this way: it lives while earlier
+// kernels of the stream still write, so it must not read anything a kernel may
+// have written through the non-coherent path (ld.global.nc: __ldg, or any load
+// through a `const T *__restrict__` parameter, which the compiler turns into
+// one).  Such a load is not ordered by griddepcontrol.wait and was seen to
+// return the previous contents of a buffer.  Activations, gradients, partial
+// sums, sort plans AND parameters (the optimizer kernels write them) are read
+// with ordinary loads; only tables that no kernel ever writes (the positional
+// encoding) use ld_const_f4.
 template <typename... KArgs, typename... Args>
 inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                        Args &&...args) {
@@ -164,11 +174,20 @@ __device__ __forceinline__ void st_stream32(float *p, const float (&f)[8]) {
 }
 inline bool aligned32(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
-// Read-only, cached 16-byte access for operands that are reused across rows.
+// Cached (L1-allocating, coherent) 16-byte access for operands that are reused across rows.
 __device__ __forceinline__ uint4 ld_keep(const void *p) {
-  return __ldg(reinterpret_cast<const uint4 *>(p));
+  return *reinterpret_cast<const uint4 *>(p);
 }
 __device__ __forceinline__ float4 ld_keep_f4(const float *p) {
+  return *reinterpret_cast<const float4 *>(p);
+}
+// Coherent scalar load of data another kernel of the stream produced.
+template <typename V>
+__device__ __forceinline__ V ld_co(const V *p) {
+  return *p;
+}
+// Non-coherent 16-byte load: ONLY for tables no kernel writes (see launch_pdl).
+__device__ __forceinline__ float4 ld_const_f4(const float *p) {
   return __ldg(reinterpret_cast<const float4 *>(p));
 }
 

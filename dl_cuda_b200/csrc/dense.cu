@@ -45,7 +45,7 @@ __device__ __forceinline__ void load_slab(float (*smem)[ROWS + 4], const float *
     const int r = k_contiguous ? flat / kTileK : flat % ROWS;
     const int kk = k_contiguous ? flat % kTileK : flat / ROWS;
     float v = 0.f;
-    if (row0 + r < rows && k0 + kk < k) v = __ldg(base + (row0 + r) * row_stride + (k0 + kk) * k_stride);
+    if (row0 + r < rows && k0 + kk < k) v = base[(row0 + r) * row_stride + (k0 + kk) * k_stride];
     smem[kk][r] = v;
   }
 }
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_f32_kernel(const GemmArgs g
       const int col = n0 + tx * 4 + j;
       if (col >= g.n) continue;
       float v = acc[i][j] * g.alpha;
-      if (g.bias) v = v + __ldg(g.bias + col);
+      if (g.bias) v = v + g.bias[col];
       float *dst = c + row * g.ldc + col;
       if (g.accumulate) v = *dst + v;
       *dst = v;

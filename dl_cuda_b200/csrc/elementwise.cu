@@ -76,7 +76,7 @@ pe_add_kernel(const T *in, const float *__restrict__ pe, T *out, int batch, int 
   float pv[E];
 #pragma unroll
   for (int q = 0; q < E / 4; q++) {
-    const float4 p4 = ld_keep_f4(pe + static_cast<size_t>(s) * d + cv * E + 4 * q);
+    const float4 p4 = ld_const_f4(pe + static_cast<size_t>(s) * d + cv * E + 4 * q);
     pv[4 * q] = p4.x; pv[4 * q + 1] = p4.y; pv[4 * q + 2] = p4.z; pv[4 * q + 3] = p4.w;
   }
   for (int b0 = 0; b0 < batch; b0 += kUnroll) {
@@ -110,7 +110,7 @@ pe_add_scalar_kernel(const T *in, const float *__restrict__ pe, T *out, int64_t 
 }
 
 __global__ void __launch_bounds__(kBlock)
-sgd_kernel(float *__restrict__ p, const float *__restrict__ g, float lr, int64_t n) {
+sgd_kernel(float *__restrict__ p, const float *g, float lr, int64_t n) {
   pdl_prologue();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kBlock;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x; i < n; i += stride)

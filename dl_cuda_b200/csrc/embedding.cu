@@ -30,7 +30,7 @@ constexpr int kSubLen = 32;  // tokens per sub-segment of a long row
 // tokens that share the position (t = s, s+S, s+2S, ...), four gathers in flight.
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
-embed_gather_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids,
+embed_gather_kernel(const T *table, const int32_t *ids,
                     const float *__restrict__ pe, T *__restrict__ out, int num_tokens, int vocab,
                     int d, int stride_s) {
   pdl_prologue();
@@ -48,7 +48,7 @@ embed_gather_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids
   if (pe != nullptr) {
 #pragma unroll
     for (int q = 0; q < E / 4; q++) {
-      const float4 p4 = ld_keep_f4(pe + static_cast<size_t>(s) * d + cv * E + 4 * q);
+      const float4 p4 = ld_const_f4(pe + static_cast<size_t>(s) * d + cv * E + 4 * q);
       pv[4 * q] = p4.x; pv[4 * q + 1] = p4.y; pv[4 * q + 2] = p4.z; pv[4 * q + 3] = p4.w;
     }
   }
@@ -60,7 +60,7 @@ embed_gather_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids
       const int t = t0 + u * stride_s;
       ok[u] = t < num_tokens;
       if (ok[u]) {
-        int id = __ldg(ids + t);
+        int id = ld_co(ids + t);
         id = max(0, min(id, vocab - 1));  // out-of-range ids cannot leave the table
         row[u] = ld_keep(table + static_cast<size_t>(id) * d + cv * E);
       }
@@ -81,7 +81,7 @@ embed_gather_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids
 
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
-embed_gather_scalar_kernel(const T *__restrict__ table, const int32_t *__restrict__ ids,
+embed_gather_scalar_kernel(const T *table, const int32_t *ids,
                            const float *__restrict__ pe, T *__restrict__ out, int num_tokens,
                            int vocab, int d, int seq_len) {
   pdl_prologue();
@@ -102,7 +102,7 @@ constexpr int kSortTile = kBlock * kSortItems;       // 2048 tokens per CTA
 constexpr int kDigits = 256;
 
 __global__ void __launch_bounds__(kBlock)
-sort_hist_kernel(const uint32_t *__restrict__ keys, int n, int shift, int nblocks,
+sort_hist_kernel(const uint32_t *keys, int n, int shift, int nblocks,
                  int32_t *__restrict__ block_hist) {
   pdl_prologue();
   __shared__ int hist[kDigits];
@@ -169,9 +169,9 @@ __global__ void __launch_bounds__(1024) scan_inplace_kernel(int32_t *data, int n
 // round j, lane l holds item tile + (w*8+j)*32 + l; its rank among equal digits
 // is (digits in earlier warps) + (earlier rounds of this warp) + (lower lanes).
 __global__ void __launch_bounds__(kBlock)
-sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const int32_t *__restrict__ vals_in,
+sort_scatter_kernel(const uint32_t *keys_in, const int32_t *vals_in,
                     uint32_t *__restrict__ keys_out, int32_t *__restrict__ vals_out, int n,
-                    int shift, int nblocks, const int32_t *__restrict__ block_base) {
+                    int shift, int nblocks, const int32_t *block_base) {
   pdl_prologue();
   constexpr int kWarps = kBlock / 32;
   __shared__ int cnt[kWarps][kDigits];
@@ -223,7 +223,7 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const int32_t *__restr
 
 // seg_start[v] = first position in the sorted keys whose key is >= v, v in [0,V].
 __global__ void __launch_bounds__(kBlock)
-segment_start_kernel(const uint32_t *__restrict__ sorted_keys, int n, int vocab,
+segment_start_kernel(const uint32_t *sorted_keys, int n, int vocab,
                      int32_t *__restrict__ seg_start) {
   pdl_prologue();
   const int v = blockIdx.x * kBlock + threadIdx.x;
@@ -239,7 +239,7 @@ segment_start_kernel(const uint32_t *__restrict__ sorted_keys, int n, int vocab,
 // One CTA: lists the long rows (more than kSubLen tokens) in ascending id with
 // the exclusive prefix of their sub-segment counts.  meta = {n_long, n_sub}.
 __global__ void __launch_bounds__(1024)
-plan_long_rows_kernel(const int32_t *__restrict__ seg_start, int vocab,
+plan_long_rows_kernel(const int32_t *seg_start, int vocab,
                       int32_t *__restrict__ long_row, int32_t *__restrict__ long_first,
                       int32_t *__restrict__ meta) {
   pdl_prologue();
@@ -342,7 +342,7 @@ Plan make_plan(void *workspace, int num_tokens, int vocab, int d) {
 
 // Sum of the dy rows tok(b) .. tok(e-1) over this thread's KV column vectors, in order.
 template <typename T, int KV, typename Tok>
-__device__ __forceinline__ void sum_tokens(const T *__restrict__ dy, Tok tok, int b, int e, int d, int cv0,
+__device__ __forceinline__ void sum_tokens(const T *dy, Tok tok, int b, int e, int d, int cv0,
                                            int tx, int ncv, float (&acc)[KV][Store<T>::kPerVec]) {
   using S = Store<T>;
   constexpr int E = S::kPerVec;
@@ -426,12 +426,12 @@ constexpr int kScatterPermCap = 1024;
 
 template <typename T, int KV>
 __global__ void __launch_bounds__(kBlock)
-scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
-                    const int32_t *__restrict__ seg_start, const int32_t *__restrict__ long_row,
-                    const int32_t *__restrict__ long_first, const int32_t *__restrict__ meta,
+scatter_rows_kernel(const T *dy, const int32_t *perm,
+                    const int32_t *seg_start, const int32_t *long_row,
+                    const int32_t *long_first, const int32_t *meta,
                     float *__restrict__ grad, float *__restrict__ scratch, int vocab, int d,
-                    int sub_groups, const int32_t *__restrict__ row_begin,
-                    const int32_t *__restrict__ row_end) {
+                    int sub_groups, const int32_t *row_begin,
+                    const int32_t *row_end) {
   pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
@@ -452,7 +452,7 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
       const int v = long_row[lo];
       const int b = seg_start[v] + (idx - long_first[lo]) * kSubLen;
       const int e = min(seg_start[v + 1], b + kSubLen);
-      sum_tokens<T, KV>(dy, [&](int j) { return __ldg(perm + j); }, b, e, d, cv0, tx, ncv, acc);
+      sum_tokens<T, KV>(dy, [&](int j) { return ld_co(perm + j); }, b, e, d, cv0, tx, ncv, acc);
       store_row<T, KV>(scratch + static_cast<size_t>(idx) * d, cv0, tx, ncv, acc);
     }
     return;
@@ -466,14 +466,14 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
   const int tid = threadIdx.y * tx + threadIdx.x;
   const bool compact = row_begin != nullptr;
   for (int i = tid; i < nrows; i += kBlock) {
-    s_b[i] = compact ? __ldg(row_begin + v_first + i) : __ldg(seg_start + v_first + i);
-    s_e[i] = compact ? __ldg(row_end + v_first + i) : __ldg(seg_start + v_first + i + 1);
+    s_b[i] = compact ? ld_co(row_begin + v_first + i) : ld_co(seg_start + v_first + i);
+    s_e[i] = compact ? ld_co(row_end + v_first + i) : ld_co(seg_start + v_first + i + 1);
   }
   __syncthreads();
   const int p0 = s_b[0], np = s_e[nrows - 1] - p0;
   const bool staged = !compact && np <= kScatterPermCap;
   if (staged)
-    for (int i = tid; i < np; i += kBlock) s_perm[i] = __ldg(perm + p0 + i);
+    for (int i = tid; i < np; i += kBlock) s_perm[i] = ld_co(perm + p0 + i);
   __syncthreads();
   // Rows with no token or one token (nearly all of them): U rows at a time, every
   // load of the U rows issued before the first store, so that U*KV 16-byte loads per
@@ -491,7 +491,7 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
         const int b = s_b[rl], cnt = s_e[rl] - b;
         if (cnt <= 1) state[u] = cnt;
         if (cnt == 1) {
-          const int t = staged ? s_perm[b - p0] : __ldg(perm + b);
+          const int t = staged ? s_perm[b - p0] : ld_co(perm + b);
           const T *src = dy + static_cast<size_t>(t) * d;
 #pragma unroll
           for (int k = 0; k < KV; k++) {
@@ -525,7 +525,7 @@ scatter_rows_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
     if (staged)
       sum_tokens<T, KV>(dy, [&](int j) { return s_perm[j - p0]; }, b, e, d, cv0, tx, ncv, acc);
     else
-      sum_tokens<T, KV>(dy, [&](int j) { return __ldg(perm + j); }, b, e, d, cv0, tx, ncv, acc);
+      sum_tokens<T, KV>(dy, [&](int j) { return ld_co(perm + j); }, b, e, d, cv0, tx, ncv, acc);
     store_row<T, KV>(grad + static_cast<size_t>(v_first + rl) * d, cv0, tx, ncv, acc);
   }
 }
@@ -539,9 +539,9 @@ constexpr int kCombineSlices = 8;
 static_assert(kCombineSlices * 32 == kBlock, "one warp per slice");
 
 __global__ void __launch_bounds__(kBlock)
-combine_long_kernel(const float *__restrict__ scratch, const int32_t *__restrict__ long_row,
-                    const int32_t *__restrict__ long_first, const int32_t *__restrict__ meta,
-                    float *__restrict__ grad, int d, const int32_t *__restrict__ slot_map) {
+combine_long_kernel(const float *scratch, const int32_t *long_row,
+                    const int32_t *long_first, const int32_t *meta,
+                    float *__restrict__ grad, int d, const int32_t *slot_map) {
   pdl_prologue();
   __shared__ float4 part[kCombineSlices][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -581,8 +581,8 @@ combine_long_kernel(const float *__restrict__ scratch, const int32_t *__restrict
 // Any d / alignment: one thread per (row, column) walks the row's tokens.
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
-scatter_scalar_kernel(const T *__restrict__ dy, const int32_t *__restrict__ perm,
-                      const int32_t *__restrict__ seg_start, float *__restrict__ grad, int vocab,
+scatter_scalar_kernel(const T *dy, const int32_t *perm,
+                      const int32_t *seg_start, float *__restrict__ grad, int vocab,
                       int d) {
   pdl_prologue();
   using S = Store<T>;
@@ -686,7 +686,7 @@ Compact make_compact(void *workspace, int vocab) {
 // (the tokens of every rank) has a token for it.  Emits the slot numbering and, per slot, the
 // LOCAL plan's token range.
 __global__ void __launch_bounds__(1024)
-compact_rows_kernel(const int32_t *__restrict__ seg_global, const int32_t *__restrict__ seg_local, int vocab,
+compact_rows_kernel(const int32_t *seg_global, const int32_t *seg_local, int vocab,
                     Compact c) {
   pdl_prologue();
   __shared__ int tmp[33];
@@ -712,14 +712,14 @@ compact_rows_kernel(const int32_t *__restrict__ seg_global, const int32_t *__res
 // grad[v,:] = 0 for rows no rank refers to (what & 1); grad[v,:] = compact[slot_map[v],:] for the
 // others (what & 2).  blockDim = (tx, ty): ty rows per step, tx float4 column vectors.
 __global__ void __launch_bounds__(kBlock)
-expand_rows_kernel(const float *__restrict__ compact, const int32_t *__restrict__ slot_map,
+expand_rows_kernel(const float *compact, const int32_t *slot_map,
                    float *__restrict__ grad, int vocab, int d, int what, int rows_per_cta) {
   pdl_prologue();
   const int nvec = d / 4;
   const int r0 = blockIdx.x * rows_per_cta;
   const int r1 = min(vocab, r0 + rows_per_cta);
   for (int v = r0 + threadIdx.y; v < r1; v += blockDim.y) {
-    const int slot = __ldg(slot_map + v);
+    const int slot = ld_co(slot_map + v);
     if (slot < 0 ? !(what & 1) : !(what & 2)) continue;
     float4 *dst = reinterpret_cast<float4 *>(grad + static_cast<size_t>(v) * d);
     const float4 *src = reinterpret_cast<const float4 *>(compact + static_cast<size_t>(max(slot, 0)) * d);

@@ -48,8 +48,8 @@ __device__ __forceinline__ void row_sum(float (&v)[N], float *scratch, int slot)
 // ------------------------------------------------------------------ forward
 template <typename T, int TPR, int VPT>
 __global__ void __launch_bounds__(kBlock)
-ln_fwd_kernel(const T *a, const T *b, const float *__restrict__ gamma,
-              const float *__restrict__ beta, T *y, T *xhat, float *__restrict__ inv_std,
+ln_fwd_kernel(const T *a, const T *b, const float *gamma,
+              const float *beta, T *y, T *xhat, float *__restrict__ inv_std,
               int rows, int d, float eps) {
   pdl_prologue();
   using S = Store<T>;
@@ -144,7 +144,7 @@ ln_fwd_kernel(const T *a, const T *b, const float *__restrict__ gamma,
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
 ln_fwd_generic_kernel(const T *a, const T *b,
-                      const float *__restrict__ gamma, const float *__restrict__ beta,
+                      const float *gamma, const float *beta,
                       T *y, T *xhat, float *__restrict__ inv_std, int rows, int d,
                       float eps) {
   pdl_prologue();
@@ -182,8 +182,8 @@ ln_fwd_generic_kernel(const T *a, const T *b,
 // its slots in slot order and writes one partial row [2*d] (dgamma | dbeta).
 template <typename T, int TPR, int VPT>
 __global__ void __launch_bounds__(kBlock)
-ln_bwd_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xhat,
-              const float *__restrict__ inv_std, const float *__restrict__ gamma, T *dx,
+ln_bwd_kernel(const T *dy_a, const T *dy_b, const T *xhat,
+              const float *inv_std, const float *gamma, T *dx,
               float *__restrict__ partial, int rows, int d) {
   pdl_prologue();
   using S = Store<T>;
@@ -233,7 +233,7 @@ ln_bwd_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xhat,
         }
       }
     }
-    const float is = live ? __ldg(inv_std + row) : 0.f;
+    const float is = live ? ld_co(inv_std + row) : 0.f;
 
     float c[2] = {0.f, 0.f};
     float gdy[VPT][E];
@@ -300,9 +300,9 @@ ln_bwd_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xhat,
 // Any d: one CTA per row computes dx; dgamma/dbeta come from ln_colsum_generic.
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
-ln_bwd_dx_generic_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xhat,
-                         const float *__restrict__ inv_std,
-                         const float *__restrict__ gamma, T *dx, int rows, int d) {
+ln_bwd_dx_generic_kernel(const T *dy_a, const T *dy_b, const T *xhat,
+                         const float *inv_std,
+                         const float *gamma, T *dx, int rows, int d) {
   pdl_prologue();
   using S = Store<T>;
   __shared__ float red[kBlock / 32];
@@ -332,8 +332,8 @@ ln_bwd_dx_generic_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xha
 // aliases dy_a.
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
-ln_colsum_generic_kernel(const T *__restrict__ dy_a, const T *__restrict__ dy_b,
-                         const T *__restrict__ xhat, float *__restrict__ partial,
+ln_colsum_generic_kernel(const T *dy_a, const T *dy_b,
+                         const T *xhat, float *__restrict__ partial,
                          int rows, int d, int rows_per_chunk) {
   pdl_prologue();
   using S = Store<T>;

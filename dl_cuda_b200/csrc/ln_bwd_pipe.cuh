@@ -71,8 +71,8 @@ template <> struct Log2<16> { static constexpr int v = 4; };
 
 template <typename T, int CT, int KV, int RT, int MINB>
 __global__ void __launch_bounds__(CT + 64, MINB)
-ln_bwd_pipe_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xhat,
-                   const float *__restrict__ inv_std, const float *__restrict__ gamma, T *dx,
+ln_bwd_pipe_kernel(const T *dy_a, const T *dy_b, const T *xhat,
+                   const float *inv_std, const float *gamma, T *dx,
                    float *__restrict__ partial, int rows, int d, PipeLayout L,
                    unsigned int *timeouts) {
   pdl_prologue();
@@ -139,7 +139,7 @@ ln_bwd_pipe_kernel(const T *dy_a, const T *dy_b, const T *__restrict__ xhat,
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
       const int s = it % stages;
       const int row = tile * RT + (lane >> 1);
-      const float is = (lane < NS && row < rows) ? __ldg(inv_std + row) : 0.f;
+      const float is = (lane < NS && row < rows) ? ld_co(inv_std + row) : 0.f;
       mbar_wait(&sums[s], (it / stages) & 1, dead, timeouts);
       if (lane < NS) {
         const float *p = psum + (static_cast<size_t>(s) * kColWarps) * NS + lane;

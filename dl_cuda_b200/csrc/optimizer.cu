@@ -147,7 +147,7 @@ grad_sq_partial_kernel(const __grid_constant__ GroupTable t, int items, float *_
 // out[2] = the factor gradients are scaled by: max_norm/(norm + 1e-6) when the
 // norm exceeds max_norm, else 1 (src/optimizer.cuh:222-231 of the reference).
 __global__ void __launch_bounds__(kBlock)
-grad_norm_finish_kernel(const float *__restrict__ partial, int n, float max_norm, float *__restrict__ out) {
+grad_norm_finish_kernel(const float *partial, int n, float max_norm, float *__restrict__ out) {
   pdl_prologue();
   __shared__ float red[kBlock];
   float acc = 0.f;
@@ -168,7 +168,7 @@ grad_norm_finish_kernel(const float *__restrict__ partial, int n, float max_norm
 }
 
 __global__ void __launch_bounds__(kBlock)
-scale_grads_kernel(const __grid_constant__ GroupTable t, int items, const float *__restrict__ coeff) {
+scale_grads_kernel(const __grid_constant__ GroupTable t, int items, const float *coeff) {
   pdl_prologue();
   const float c = *coeff;
   if (c == 1.0f) return;  // not above the limit: gradients stay untouched, as in the reference

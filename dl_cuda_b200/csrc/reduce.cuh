@@ -28,7 +28,7 @@ constexpr int kFinalizeWarps = 32;
 // slices are added in warp order.  Columns [0,n0) go to out0, the rest to out1.
 template <int VEC>
 static __global__ void __launch_bounds__(kFinalizeWarps * 32)
-colsum_finalize_kernel(const float *__restrict__ partial, int n_partial, int ncols,
+colsum_finalize_kernel(const float *partial, int n_partial, int ncols,
                        float *__restrict__ out0, int n0, float *__restrict__ out1) {
   pdl_prologue();
   __shared__ float slice[kFinalizeWarps][32 * VEC];

@@ -2,7 +2,7 @@
 
 The products keep the reference's per-element arithmetic (one fused multiply-add per k in ascending
 order), so they are compared bit for bit; softmax and the losses go through expf/logf and a
-warp-parallel row sum and are compared within 1e-6 relative."""
+warp-parallel row sum and are compared within 1e-5 relative."""
 import numpy as np
 import pytest
 import torch
@@ -93,7 +93,8 @@ def test_softmax_forward_backward(rows, width):
     dy = g.standard_normal((rows, width)).astype(np.float32)
     y = ops.softmax_fwd(dev(x))
     want = oracle.softmax_fwd(x)
-    assert rel_err(y.cpu().numpy(), want) < 1e-6
+    # the oracle adds the row's exponentials one after another in fp32, the kernel in a lane-strided tree
+    assert rel_err(y.cpu().numpy(), want) < 1e-5
     assert np.allclose(y.cpu().numpy().sum(axis=1), 1.0, atol=1e-5)
     dx = ops.softmax_bwd(dev(dy), y, scale=0.5).cpu().numpy()
     assert rel_err(dx, oracle.softmax_bwd(dy, y.cpu().numpy(), 0.5)) < 1e-5
@@ -125,7 +126,7 @@ def test_losses(kind):
     elif kind == capi.LOSS_BCE:
         y = g.integers(0, 2, n).astype(np.float32)
         pred = g.random(n).astype(np.float32)
-        pred[:3] = [0.0, 1.0, 1e-12]  # the clamp
+        pred[:3] = [0.0, 0.999999, 1e-12]  # the clamp from below; p = 1 gives inf - inf in the reference too
     else:
         y = g.standard_normal(n).astype(np.float32)
         pred = g.standard_normal(n).astype(np.float32)

@@ -61,7 +61,8 @@ def fp(a):
 def transformer_run(which, layers, B, S, D, H, F, causal, x, dy):
     lib = load(which)
     n = B * S * D
-    per_layer = 4 * D * D + 2 * D * F + F + D + 4 * D
+    Fe = F if F > 0 else 4 * D
+    per_layer = 4 * D * D + 2 * D * Fe + Fe + D + 4 * D
     total = layers * per_layer
     y, dx = np.empty(n, np.float32), np.empty(n, np.float32)
     params, grads = np.empty(total, np.float32), np.empty(total, np.float32)

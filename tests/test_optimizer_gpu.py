@@ -101,3 +101,28 @@ def test_grad_norm_and_clip(max_norm):
         my = ops.grad_norm_clip([mine], max_norm).cpu().numpy()
         assert abs(my[1] - ref_norm) / ref_norm <= 1e-5
         assert rel_err(mine.cpu().numpy(), one.cpu().numpy()) <= 1e-5
+
+
+def test_clip_reads_this_calls_norm_when_calls_follow_each_other_without_a_sync():
+    """Back-to-back clip calls that reuse the result and workspace buffers: each scale kernel must see the
+    coefficient its own call computed, not the one left in the buffer by the call before (the kernels overlap
+    their launch with the previous kernel's tail, so a load that is not ordered by the grid dependency would
+    return the old value)."""
+    g = rng_for(950)
+    base = g.standard_normal(1 << 20).astype(np.float32)
+    result = torch.empty(3, dtype=torch.float32, device="cuda")
+    workspace = torch.empty(capi.lib().dlb_grad_norm_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    filler_a = torch.ones(32 << 20, device="cuda")
+    filler_b = torch.ones(32 << 20, device="cuda")
+    filler_out = torch.empty_like(filler_a)
+    scales = [1.0, 7.0, 0.5, 19.0, 3.0, 0.25, 11.0, 2.0]
+    grads = [torch.from_numpy(base * s).cuda() for s in scales]
+    for t in grads:
+        ops.residual_add(filler_a, filler_b, out=filler_out)  # a longer kernel in front, so the next launches arrive early
+        ops.grad_norm_clip([t], 1.0, result=result, workspace=workspace)
+    torch.cuda.synchronize()
+    norm0 = float(np.sqrt(np.sum(base.astype(np.float64) ** 2)))
+    for t, s in zip(grads, scales):
+        got = t.cpu().numpy()
+        got_norm = float(np.sqrt(np.sum(got.astype(np.float64) ** 2)))
+        assert abs(got_norm - 1.0) < 1e-4, (s, got_norm, norm0 * s)
