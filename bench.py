@@ -571,11 +571,11 @@ def kernel_sweep(peak):
 # summarised under profiles/, taken on a quarter-size case (8192 or 16384 rows) and scaled by rows:
 # traffic of these streaming kernels grows in proportion to the rows.  Bytes per token row.
 NCU_TRAFFIC_PER_ROW = {
-    "relu_fwd": (268.517632e6 + 231.812096e6) / 8192,   # profiles/act_relu_kernels_bf16_8192x16384.txt
-    "relu_bwd": (285.612288e6 + 232.156160e6) / 8192,
-    "ln1_fwd": (268.487168e6 + 217.069312e6) / 16384,   # profiles/ln_fwd_kernel_bf16_16384x4096.txt
-    "ln2_fwd": (268.487168e6 + 217.069312e6) / 16384,
-    "ln2_bwd": (268.619264e6 + 98.678528e6) / 16384,    # profiles/ln_bwd_pipe_kernel_bf16_16384x4096.txt
+    "relu_fwd": (268.512768e6 + 230.742528e6) / 8192,   # profiles/act_relu_kernels_bf16_8192x16384.txt
+    "relu_bwd": (286.164736e6 + 246.704896e6) / 8192,
+    "ln1_fwd": (268.486656e6 + 216.835328e6) / 16384,   # profiles/ln_fwd_kernel_bf16_16384x4096.txt
+    "ln2_fwd": (268.486656e6 + 216.835328e6) / 16384,
+    "ln2_bwd": (268.583424e6 + 98.576896e6) / 16384,    # profiles/ln_bwd_pipe_kernel_bf16_16384x4096.txt
 }
 NCU_TRAFFIC_NOTE = ("ncu dram__bytes_read+write of a quarter-size capture (profiles/*.txt) scaled by rows; writes still "
                     "in L2 when the kernel ends are not counted by ncu, so it can read below the algorithmic bytes")
