@@ -431,7 +431,7 @@ scatter_rows_kernel(const T *dy, const int32_t *perm,
                     const int32_t *long_first, const int32_t *meta,
                     float *__restrict__ grad, float *__restrict__ scratch, int vocab, int d,
                     int sub_groups, const int32_t *row_begin,
-                    const int32_t *row_end) {
+                    const int32_t *row_end, int rows_cta) {
   pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
@@ -457,7 +457,6 @@ scatter_rows_kernel(const T *dy, const int32_t *perm,
     }
     return;
   }
-  const int rows_cta = ty > kScatterRowsPerCta ? ty : kScatterRowsPerCta;
   const int v_first = (blockIdx.x - sub_groups) * rows_cta;
   // Output row r takes the sorted tokens [begin, end).  Dense mode: r is the table row and the
   // range is seg_start[r], seg_start[r+1].  Compact mode (row_begin given): r is a slot of the
@@ -747,12 +746,13 @@ int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *gr
   const int ncv = d / E;
   // Sub-segment groups loop over the sub-segments, so a few hundred CTAs cover any count.
   const int sub_groups = min(ceil_div(p.max_sub, bs.ty), 4 * sm_count());
-  const int row_groups = ceil_div(out_rows, bs.ty > kScatterRowsPerCta ? bs.ty : kScatterRowsPerCta);
+  const int rows_cta = bs.ty > kScatterRowsPerCta ? bs.ty : kScatterRowsPerCta;
+  const int row_groups = ceil_div(out_rows, rows_cta);
   dim3 grid(sub_groups + row_groups, ceil_div(ncv, bs.tx * KV));
   launch_pdl(scatter_rows_kernel<T, KV>, grid, dim3(bs.tx, bs.ty), 0, st,
              static_cast<const T *>(dy), perm, p.seg_start, p.long_row, p.long_first, p.meta, grad, p.scratch,
              out_rows, d, sub_groups, compact ? compact->row_begin : nullptr,
-             compact ? compact->row_end : nullptr);
+             compact ? compact->row_end : nullptr, rows_cta);
   DLB_LAUNCH_CHECK("scatter_rows");
   return DLB_OK;
 }
