@@ -165,7 +165,7 @@ class Chain:
     OPS = ["sort_tokens", "embed_gather_pe", "ln1_fwd", "relu_fwd", "ln2_fwd",
            "ln2_bwd", "relu_bwd", "ln1_bwd", "embed_scatter", "allreduce"]
 
-    def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist):
+    def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist, exchange="peer"):
         from dl_cuda_b200 import capi, ops
         global allreduce_param_grads
         from dl_cuda_b200.sharding import allreduce_param_grads
@@ -229,8 +229,22 @@ class Chain:
             self.ids_all = torch.empty(Tg, dtype=torch.int32, device=dev)
             self.ws_global = ops.embed_workspace(Tg, V, D, dev)
             self.ws_compact = ops.embed_compact_workspace(V, dev)
-            self.compact_rows = torch.empty(min(V, Tg), D, device=dev)
             self.h_used = torch.zeros(1, dtype=torch.int32).pin_memory()
+            # Table-gradient exchange: the library's fused scatter-add + peer-memory exchange, or (asked for, or when
+            # symmetric memory cannot be set up) NCCL's all-reduce of the compacted rows.
+            self.peer = None
+            self.exchange_note = "nccl all-reduce of the compacted rows"
+            if exchange == "peer":
+                try:
+                    from dl_cuda_b200.sharding import PeerExchange
+                    self.peer = PeerExchange(dist.dist, V, D, min(V, Tg), dev)
+                    self.table_grad = self.peer.table_grad()
+                    self.exchange_note = "scatter-add fused with a peer-memory exchange (owner-reduce, broadcast into the dense tables)"
+                except Exception as exc:  # no symmetric memory on this box / build
+                    print(f"[bench] peer exchange unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+                    self.exchange_note += f" (peer exchange unavailable: {type(exc).__name__})"
+            if self.peer is None:
+                self.compact_rows = torch.empty(min(V, Tg), D, device=dev)
         self.distinct_ids = int(np.unique(self.h_ids.numpy()).size)
 
     # algorithmic HBM bytes of each op for the local tokens (each input byte read once,
@@ -315,6 +329,27 @@ class Chain:
             # Compacted form: only the rows some rank uses are summed, all-reduced and expanded.
             self.plan_ready.synchronize()  # the row count is a host argument of the calls below
             used = int(self.h_used[0])
+            if self.peer is not None:
+                px, ops = self.peer, self.ops
+                # every rank pushes the rows it has tokens for into their owners' receive areas
+                ops.embed_scatter_bwd_peer(self.dx1, self.ws_embed, self.ws_compact, px.recv_ptrs, px.rank, px.cap_rows,
+                                           used, V, stream=st)
+                mark()
+                # rows no rank uses are zeroed locally, beside the exchange
+                self.side.wait_stream(torch.cuda.current_stream())
+                chk(lib.dlb_embed_expand_rows(None, p(self.ws_compact), p(self.table_grad), V, D, 1, self.side.cuda_stream))
+                self.zero_done.record(self.side)
+                px.barrier(0, stream=st)      # all partial rows have arrived
+                ops.embed_reduce_broadcast_peer(px.recv, self.ws_compact, px.grad_ptrs, px.rank, px.cap_rows, V, D, stream=st)
+                self.dist.dist.all_reduce(self.small_grads)
+                torch.cuda.current_stream().wait_event(self.zero_done)
+                px.barrier(1, stream=st)      # every rank's table holds every reduced row; receive areas are zero again
+                mark()
+                if copy_inputs:
+                    self.h_result.copy_(self.small_grads, non_blocking=True)
+                    torch.cuda.current_stream().synchronize()
+                    return float(self.h_result[0])
+                return None
             chk(lib.dlb_embed_scatter_bwd_compact(p(self.dx1), p(self.ws_embed), self.ws_embed.numel(),
                                                   p(self.ws_compact), p(self.compact_rows), used, T, V, D, code, st))
             mark()
@@ -663,6 +698,8 @@ def main():
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
     ap.add_argument("--tokens", type=int, default=BATCH * SEQ, help="global token rows (default: batch 8 x seq 4096)")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: how the embedding-table gradient is exchanged (default: the library's peer-memory kernels)")
     ap.add_argument("--skip-kernels", action="store_true", help="skip the per-kernel fp32 sweep")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the host baseline")
     ap.add_argument("--case", default=None, help="run one small kernel case (for ncu) and exit: " + ", ".join(PROFILE_CASES))
@@ -686,7 +723,8 @@ def main():
     from dl_cuda_b200.sharding import shard_rows
     _, tokens_local = shard_rows(args.tokens, n, dist.rank, SEQ if args.tokens % (SEQ * n) == 0 else 1)
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
-    chain = Chain(tokens_local, SEQ, D_MODEL, D_FF, VOCAB, dtype, seed=1234 + dist.rank, dist=dist)
+    chain = Chain(tokens_local, SEQ, D_MODEL, D_FF, VOCAB, dtype, seed=1234 + dist.rank, dist=dist,
+                  exchange=args.exchange)
     lib = chain.lib
 
     # device-resident run: the headline `value` (no events between the kernels)
@@ -757,6 +795,12 @@ def main():
         "chain_bytes_per_step": int(sum(op_bytes.values()) * n),
         "chain_gbs": round(sum(op_bytes.values()) * n / ms_per_step / 1e6, 1),
     }
+    if dist.active:
+        result["config"]["table_grad_exchange"] = chain.exchange_note
+        if chain.peer is not None:
+            gave_up = chain.peer.timed_out()
+            if gave_up:
+                raise SystemExit(f"peer barrier wait gave up (channel mask {gave_up}): the measurement is void")
     del chain
     torch.cuda.empty_cache()
     if dist.rank == 0 and n == 1:

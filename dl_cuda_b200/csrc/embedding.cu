@@ -424,14 +424,33 @@ __device__ __forceinline__ void store_row(float *dst, int cv0, int tx, int ncv,
 constexpr int kScatterRowsPerCta = 16;
 constexpr int kScatterPermCap = 1024;
 
-template <typename T, int KV>
+// Multi-GPU "peer" output: output row r (a slot of the compacted row list) belongs to rank
+// r % n, which sums it.  A rank that has tokens for the row stores its partial sum straight into
+// the owner's receive area, laid out [source rank][r / n][d], through the owner's peer mapping;
+// rows without local tokens are not sent (the receive area is zero where nothing arrives).
+constexpr int kMaxPeers = 16;
+struct PeerOut {
+  float *recv[kMaxPeers];  // every rank's receive area as mapped into this GPU's address space
+  int n, me, cap;          // ranks, this rank, rows per source in a receive area
+};
+
+template <bool PEER>
+__device__ __forceinline__ float *out_row_ptr(float *grad, const PeerOut &po, int r, int d) {
+  if constexpr (PEER) {
+    return po.recv[r % po.n] + (static_cast<size_t>(po.me) * po.cap + r / po.n) * d;
+  } else {
+    return grad + static_cast<size_t>(r) * d;
+  }
+}
+
+template <typename T, int KV, bool PEER>
 __global__ void __launch_bounds__(kBlock)
 scatter_rows_kernel(const T *dy, const int32_t *perm,
                     const int32_t *seg_start, const int32_t *long_row,
                     const int32_t *long_first, const int32_t *meta,
                     float *__restrict__ grad, float *__restrict__ scratch, int vocab, int d,
                     int sub_groups, const int32_t *row_begin,
-                    const int32_t *row_end, int rows_cta) {
+                    const int32_t *row_end, int rows_cta, const __grid_constant__ PeerOut po) {
   pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
@@ -503,6 +522,7 @@ scatter_rows_kernel(const T *dy, const int32_t *perm,
 #pragma unroll
     for (int u = 0; u < U; u++) {
       if (state[u] < 0) continue;
+      if (PEER && state[u] == 0) continue;  // nothing to send for a row without local tokens
 #pragma unroll
       for (int k = 0; k < KV; k++) {
 #pragma unroll
@@ -514,7 +534,7 @@ scatter_rows_kernel(const T *dy, const int32_t *perm,
           for (int q = 0; q < E; q++) acc[k][q] += f[q];
         }
       }
-      store_row<T, KV>(grad + static_cast<size_t>(v_first + rl0 + u * ty) * d, cv0, tx, ncv, acc);
+      store_row<T, KV>(out_row_ptr<PEER>(grad, po, v_first + rl0 + u * ty, d), cv0, tx, ncv, acc);
     }
   }
   // Rows with 2..kSubLen tokens.
@@ -525,7 +545,7 @@ scatter_rows_kernel(const T *dy, const int32_t *perm,
       sum_tokens<T, KV>(dy, [&](int j) { return s_perm[j - p0]; }, b, e, d, cv0, tx, ncv, acc);
     else
       sum_tokens<T, KV>(dy, [&](int j) { return ld_co(perm + j); }, b, e, d, cv0, tx, ncv, acc);
-    store_row<T, KV>(grad + static_cast<size_t>(v_first + rl) * d, cv0, tx, ncv, acc);
+    store_row<T, KV>(out_row_ptr<PEER>(grad, po, v_first + rl, d), cv0, tx, ncv, acc);
   }
 }
 
@@ -537,10 +557,12 @@ scatter_rows_kernel(const T *dy, const int32_t *perm,
 constexpr int kCombineSlices = 8;
 static_assert(kCombineSlices * 32 == kBlock, "one warp per slice");
 
+template <bool PEER>
 __global__ void __launch_bounds__(kBlock)
 combine_long_kernel(const float *scratch, const int32_t *long_row,
                     const int32_t *long_first, const int32_t *meta,
-                    float *__restrict__ grad, int d, const int32_t *slot_map) {
+                    float *__restrict__ grad, int d, const int32_t *slot_map,
+                    const __grid_constant__ PeerOut po) {
   pdl_prologue();
   __shared__ float4 part[kCombineSlices][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -572,7 +594,7 @@ combine_long_kernel(const float *scratch, const int32_t *long_row,
       }
       const int v = long_row[li];
       const int out_row = slot_map != nullptr ? slot_map[v] : v;  // compact mode: the row's slot
-      __stcs(reinterpret_cast<float4 *>(grad + static_cast<size_t>(out_row) * d + c), r);
+      __stcs(reinterpret_cast<float4 *>(out_row_ptr<PEER>(grad, po, out_row, d) + c), r);
     }
   }
 }
@@ -739,9 +761,44 @@ expand_rows_kernel(const float *compact, const int32_t *slot_map,
   }
 }
 
+// Second half of the peer exchange, run by the owner of a row.  For each owned slot (slots me,
+// me+n, me+2n, ... of the compacted row list) the partial sums that arrived from the n source
+// ranks are added in rank order (what did not arrive is zero), the receive rows are put back to
+// zero for the next step, and the sum is stored into row used_rows[slot] of EVERY rank's dense
+// gradient table through the peer mappings: reduction, broadcast and the expansion into the
+// dense layout are one pass.  One CTA per owned slot, a thread owns float4 columns.
+struct PeerTables {
+  float *grad[kMaxPeers];  // every rank's dense [vocab, d] gradient as mapped into this GPU
+  int n, me, cap;
+};
+
+__global__ void __launch_bounds__(kBlock)
+reduce_broadcast_kernel(float *recv, const int32_t *used_rows, const int32_t *header, int d,
+                        const __grid_constant__ PeerTables pt) {
+  pdl_prologue();
+  const int used = ld_co(header);
+  const int nvec = d / 4;
+  for (int j = blockIdx.x; pt.me + j * pt.n < used; j += gridDim.x) {
+    const int v = ld_co(used_rows + pt.me + j * pt.n);
+    for (int c = threadIdx.x; c < nvec; c += kBlock) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int src = 0; src < pt.n; src++) {
+        float4 *cell = reinterpret_cast<float4 *>(recv + (static_cast<size_t>(src) * pt.cap + j) * d) + c;
+        const float4 p = __ldcg(cell);  // written by a peer: read at L2, never through L1
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        const bool nonzero = ((__float_as_uint(p.x) | __float_as_uint(p.y) | __float_as_uint(p.z) |
+                               __float_as_uint(p.w)) << 1) != 0;
+        if (nonzero) __stcg(cell, make_float4(0.f, 0.f, 0.f, 0.f));
+      }
+      for (int q = 0; q < pt.n; q++)
+        __stcs(reinterpret_cast<float4 *>(pt.grad[q] + static_cast<size_t>(v) * d) + c, acc);
+    }
+  }
+}
+
 template <typename T, int KV>
 int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *grad, int out_rows, int d,
-                   BlockShape bs, const Compact *compact, cudaStream_t st) {
+                   BlockShape bs, const Compact *compact, const PeerOut *peer, cudaStream_t st) {
   constexpr int E = Store<T>::kPerVec;
   const int ncv = d / E;
   // Sub-segment groups loop over the sub-segments, so a few hundred CTAs cover any count.
@@ -749,10 +806,15 @@ int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *gr
   const int rows_cta = bs.ty > kScatterRowsPerCta ? bs.ty : kScatterRowsPerCta;
   const int row_groups = ceil_div(out_rows, rows_cta);
   dim3 grid(sub_groups + row_groups, ceil_div(ncv, bs.tx * KV));
-  launch_pdl(scatter_rows_kernel<T, KV>, grid, dim3(bs.tx, bs.ty), 0, st,
-             static_cast<const T *>(dy), perm, p.seg_start, p.long_row, p.long_first, p.meta, grad, p.scratch,
-             out_rows, d, sub_groups, compact ? compact->row_begin : nullptr,
-             compact ? compact->row_end : nullptr, rows_cta);
+  const PeerOut none{};
+  auto go = [&](auto kern) {
+    launch_pdl(kern, grid, dim3(bs.tx, bs.ty), 0, st, static_cast<const T *>(dy), perm, p.seg_start, p.long_row,
+               p.long_first, p.meta, grad, p.scratch, out_rows, d, sub_groups,
+               compact ? compact->row_begin : nullptr, compact ? compact->row_end : nullptr, rows_cta,
+               peer ? *peer : none);
+  };
+  if (peer) go(scatter_rows_kernel<T, KV, true>);
+  else go(scatter_rows_kernel<T, KV, false>);
   DLB_LAUNCH_CHECK("scatter_rows");
   return DLB_OK;
 }
@@ -760,7 +822,7 @@ int launch_scatter(const Plan &p, const void *dy, const int32_t *perm, float *gr
 // out_rows: table rows (dense) or used rows (compact: `grad` is then the [used, d] buffer).
 template <typename T>
 int scatter_typed(const Plan &p, const void *dy, float *grad, int out_rows, int d, const Compact *compact,
-                  cudaStream_t st) {
+                  cudaStream_t st, const PeerOut *peer = nullptr) {
   constexpr int E = Store<T>::kPerVec;
   const int32_t *perm = p.vals[p.passes & 1];
   // bf16 input: rows of grad and scratch are written 32 bytes at a time (d % 8 == 0 makes row starts 32-byte aligned).
@@ -779,13 +841,17 @@ int scatter_typed(const Plan &p, const void *dy, float *grad, int out_rows, int 
   const BlockShape bs = shape_for(ncv);
   const int need = ceil_div(ncv, bs.tx);
   int rc;
-  if (need >= 4) rc = launch_scatter<T, 4>(p, dy, perm, grad, out_rows, d, bs, compact, st);
-  else if (need >= 2) rc = launch_scatter<T, 2>(p, dy, perm, grad, out_rows, d, bs, compact, st);
-  else rc = launch_scatter<T, 1>(p, dy, perm, grad, out_rows, d, bs, compact, st);
+  if (need >= 4) rc = launch_scatter<T, 4>(p, dy, perm, grad, out_rows, d, bs, compact, peer, st);
+  else if (need >= 2) rc = launch_scatter<T, 2>(p, dy, perm, grad, out_rows, d, bs, compact, peer, st);
+  else rc = launch_scatter<T, 1>(p, dy, perm, grad, out_rows, d, bs, compact, peer, st);
   if (rc != DLB_OK) return rc;
   const int grid = 8 * sm_count();  // 8 CTAs fit an SM; each loops over (long row, column block) items
-  launch_pdl(combine_long_kernel, grid, kBlock, 0, st, p.scratch, p.long_row, p.long_first, p.meta, grad, d,
-             compact ? compact->slot_map : nullptr);
+  if (peer)
+    launch_pdl(combine_long_kernel<true>, grid, kBlock, 0, st, p.scratch, p.long_row, p.long_first, p.meta, grad, d,
+               compact->slot_map, *peer);
+  else
+    launch_pdl(combine_long_kernel<false>, grid, kBlock, 0, st, p.scratch, p.long_row, p.long_first, p.meta, grad, d,
+               compact ? compact->slot_map : nullptr, PeerOut{});
   DLB_LAUNCH_CHECK("combine_long");
   return DLB_OK;
 }
@@ -951,5 +1017,66 @@ extern "C" int dlb_embed_expand_rows(const float *compact_rows, const void *comp
   launch_pdl(expand_rows_kernel, ceil_div(vocab, rows_per_cta), dim3(tx, ty), 0, as_stream(stream), compact_rows,
              c.slot_map, grad, vocab, d, what, rows_per_cta);
   DLB_LAUNCH_CHECK("expand_rows");
+  return DLB_OK;
+}
+
+// ---- multi-GPU: table gradient exchanged over peer memory ---------------------------------------
+
+static bool peer_args_ok(int n_ranks, int my_rank, int cap_rows) {
+  return n_ranks >= 1 && n_ranks <= kMaxPeers && my_rank >= 0 && my_rank < n_ranks && cap_rows >= 0;
+}
+
+extern "C" int dlb_embed_scatter_bwd_peer(const void *dy, void *local_plan, size_t local_plan_bytes,
+                                          const void *compact_ws, float *const *h_peer_recv, int n_ranks,
+                                          int my_rank, int cap_rows, int used_rows, int local_tokens, int vocab,
+                                          int d, int dtype, void *stream) {
+  DLB_REQUIRE(embed_args_ok(local_tokens, vocab, d) && used_rows >= 0 && used_rows <= vocab, DLB_ERR_INVALID_ARG,
+              "embed_scatter_bwd_peer: tokens=%d vocab=%d d=%d used_rows=%d", local_tokens, vocab, d, used_rows);
+  DLB_REQUIRE(peer_args_ok(n_ranks, my_rank, cap_rows) && h_peer_recv, DLB_ERR_INVALID_ARG,
+              "embed_scatter_bwd_peer: n_ranks=%d (1..%d) my_rank=%d cap_rows=%d", n_ranks, kMaxPeers, my_rank,
+              cap_rows);
+  DLB_REQUIRE(static_cast<int64_t>(cap_rows) * n_ranks >= used_rows, DLB_ERR_INVALID_ARG,
+              "embed_scatter_bwd_peer: %d rows per source hold fewer than the %d used rows", cap_rows, used_rows);
+  DLB_REQUIRE(local_plan && compact_ws && local_plan_bytes >= dlb_embed_workspace_bytes(local_tokens, vocab, d),
+              DLB_ERR_WORKSPACE, "embed_scatter_bwd_peer: plan workspaces required");
+  DLB_REQUIRE(dy || local_tokens == 0, DLB_ERR_INVALID_ARG, "embed_scatter_bwd_peer: null dy");
+  PeerOut po{};
+  po.n = n_ranks; po.me = my_rank; po.cap = cap_rows;
+  for (int r = 0; r < n_ranks; r++) {
+    DLB_REQUIRE(h_peer_recv[r] && aligned32(h_peer_recv[r]), DLB_ERR_INVALID_ARG,
+                "embed_scatter_bwd_peer: receive area of rank %d is null or not 32-byte aligned", r);
+    po.recv[r] = h_peer_recv[r];
+  }
+  const Plan p = make_plan(local_plan, local_tokens, vocab, d);
+  const Compact c = make_compact(const_cast<void *>(compact_ws), vocab);
+  if (dtype == DLB_F32) return scatter_typed<float>(p, dy, nullptr, used_rows, d, &c, as_stream(stream), &po);
+  if (dtype == DLB_BF16)
+    return scatter_typed<__nv_bfloat16>(p, dy, nullptr, used_rows, d, &c, as_stream(stream), &po);
+  set_error("embed_scatter_bwd_peer: unknown dtype %d", dtype);
+  return DLB_ERR_INVALID_ARG;
+}
+
+extern "C" int dlb_embed_reduce_broadcast_peer(float *my_recv, const void *compact_ws, float *const *h_peer_grad,
+                                               int n_ranks, int my_rank, int cap_rows, int vocab, int d,
+                                               void *stream) {
+  DLB_REQUIRE(vocab > 0 && d > 0 && d % 4 == 0, DLB_ERR_INVALID_ARG,
+              "embed_reduce_broadcast_peer: vocab=%d d=%d (a multiple of 4)", vocab, d);
+  DLB_REQUIRE(peer_args_ok(n_ranks, my_rank, cap_rows) && h_peer_grad, DLB_ERR_INVALID_ARG,
+              "embed_reduce_broadcast_peer: n_ranks=%d (1..%d) my_rank=%d cap_rows=%d", n_ranks, kMaxPeers, my_rank,
+              cap_rows);
+  DLB_REQUIRE(my_recv && aligned16(my_recv) && compact_ws, DLB_ERR_INVALID_ARG,
+              "embed_reduce_broadcast_peer: null or unaligned pointer");
+  PeerTables pt{};
+  pt.n = n_ranks; pt.me = my_rank; pt.cap = cap_rows;
+  for (int r = 0; r < n_ranks; r++) {
+    DLB_REQUIRE(h_peer_grad[r] && aligned16(h_peer_grad[r]), DLB_ERR_INVALID_ARG,
+                "embed_reduce_broadcast_peer: gradient table of rank %d is null or unaligned", r);
+    pt.grad[r] = h_peer_grad[r];
+  }
+  if (cap_rows == 0) return DLB_OK;
+  const Compact c = make_compact(const_cast<void *>(compact_ws), vocab);
+  const int grid = min(cap_rows, 16 * sm_count());
+  launch_pdl(reduce_broadcast_kernel, grid, kBlock, 0, as_stream(stream), my_recv, c.used_rows, c.header, d, pt);
+  DLB_LAUNCH_CHECK("reduce_broadcast");
   return DLB_OK;
 }

@@ -301,3 +301,32 @@ def ce_from_ids_bwd(target_ids, y_pred, eps=1e-10):
     grad = torch.empty_like(y_pred)
     check(capi.lib().dlb_ce_from_ids_bwd(ptr(target_ids), ptr(y_pred), ptr(grad), n, classes, eps, current_stream()))
     return grad
+
+
+# --- multi-GPU: table gradient over peer memory ---------------------------------------------
+def _addr_array(addresses):
+    """HOST array of device addresses (ints) for the h_* arguments of the peer entry points."""
+    import ctypes
+    return (ctypes.c_void_p * len(addresses))(*addresses)
+
+
+def embed_scatter_bwd_peer(dy, local_plan, compact_ws, peer_recv, my_rank, cap_rows, used_rows, vocab, stream=None):
+    """peer_recv: device addresses (ints) of every rank's receive area as mapped on this GPU."""
+    n, d = dy.shape
+    check(capi.lib().dlb_embed_scatter_bwd_peer(ptr(dy), ptr(local_plan), local_plan.numel(), ptr(compact_ws),
+                                                _addr_array(peer_recv), len(peer_recv), my_rank, cap_rows,
+                                                used_rows, n, vocab, d, dtype_of(dy),
+                                                current_stream() if stream is None else stream))
+
+
+def embed_reduce_broadcast_peer(my_recv, compact_ws, peer_grad, my_rank, cap_rows, vocab, d, stream=None):
+    """peer_grad: device addresses (ints) of every rank's dense [vocab, d] gradient as mapped on this GPU."""
+    check(capi.lib().dlb_embed_reduce_broadcast_peer(ptr(my_recv), ptr(compact_ws), _addr_array(peer_grad),
+                                                     len(peer_grad), my_rank, cap_rows, vocab, d,
+                                                     current_stream() if stream is None else stream))
+
+
+def peer_barrier(peer_flags, my_rank, channel, epoch, status, timeout_ms=2000, stream=None):
+    """peer_flags: device addresses (ints) of every rank's flag words; status: uint32/int32 device tensor [1]."""
+    check(capi.lib().dlb_peer_barrier(_addr_array(peer_flags), len(peer_flags), my_rank, channel, epoch, timeout_ms,
+                                      ptr(status), current_stream() if stream is None else stream))

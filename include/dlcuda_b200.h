@@ -277,6 +277,50 @@ DLB_API int dlb_grad_norm_clip(int n_groups, float *const *h_grads, const int *h
                                float max_norm, void *workspace, size_t workspace_bytes,
                                float *d_result, void *stream);
 
+/* ---- multi-GPU: table gradient exchanged over peer memory (one node) ----------
+ * No counterpart in the reference (it is single-GPU).  Alternative to the NCCL
+ * all-reduce of the compacted rows: the scatter-add and the exchange are fused.
+ * Used row number s (dlb_embed_compact_plan) belongs to rank s % n_ranks.
+ *
+ * dlb_embed_scatter_bwd_peer: dlb_embed_scatter_bwd_compact, except that each row
+ * this rank has tokens for is stored straight into the OWNER's receive area
+ * (h_peer_recv[owner], laid out [n_ranks sources][cap_rows][d] fp32, zero where
+ * nothing arrives) through the peer mapping; rows without local tokens send
+ * nothing.  h_peer_recv is a HOST array of n_ranks device addresses valid on the
+ * calling GPU (its own area at index my_rank).
+ *
+ * dlb_embed_reduce_broadcast_peer: for every row this rank owns, adds the n_ranks
+ * partial sums of its receive area in rank order (reproducible), puts the
+ * receive rows back to zero, and stores the sum into that row of EVERY rank's
+ * dense [vocab, d] gradient (h_peer_grad, peer mappings): reduction, broadcast
+ * and dense expansion in one pass.  Rows no rank uses are zeroed locally with
+ * dlb_embed_expand_rows(what = 1).
+ *
+ * Between the two calls, and after the second, all ranks must meet in
+ * dlb_peer_barrier, so that a rank reads what its peers wrote only after they
+ * wrote it.  The receive areas start zeroed (caller), followed by one barrier. */
+DLB_API int dlb_embed_scatter_bwd_peer(const void *dy, void *local_plan, size_t local_plan_bytes,
+                                       const void *compact_ws, float *const *h_peer_recv,
+                                       int n_ranks, int my_rank, int cap_rows, int used_rows,
+                                       int local_tokens, int vocab, int d, int dtype,
+                                       void *stream);
+DLB_API int dlb_embed_reduce_broadcast_peer(float *my_recv, const void *compact_ws,
+                                            float *const *h_peer_grad, int n_ranks, int my_rank,
+                                            int cap_rows, int vocab, int d, void *stream);
+
+/* Barrier between the ranks' streams over peer-mapped flags.  Every rank owns
+ * dlb_peer_flags_bytes() bytes of zero-initialised memory that all ranks have
+ * mapped (h_peer_flags: HOST array of n_ranks device addresses).  The call
+ * enqueues one small kernel: it announces `epoch` to every rank and waits until
+ * every rank has announced it.  Per channel (0..3) epochs must be 1, 2, 3, ... in
+ * call order, the same on all ranks.  The wait gives up after timeout_ms: bit
+ * `channel` of *d_status (device memory) is then set and the kernel returns; the
+ * caller checks it after synchronising.  One rank per GPU. */
+DLB_API size_t dlb_peer_flags_bytes(void);
+DLB_API int dlb_peer_barrier(uint32_t *const *h_peer_flags, int n_ranks, int my_rank,
+                             int channel, uint32_t epoch, int timeout_ms, uint32_t *d_status,
+                             void *stream);
+
 /* ---- pass-through dense ops (fp32 only, correctness implementations) ----------
  * The matrix products, row softmax and loss kernels that the reference's
  * TransformerLayer / LinearLayer / SoftmaxActivation / loss helpers run between

@@ -231,3 +231,66 @@ def test_compacted_multi_rank_gradient(vocab, d, n, ranks, storage):
     both = torch.full((vocab, d), 5.0, device="cuda")
     ops.embed_expand_rows(total, compact_ws, both, what=3)
     assert torch.equal(both, grad)
+
+
+@pytest.mark.parametrize("storage", ["fp32", "bf16"])
+@pytest.mark.parametrize("vocab,d,n,ranks", [(50, 64, 300, 2), (1000, 256, 5000, 4), (32000, 512, 16384, 8),
+                                             (97, 128, 4000, 3)])
+def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, storage):
+    """The peer-memory form of the table-gradient exchange, every rank's buffers on this one GPU and the
+    ranks run one after the other (no barrier is needed then): each rank pushes the rows it has tokens for
+    into the owners' receive areas, each owner adds what arrived in rank order and stores the sum into every
+    rank's dense table.  Every table must equal the single-rank dense gradient, twice in a row (the receive
+    areas must come back zeroed)."""
+    dt = torch.bfloat16 if storage == "bf16" else torch.float32
+    ids = zipf_ids(rng_for(71, 0), n, vocab)
+    dy = dev(rng_for(71, 1).standard_normal((n, d)).astype(np.float32), dt)
+    tids = dev(ids)
+    dense = scatter(dy, tids, vocab).cpu().numpy()
+    global_plan = ops.embed_sort_tokens(tids, vocab, d)
+    used_host = int(np.unique(ids).size)
+    cap = (min(vocab, n) + ranks - 1) // ranks
+    recv = [torch.zeros(ranks * cap * d, device="cuda") for _ in range(ranks)]
+    tables = [torch.full((vocab, d), 5.0, device="cuda") for _ in range(ranks)]
+    per = n // ranks
+    for attempt in range(2):
+        plans = []
+        for r in range(ranks):
+            lo, hi = r * per, (n if r == ranks - 1 else (r + 1) * per)
+            ids_r, dy_r = tids[lo:hi].contiguous(), dy[lo:hi].contiguous()
+            local_plan = ops.embed_sort_tokens(ids_r, vocab, d)
+            compact_ws = ops.embed_compact_plan(global_plan, n, local_plan, hi - lo, vocab, d)
+            used = int(compact_ws[:4].view(torch.int32)[0].item())
+            assert used == used_host
+            ops.embed_scatter_bwd_peer(dy_r, local_plan, compact_ws, [t.data_ptr() for t in recv], r, cap, used, vocab)
+            plans.append(compact_ws)
+        for r in range(ranks):
+            ops.embed_expand_rows(None, plans[r], tables[r], what=1)
+            ops.embed_reduce_broadcast_peer(recv[r], plans[r], [t.data_ptr() for t in tables], r, cap, vocab, d)
+        torch.cuda.synchronize()
+        for r in range(ranks):
+            assert rel_err(tables[r].cpu().numpy(), dense) <= 1e-5, (attempt, r)
+            assert float(recv[r].abs().sum()) == 0.0, "receive area must be zero again"
+            if r:
+                assert torch.equal(tables[r], tables[0])  # every rank holds the same bits
+            tables[r].fill_(7.0)
+
+
+def test_peer_barrier_single_rank_and_timeout():
+    """n = 1: the rank signals itself and passes.  A flag nobody sets: the wait runs out after the given time,
+    the status bit of the channel is set and the stream keeps working."""
+    flags = torch.zeros(capi.lib().dlb_peer_flags_bytes() // 4, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for epoch in (1, 2, 3):
+        ops.peer_barrier([flags.data_ptr()], 0, 1, epoch, status, timeout_ms=1000)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert int(flags[16].item()) == 3  # channel 1, source rank 0
+    # two ranks, but the other one never arrives (its flag array is a second buffer that nothing writes)
+    other = torch.zeros_like(flags)
+    ops.peer_barrier([flags.data_ptr(), other.data_ptr()], 0, 2, 1, status, timeout_ms=50)
+    probe = ops.residual_add(torch.ones(8, device="cuda"), torch.ones(8, device="cuda"))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1 << 2
+    assert int(other[2 * 16].item()) == 1      # the announcement to the absent rank was made
+    assert float(probe.sum()) == 16.0          # the context is alive
