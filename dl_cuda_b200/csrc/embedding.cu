@@ -781,17 +781,32 @@ reduce_broadcast_kernel(float *recv, const int32_t *used_rows, const int32_t *he
   for (int j = blockIdx.x; pt.me + j * pt.n < used; j += gridDim.x) {
     const int v = ld_co(used_rows + pt.me + j * pt.n);
     for (int c = threadIdx.x; c < nvec; c += kBlock) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int src = 0; src < pt.n; src++) {
-        float4 *cell = reinterpret_cast<float4 *>(recv + (static_cast<size_t>(src) * pt.cap + j) * d) + c;
-        const float4 p = __ldcg(cell);  // written by a peer: read at L2, never through L1
-        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-        const bool nonzero = ((__float_as_uint(p.x) | __float_as_uint(p.y) | __float_as_uint(p.z) |
-                               __float_as_uint(p.w)) << 1) != 0;
-        if (nonzero) __stcg(cell, make_float4(0.f, 0.f, 0.f, 0.f));
+      // every source's cell is loaded before the first add, so the n L2 reads are in flight together
+      float4 part[kMaxPeers];
+#pragma unroll
+      for (int src = 0; src < kMaxPeers; src++) {
+        if (src < pt.n) {
+          // written by a peer: read at L2, never through L1
+          part[src] = __ldcg(reinterpret_cast<const float4 *>(recv + (static_cast<size_t>(src) * pt.cap + j) * d) + c);
+        }
       }
-      for (int q = 0; q < pt.n; q++)
-        __stcs(reinterpret_cast<float4 *>(pt.grad[q] + static_cast<size_t>(v) * d) + c, acc);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int src = 0; src < kMaxPeers; src++) {
+        if (src < pt.n) {
+          const float4 p = part[src];
+          acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+          const bool nonzero = ((__float_as_uint(p.x) | __float_as_uint(p.y) | __float_as_uint(p.z) |
+                                 __float_as_uint(p.w)) << 1) != 0;
+          if (nonzero)
+            __stcg(reinterpret_cast<float4 *>(recv + (static_cast<size_t>(src) * pt.cap + j) * d) + c,
+                   make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < kMaxPeers; q++) {
+        if (q < pt.n) __stcs(reinterpret_cast<float4 *>(pt.grad[q] + static_cast<size_t>(v) * d) + c, acc);
+      }
     }
   }
 }

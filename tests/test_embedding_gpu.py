@@ -247,6 +247,12 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
     dy = dev(rng_for(71, 1).standard_normal((n, d)).astype(np.float32), dt)
     tids = dev(ids)
     dense = scatter(dy, tids, vocab).cpu().numpy()
+    # The sums in double.  Hot rows add thousands of N(0,1) terms in fp32 and the error measure divides by the
+    # rms of a table that is mostly zero rows, so the single-rank gradient itself sits at 1.1e-5 from them at
+    # the largest case; every grouping is held to 3e-5 here.
+    exact = np.zeros((vocab, d), np.float64)
+    np.add.at(exact, ids, dy.float().cpu().numpy().astype(np.float64))
+    assert rel_err(dense, exact) <= 3e-5
     global_plan = ops.embed_sort_tokens(tids, vocab, d)
     used_host = int(np.unique(ids).size)
     cap = (min(vocab, n) + ranks - 1) // ranks
@@ -269,11 +275,14 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
             ops.embed_reduce_broadcast_peer(recv[r], plans[r], [t.data_ptr() for t in tables], r, cap, vocab, d)
         torch.cuda.synchronize()
         for r in range(ranks):
-            assert rel_err(tables[r].cpu().numpy(), dense) <= 1e-5, (attempt, r)
+            got = tables[r].cpu().numpy()
+            assert rel_err(got, exact) <= 3e-5, (attempt, r)
+            assert rel_err(got, dense) <= 3e-5, (attempt, r)  # two fp32 groupings of the same terms
             assert float(recv[r].abs().sum()) == 0.0, "receive area must be zero again"
             if r:
                 assert torch.equal(tables[r], tables[0])  # every rank holds the same bits
-            tables[r].fill_(7.0)
+        for t in tables:
+            t.fill_(7.0)
 
 
 def test_peer_barrier_single_rank_and_timeout():
