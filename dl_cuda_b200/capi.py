@@ -53,6 +53,9 @@ SIGNATURES = {
     "dlb_optim_step": (_i, [_i, _i, _p, _p, _p, _p, _p, _f, _f, _f, _f, _f, _f, _f, _p]),
     "dlb_grad_norm_workspace_bytes": (_sz, []),
     "dlb_grad_norm_clip": (_i, [_i, _p, _p, _f, _p, _sz, _p, _p]),
+    "dlb_checkpoint_body_bytes": (_sz, [_i, _p]),
+    "dlb_checkpoint_pack": (_i, [_i, _p, _p, _p, _sz, _p]),
+    "dlb_checkpoint_unpack": (_i, [_i, _p, _p, _p, _sz, _p]),
     "dlb_embed_scatter_bwd_peer": (_i, [_p, _p, _sz, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
     "dlb_embed_reduce_broadcast_peer": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dlb_peer_flags_bytes": (_sz, []),

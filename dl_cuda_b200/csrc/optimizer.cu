@@ -188,6 +188,38 @@ scale_grads_kernel(const __grid_constant__ GroupTable t, int items, const float 
   }
 }
 
+// Checkpoint body: per group one int32 size word followed by the group's floats, groups back to
+// back (the DLCU file after its 12-byte header).  word_offset[i] is where group i's size word sits.
+struct PackTable {
+  float *group[kMaxGroups];
+  long long word_offset[kMaxGroups];
+  int chunk_start[kMaxGroups + 1];
+  int size[kMaxGroups];
+  int count;
+};
+
+__global__ void __launch_bounds__(kBlock)
+checkpoint_copy_kernel(const __grid_constant__ PackTable t, int items, uint32_t *body, int to_body) {
+  pdl_prologue();
+  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    int lo = 0, hi = t.count;  // last group whose first item is <= item
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (t.chunk_start[mid] <= item) lo = mid; else hi = mid;
+    }
+    const int begin = (item - t.chunk_start[lo]) * kChunk;
+    const int end = min(t.size[lo], begin + kChunk);
+    uint32_t *words = body + t.word_offset[lo];
+    float *g = t.group[lo];
+    if (to_body) {
+      if (begin == 0 && threadIdx.x == 0) words[0] = static_cast<uint32_t>(t.size[lo]);
+      for (int i = begin + threadIdx.x; i < end; i += kBlock) words[1 + i] = __float_as_uint(g[i]);
+    } else {
+      for (int i = begin + threadIdx.x; i < end; i += kBlock) g[i] = __uint_as_float(words[1 + i]);
+    }
+  }
+}
+
 // Fills a table with groups [first, first+count) of the caller's arrays; returns the work items.
 int fill_table(GroupTable &t, int first, int count, float *const *params, float *const *grads,
                float *const *m, float *const *v, const int *sizes) {
@@ -287,4 +319,56 @@ extern "C" int dlb_grad_norm_clip(int n_groups, float *const *h_grads, const int
     }
   }
   return DLB_OK;
+}
+
+// ---- checkpoint staging ------------------------------------------------------------------------
+
+extern "C" size_t dlb_checkpoint_body_bytes(int n_groups, const int *h_sizes) {
+  if (n_groups < 0 || (n_groups > 0 && !h_sizes)) return 0;
+  size_t words = 0;
+  for (int i = 0; i < n_groups; i++) {
+    if (h_sizes[i] < 0) return 0;
+    words += 1 + static_cast<size_t>(h_sizes[i]);
+  }
+  return words * sizeof(uint32_t);
+}
+
+static int checkpoint_copy(const char *what, int n_groups, float *const *h_params, const int *h_sizes, void *d_body,
+                           size_t body_bytes, int to_body, void *stream) {
+  DLB_REQUIRE(groups_ok(n_groups, h_params, h_sizes), DLB_ERR_INVALID_ARG, "%s: bad group arrays", what);
+  DLB_REQUIRE(n_groups == 0 || (d_body && (reinterpret_cast<uintptr_t>(d_body) & 3u) == 0 &&
+                                body_bytes >= dlb_checkpoint_body_bytes(n_groups, h_sizes)),
+              DLB_ERR_WORKSPACE, "%s: a body buffer of %zu bytes is required", what,
+              dlb_checkpoint_body_bytes(n_groups, h_sizes));
+  long long offset = 0;
+  for (int first = 0; first < n_groups; first += kMaxGroups) {
+    PackTable t;
+    t.count = n_groups - first < kMaxGroups ? n_groups - first : kMaxGroups;
+    int items = 0;
+    for (int i = 0; i < t.count; i++) {
+      t.group[i] = h_params[first + i];
+      t.size[i] = h_sizes[first + i];
+      t.word_offset[i] = offset;
+      t.chunk_start[i] = items;
+      // a group of size 0 still owns its size word: give it one (empty) work item
+      items += h_sizes[first + i] > 0 ? ceil_div(h_sizes[first + i], kChunk) : 1;
+      offset += 1 + static_cast<long long>(h_sizes[first + i]);
+    }
+    t.chunk_start[t.count] = items;
+    launch_pdl(checkpoint_copy_kernel, grid_for(items, sm_count() * 16), kBlock, 0, as_stream(stream), t, items,
+               static_cast<uint32_t *>(d_body), to_body);
+    DLB_LAUNCH_CHECK(what);
+  }
+  return DLB_OK;
+}
+
+extern "C" int dlb_checkpoint_pack(int n_groups, float *const *h_params, const int *h_sizes, void *d_body,
+                                   size_t body_bytes, void *stream) {
+  return checkpoint_copy("checkpoint_pack", n_groups, h_params, h_sizes, d_body, body_bytes, 1, stream);
+}
+
+extern "C" int dlb_checkpoint_unpack(int n_groups, float *const *h_params, const int *h_sizes, const void *d_body,
+                                     size_t body_bytes, void *stream) {
+  return checkpoint_copy("checkpoint_unpack", n_groups, h_params, h_sizes, const_cast<void *>(d_body), body_bytes, 0,
+                         stream);
 }

@@ -330,3 +330,23 @@ def peer_barrier(peer_flags, my_rank, channel, epoch, status, timeout_ms=2000, s
     """peer_flags: device addresses (ints) of every rank's flag words; status: uint32/int32 device tensor [1]."""
     check(capi.lib().dlb_peer_barrier(_addr_array(peer_flags), len(peer_flags), my_rank, channel, epoch, timeout_ms,
                                       ptr(status), current_stream() if stream is None else stream))
+
+
+# --- checkpoint staging ---------------------------------------------------------------------
+def checkpoint_pack(params):
+    """The DLCU file body (per group: int32 size, then the floats) of a list of fp32 tensors, as a uint8 device tensor."""
+    import ctypes
+    n = len(params)
+    sizes = (ctypes.c_int * n)(*[p.numel() for p in params])
+    nbytes = capi.lib().dlb_checkpoint_body_bytes(n, sizes)
+    body = torch.empty(nbytes, dtype=torch.uint8, device=params[0].device if n else "cuda")
+    check(capi.lib().dlb_checkpoint_pack(n, _ptr_array(params), sizes, ptr(body), nbytes, current_stream()))
+    return body
+
+
+def checkpoint_unpack(body, params):
+    """Scatters a DLCU file body (uint8 device tensor) into the fp32 tensors of `params`, in place."""
+    import ctypes
+    n = len(params)
+    sizes = (ctypes.c_int * n)(*[p.numel() for p in params])
+    check(capi.lib().dlb_checkpoint_unpack(n, _ptr_array(params), sizes, ptr(body), body.numel(), current_stream()))

@@ -123,63 +123,85 @@ public:
 
   std::vector<Operation *> &get_operations() { return ops_; }
 
+  // The file is assembled on the device (one launch writes every group's size word and values
+  // into one buffer), copied to pinned host memory in one transfer and written with one fwrite.
   bool save_weights(const std::string &path) {
-    std::vector<ParamGroup> groups = all_groups();
-    // Stage the whole file in host memory, then write it in one go.
-    std::vector<char> bytes;
-    auto put = [&bytes](const void *p, size_t n) {
-      const char *c = static_cast<const char *>(p);
-      bytes.insert(bytes.end(), c, c + n);
-    };
-    put("DLCU", 4);
-    const int version = kVersion, count = static_cast<int>(groups.size());
-    put(&version, sizeof(int));
-    put(&count, sizeof(int));
-    std::vector<float> host;
-    for (const ParamGroup &g : groups) {
-      put(&g.size, sizeof(int));
-      host.resize(static_cast<size_t>(g.size));
-      CUDA_CHECK(cudaMemcpy(host.data(), g.params, sizeof(float) * host.size(), cudaMemcpyDeviceToHost));
-      put(host.data(), sizeof(float) * host.size());
+    const GroupArrays g = group_arrays();
+    const size_t body = dlb_checkpoint_body_bytes(static_cast<int>(g.sizes.size()), g.sizes.data());
+    PinnedFile file(kHeaderBytes + body);
+    memcpy(file.bytes, "DLCU", 4);
+    const int version = kVersion, count = static_cast<int>(g.sizes.size());
+    memcpy(file.bytes + 4, &version, sizeof(int));
+    memcpy(file.bytes + 8, &count, sizeof(int));
+    if (body > 0) {
+      DeviceBuffer<unsigned char> staging(body);
+      DLB_CHECK(dlb_checkpoint_pack(count, g.params.data(), g.sizes.data(), staging.get(), body, nullptr));
+      CUDA_CHECK(cudaMemcpy(file.bytes + kHeaderBytes, staging.get(), body, cudaMemcpyDeviceToHost));
     }
     FILE *f = fopen(path.c_str(), "wb");
     if (!f) return false;
-    const bool ok = fwrite(bytes.data(), 1, bytes.size(), f) == bytes.size();
+    const bool ok = fwrite(file.bytes, 1, file.size, f) == file.size;
     return (fclose(f) == 0) && ok;
   }
 
-  // Any mismatch (magic, version, group count, a group's size, a short file)
-  // returns false.  Groups read before the mismatch have already been uploaded,
-  // as in the reference.
+  // Any mismatch (magic, version, group count, a group's size, a short file) returns false and
+  // leaves every parameter untouched: the file is validated on the host before its body goes to
+  // the device in one transfer and one launch scatters it into the groups.
   bool load_weights(const std::string &path) {
     FILE *f = fopen(path.c_str(), "rb");
     if (!f) return false;
-    bool ok = false;
-    do {
-      char magic[4];
-      int version = 0, count = 0;
-      if (fread(magic, 1, 4, f) != 4 || memcmp(magic, "DLCU", 4) != 0) break;
-      if (fread(&version, sizeof(int), 1, f) != 1 || version != kVersion) break;
-      std::vector<ParamGroup> groups = all_groups();
-      if (fread(&count, sizeof(int), 1, f) != 1 || count != static_cast<int>(groups.size())) break;
-      std::vector<float> host;
-      size_t done = 0;
-      for (const ParamGroup &g : groups) {
-        int size = 0;
-        if (fread(&size, sizeof(int), 1, f) != 1 || size != g.size) break;
-        host.resize(static_cast<size_t>(size));
-        if (fread(host.data(), sizeof(float), host.size(), f) != host.size()) break;
-        CUDA_CHECK(cudaMemcpy(g.params, host.data(), sizeof(float) * host.size(), cudaMemcpyHostToDevice));
-        ++done;
-      }
-      ok = done == groups.size();
-    } while (false);
+    const GroupArrays g = group_arrays();
+    const size_t body = dlb_checkpoint_body_bytes(static_cast<int>(g.sizes.size()), g.sizes.data());
+    PinnedFile file(kHeaderBytes + body);
+    const size_t got = fread(file.bytes, 1, file.size, f);
     fclose(f);
-    return ok;
+    if (got != file.size || memcmp(file.bytes, "DLCU", 4) != 0) return false;
+    int version = 0, count = 0;
+    memcpy(&version, file.bytes + 4, sizeof(int));
+    memcpy(&count, file.bytes + 8, sizeof(int));
+    if (version != kVersion || count != static_cast<int>(g.sizes.size())) return false;
+    size_t at = kHeaderBytes;
+    for (int size : g.sizes) {
+      int stored = 0;
+      memcpy(&stored, file.bytes + at, sizeof(int));
+      if (stored != size) return false;
+      at += sizeof(int) + sizeof(float) * static_cast<size_t>(size);
+    }
+    if (body > 0) {
+      DeviceBuffer<unsigned char> staging(body);
+      CUDA_CHECK(cudaMemcpy(staging.get(), file.bytes + kHeaderBytes, body, cudaMemcpyHostToDevice));
+      DLB_CHECK(dlb_checkpoint_unpack(count, g.params.data(), g.sizes.data(), staging.get(), body, nullptr));
+      CUDA_CHECK(cudaDeviceSynchronize());  // the staging buffer is freed on return
+    }
+    return true;
   }
 
 private:
   static constexpr int kVersion = 1;
+  static constexpr size_t kHeaderBytes = 12;  // magic, version, group count
+
+  struct GroupArrays {
+    std::vector<float *> params;
+    std::vector<int> sizes;
+  };
+  GroupArrays group_arrays() {
+    GroupArrays g;
+    for (const ParamGroup &pg : all_groups()) {
+      g.params.push_back(pg.params);
+      g.sizes.push_back(pg.size);
+    }
+    return g;
+  }
+
+  // Page-locked host image of a weights file.
+  struct PinnedFile {
+    unsigned char *bytes = nullptr;
+    size_t size;
+    explicit PinnedFile(size_t n) : size(n) { CUDA_CHECK(cudaMallocHost(reinterpret_cast<void **>(&bytes), n ? n : 1)); }
+    PinnedFile(const PinnedFile &) = delete;
+    PinnedFile &operator=(const PinnedFile &) = delete;
+    ~PinnedFile() { cudaFreeHost(bytes); }
+  };
 
   std::vector<ParamGroup> all_groups() {
     std::vector<ParamGroup> groups;

@@ -277,6 +277,22 @@ DLB_API int dlb_grad_norm_clip(int n_groups, float *const *h_grads, const int *h
                                float max_norm, void *workspace, size_t workspace_bytes,
                                float *d_result, void *stream);
 
+/* ---- checkpoint staging -----------------------------------------------------
+ * The body of a DLCU weights file (everything after the 12-byte header 'DLCU',
+ * int32 version, int32 group count; src/sequential.cuh:161-205) is, per
+ * parameter group, one int32 size followed by that many floats.  pack writes
+ * exactly those bytes into one device buffer in a single launch, so that saving
+ * is ONE device-to-host copy instead of the reference's one per group
+ * (src/sequential.cuh:190-200); unpack scatters a body that was uploaded with
+ * ONE host-to-device copy back into the groups (the reference: :245-262).  The
+ * size words of the body are written by pack and ignored by unpack (the host
+ * validates them before uploading).  h_params / h_sizes are HOST arrays. */
+DLB_API size_t dlb_checkpoint_body_bytes(int n_groups, const int *h_sizes);
+DLB_API int dlb_checkpoint_pack(int n_groups, float *const *h_params, const int *h_sizes,
+                                void *d_body, size_t body_bytes, void *stream);
+DLB_API int dlb_checkpoint_unpack(int n_groups, float *const *h_params, const int *h_sizes,
+                                  const void *d_body, size_t body_bytes, void *stream);
+
 /* ---- multi-GPU: table gradient exchanged over peer memory (one node) ----------
  * No counterpart in the reference (it is single-GPU).  Alternative to the NCCL
  * all-reduce of the compacted rows: the scatter-add and the exchange are fused.

@@ -126,3 +126,23 @@ def test_clip_reads_this_calls_norm_when_calls_follow_each_other_without_a_sync(
         got = t.cpu().numpy()
         got_norm = float(np.sqrt(np.sum(got.astype(np.float64) ** 2)))
         assert abs(got_norm - 1.0) < 1e-4, (s, got_norm, norm0 * s)
+
+
+def test_checkpoint_body_pack_and_unpack():
+    """One launch lays the parameter groups out as the body of a DLCU weights file (int32 size, floats, per group);
+    one launch scatters such a body back.  More than 64 groups, an empty group and odd sizes included."""
+    g = rng_for(960)
+    sizes = [5, 4096, 0, 4097, 1, 12345] + [7 + i for i in range(70)]
+    params = [torch.from_numpy(g.standard_normal(n).astype(np.float32)).cuda() for n in sizes]
+    body = ops.checkpoint_pack(params).cpu().numpy()
+    want = b"".join(np.int32(n).tobytes() + p.cpu().numpy().tobytes() for n, p in zip(sizes, params))
+    assert body.tobytes() == want
+    fresh = [torch.full((n,), 3.0, device="cuda") for n in sizes]
+    ops.checkpoint_unpack(torch.from_numpy(body).cuda(), fresh)
+    for a, b in zip(params, fresh):
+        assert torch.equal(a, b)
+    small = torch.empty(8, dtype=torch.uint8, device="cuda")
+    import ctypes
+    arr = (ctypes.c_int * 1)(100)
+    assert capi.lib().dlb_checkpoint_pack(1, ops._ptr_array(params[1:2]), arr, small.data_ptr(), 8, None) \
+        == capi.ERR_WORKSPACE
