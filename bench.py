@@ -238,9 +238,18 @@ class Chain:
                 try:
                     from dl_cuda_b200.sharding import PeerExchange
                     self.peer = PeerExchange(dist.dist, V, D, min(V, Tg), dev)
+                    # One barrier on each channel before anything depends on it; the verdict is shared, so
+                    # either every rank uses the peer exchange or none does.
+                    self.peer.barrier(0)
+                    self.peer.barrier(1)
+                    verdict = torch.tensor([self.peer.timed_out()], dtype=torch.int32, device=dev)
+                    dist.dist.all_reduce(verdict, op=dist.dist.ReduceOp.MAX)
+                    if int(verdict.item()) != 0:
+                        raise RuntimeError("the peer barrier did not complete on every rank")
                     self.table_grad = self.peer.table_grad()
                     self.exchange_note = "scatter-add fused with a peer-memory exchange (owner-reduce, broadcast into the dense tables)"
                 except Exception as exc:  # no symmetric memory on this box / build
+                    self.peer = None
                     print(f"[bench] peer exchange unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
                     self.exchange_note += f" (peer exchange unavailable: {type(exc).__name__})"
             if self.peer is None:
