@@ -336,10 +336,11 @@ class Chain:
             mark()
         else:
             # Compacted form: only the rows some rank uses are summed, all-reduced and expanded.
-            self.plan_ready.synchronize()  # the row count is a host argument of the calls below
-            used = int(self.h_used[0])
             if self.peer is not None:
                 px, ops = self.peer, self.ops
+                # no host wait: the launch is sized from an upper bound, the kernels read the exact count
+                torch.cuda.current_stream().wait_event(self.plan_ready)
+                used = min(V, self.ids_all.numel())
                 # every rank pushes the rows it has tokens for into their owners' receive areas
                 ops.embed_scatter_bwd_peer(self.dx1, self.ws_embed, self.ws_compact, px.recv_ptrs, px.rank, px.cap_rows,
                                            used, V, stream=st)
@@ -359,6 +360,8 @@ class Chain:
                     torch.cuda.current_stream().synchronize()
                     return float(self.h_result[0])
                 return None
+            self.plan_ready.synchronize()  # the row count is a host argument of the calls below
+            used = int(self.h_used[0])
             chk(lib.dlb_embed_scatter_bwd_compact(p(self.dx1), p(self.ws_embed), self.ws_embed.numel(),
                                                   p(self.ws_compact), p(self.compact_rows), used, T, V, D, code, st))
             mark()

@@ -431,6 +431,7 @@ constexpr int kScatterPermCap = 1024;
 constexpr int kMaxPeers = 16;
 struct PeerOut {
   float *recv[kMaxPeers];  // every rank's receive area as mapped into this GPU's address space
+  const int32_t *used;     // device word holding the number of used rows (the compact plan's header)
   int n, me, cap;          // ranks, this rank, rows per source in a receive area
 };
 
@@ -477,6 +478,12 @@ scatter_rows_kernel(const T *dy, const int32_t *perm,
     return;
   }
   const int v_first = (blockIdx.x - sub_groups) * rows_cta;
+  // Peer mode: the host may have sized the grid from an upper bound of the used rows (it need not
+  // wait for the plan); the exact count is read here and surplus CTAs leave.
+  if constexpr (PEER) {
+    vocab = min(vocab, ld_co(po.used));
+    if (v_first >= vocab) return;
+  }
   // Output row r takes the sorted tokens [begin, end).  Dense mode: r is the table row and the
   // range is seg_start[r], seg_start[r+1].  Compact mode (row_begin given): r is a slot of the
   // compacted row list, `vocab` is the number of slots, and the ranges come from row_begin/end.
@@ -1064,6 +1071,7 @@ extern "C" int dlb_embed_scatter_bwd_peer(const void *dy, void *local_plan, size
   }
   const Plan p = make_plan(local_plan, local_tokens, vocab, d);
   const Compact c = make_compact(const_cast<void *>(compact_ws), vocab);
+  po.used = c.header;
   if (dtype == DLB_F32) return scatter_typed<float>(p, dy, nullptr, used_rows, d, &c, as_stream(stream), &po);
   if (dtype == DLB_BF16)
     return scatter_typed<__nv_bfloat16>(p, dy, nullptr, used_rows, d, &c, as_stream(stream), &po);

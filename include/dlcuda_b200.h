@@ -303,7 +303,10 @@ DLB_API int dlb_checkpoint_unpack(int n_groups, float *const *h_params, const in
  * (h_peer_recv[owner], laid out [n_ranks sources][cap_rows][d] fp32, zero where
  * nothing arrives) through the peer mapping; rows without local tokens send
  * nothing.  h_peer_recv is a HOST array of n_ranks device addresses valid on the
- * calling GPU (its own area at index my_rank).
+ * calling GPU (its own area at index my_rank).  used_rows may be the exact
+ * number of used rows or any upper bound of it (e.g. min(vocab, all tokens)):
+ * it only sizes the launch, the kernels read the exact count from the plan on
+ * the device, so the host need not wait for the plan.
  *
  * dlb_embed_reduce_broadcast_peer: for every row this rank owns, adds the n_ranks
  * partial sums of its receive area in rank order (reproducible), puts the

@@ -45,7 +45,8 @@ def main():
         table.fill_(float(3 + step))  # stale contents must vanish
         torch.cuda.synchronize()
         dist.barrier()                # nobody pushes rows into a table that is still being filled
-        ops.embed_scatter_bwd_peer(dy, local_plan, compact, px.recv_ptrs, rank, px.cap_rows, used, vocab)
+        ops.embed_scatter_bwd_peer(dy, local_plan, compact, px.recv_ptrs, rank, px.cap_rows,
+                                   used if step == 0 else min(vocab, total), vocab)
         side.wait_stream(torch.cuda.current_stream())
         ops.embed_expand_rows(None, compact, table, what=1, stream=side.cuda_stream)
         px.barrier(0)
