@@ -678,6 +678,17 @@ def profile_case(name):
             ops.embed_gather_fwd(table, ids, pe, S, out=out)
             ops.embed_sort_tokens(ids, V, D, workspace=ws)
             ops.embed_scatter_bwd(dy, ids, V, ws, grad=grad)
+    elif kind == "optim":
+        # AdamW over six groups of 8 Mi parameters, then the gradient norm + clip (fp32 only)
+        sizes = [8 << 20] * 6
+        params = [randn(n) for n in sizes]
+        grads = [randn(n) for n in sizes]
+        m = [torch.zeros(n, device=dev) for n in sizes]
+        v = [torch.zeros(n, device=dev) for n in sizes]
+        result = torch.empty(3, device=dev)
+        for step in range(1, 4):
+            ops.grad_norm_clip(grads, 1.0, result=result)
+            ops.optim_step(capi.OPT_ADAMW, params, grads, m, v, lr=1e-3, step=step)
     else:
         raise SystemExit(f"unknown case {name}; choose from {PROFILE_CASES}")
     torch.cuda.synchronize()
@@ -686,6 +697,7 @@ def profile_case(name):
 
 
 PROFILE_CASES = [f"{k}_{s}" for k in ("ln_fwd", "ln_bwd", "ln_bwd2", "relu", "tanh", "embed") for s in ("fp32", "bf16")]
+PROFILE_CASES.append("optim_fp32")
 
 
 # --------------------------------------------------------------------------- main

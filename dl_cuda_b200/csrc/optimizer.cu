@@ -296,7 +296,7 @@ extern "C" int dlb_grad_norm_clip(int n_groups, float *const *h_grads, const int
   cudaStream_t st = as_stream(stream);
   float *partial = static_cast<float *>(workspace);
   // Every launch uses the same grid so that partial[b] accumulates across launches.
-  const int grid = grid_for(INT32_MAX, min(kNormPartials, sm_count() * 4));
+  const int grid = grid_for(INT32_MAX, min(kNormPartials, sm_count() * 6));
   bool any = false;
   for (int first = 0; first < n_groups; first += kMaxGroups) {
     GroupTable t;
