@@ -294,13 +294,11 @@ class Chain:
         # backward: in the headline pass it is built on a side stream, beside the forward kernels.
         plan_stream = self.side if marks is None else torch.cuda.current_stream()
         pst = plan_stream.cuda_stream
+        if self.dist.active:
+            # every rank needs every rank's ids to number the table rows used anywhere
+            self.dist.dist.all_gather_into_tensor(self.ids_all, self.ids)
         if marks is None:
             self.side.wait_stream(torch.cuda.current_stream())
-        if self.dist.active:
-            # every rank needs every rank's ids to number the table rows used anywhere; the gather
-            # rides on the plan's stream, so the forward kernels do not wait for it
-            with torch.cuda.stream(plan_stream):
-                self.dist.dist.all_gather_into_tensor(self.ids_all, self.ids)
         chk(lib.dlb_embed_sort_tokens(p(self.ids), p(self.ws_embed), self.ws_embed.numel(), T, V, D, pst))
         if self.dist.active:
             Tg = self.ids_all.numel()
@@ -347,15 +345,13 @@ class Chain:
                 ops.embed_scatter_bwd_peer(self.dx1, self.ws_embed, self.ws_compact, px.recv_ptrs, px.rank, px.cap_rows,
                                            used, V, stream=st)
                 mark()
-                # beside the exchange, on the second stream: the table rows no rank uses are zeroed (local work, waits
-                # for nobody), then the small gradients are all-reduced
+                # rows no rank uses are zeroed locally, beside the exchange
                 self.side.wait_stream(torch.cuda.current_stream())
                 chk(lib.dlb_embed_expand_rows(None, p(self.ws_compact), p(self.table_grad), V, D, 1, self.side.cuda_stream))
-                with torch.cuda.stream(self.side):
-                    self.dist.dist.all_reduce(self.small_grads)
                 self.zero_done.record(self.side)
                 px.barrier(0, stream=st)      # all partial rows have arrived
                 ops.embed_reduce_broadcast_peer(px.recv, self.ws_compact, px.grad_ptrs, px.rank, px.cap_rows, V, D, stream=st)
+                self.dist.dist.all_reduce(self.small_grads)
                 torch.cuda.current_stream().wait_event(self.zero_done)
                 px.barrier(1, stream=st)      # every rank's table holds every reduced row; receive areas are zero again
                 mark()

@@ -444,10 +444,8 @@ __device__ __forceinline__ float *out_row_ptr(float *grad, const PeerOut &po, in
   }
 }
 
-// Up to two vectors per thread the kernel fits 64 registers (4 CTAs per SM instead of 3); with four
-// it would spill, so that variant keeps the registers it wants.
 template <typename T, int KV, bool PEER>
-__global__ void __launch_bounds__(kBlock, KV >= 4 ? 1 : 4)
+__global__ void __launch_bounds__(kBlock)
 scatter_rows_kernel(const T *dy, const int32_t *perm,
                     const int32_t *seg_start, const int32_t *long_row,
                     const int32_t *long_first, const int32_t *meta,
@@ -775,50 +773,48 @@ expand_rows_kernel(const float *compact, const int32_t *slot_map,
 // ranks are added in rank order (what did not arrive is zero), the receive rows are put back to
 // zero for the next step, and the sum is stored into row used_rows[slot] of EVERY rank's dense
 // gradient table through the peer mappings: reduction, broadcast and the expansion into the
-// dense layout are one pass.
+// dense layout are one pass.  One CTA per owned slot, a thread owns float4 columns.
 struct PeerTables {
   float *grad[kMaxPeers];  // every rank's dense [vocab, d] gradient as mapped into this GPU
   int n, me, cap;
 };
 
-// N: upper bound of the ranks this instantiation serves (sizes the register arrays).  A work item
-// is (owned slot, block of kBlock float4 columns): many small CTAs, each thread one column vector.
-template <int N>
 __global__ void __launch_bounds__(kBlock)
-reduce_broadcast_kernel(float *recv, const int32_t *used_rows, const int32_t *header, int d, int col_blocks,
+reduce_broadcast_kernel(float *recv, const int32_t *used_rows, const int32_t *header, int d,
                         const __grid_constant__ PeerTables pt) {
   pdl_prologue();
   const int used = ld_co(header);
   const int nvec = d / 4;
-  const int j = blockIdx.x / col_blocks;
-  const int c = (blockIdx.x % col_blocks) * kBlock + threadIdx.x;
-  if (pt.me + j * pt.n >= used || c >= nvec) return;
-  const int v = ld_co(used_rows + pt.me + j * pt.n);
-  // every source's cell is loaded before the first add, so the n L2 reads are in flight together
-  float4 part[N];
+  for (int j = blockIdx.x; pt.me + j * pt.n < used; j += gridDim.x) {
+    const int v = ld_co(used_rows + pt.me + j * pt.n);
+    for (int c = threadIdx.x; c < nvec; c += kBlock) {
+      // every source's cell is loaded before the first add, so the n L2 reads are in flight together
+      float4 part[kMaxPeers];
 #pragma unroll
-  for (int src = 0; src < N; src++) {
-    if (src < pt.n) {
-      // written by a peer: read at L2, never through L1
-      part[src] = __ldcg(reinterpret_cast<const float4 *>(recv + (static_cast<size_t>(src) * pt.cap + j) * d) + c);
+      for (int src = 0; src < kMaxPeers; src++) {
+        if (src < pt.n) {
+          // written by a peer: read at L2, never through L1
+          part[src] = __ldcg(reinterpret_cast<const float4 *>(recv + (static_cast<size_t>(src) * pt.cap + j) * d) + c);
+        }
+      }
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int src = 0; src < kMaxPeers; src++) {
+        if (src < pt.n) {
+          const float4 p = part[src];
+          acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+          const bool nonzero = ((__float_as_uint(p.x) | __float_as_uint(p.y) | __float_as_uint(p.z) |
+                                 __float_as_uint(p.w)) << 1) != 0;
+          if (nonzero)
+            __stcg(reinterpret_cast<float4 *>(recv + (static_cast<size_t>(src) * pt.cap + j) * d) + c,
+                   make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < kMaxPeers; q++) {
+        if (q < pt.n) __stcs(reinterpret_cast<float4 *>(pt.grad[q] + static_cast<size_t>(v) * d) + c, acc);
+      }
     }
-  }
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-  for (int src = 0; src < N; src++) {
-    if (src < pt.n) {
-      const float4 p = part[src];
-      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-      const bool nonzero = ((__float_as_uint(p.x) | __float_as_uint(p.y) | __float_as_uint(p.z) |
-                             __float_as_uint(p.w)) << 1) != 0;
-      if (nonzero)
-        __stcg(reinterpret_cast<float4 *>(recv + (static_cast<size_t>(src) * pt.cap + j) * d) + c,
-               make_float4(0.f, 0.f, 0.f, 0.f));
-    }
-  }
-#pragma unroll
-  for (int q = 0; q < N; q++) {
-    if (q < pt.n) __stcs(reinterpret_cast<float4 *>(pt.grad[q] + static_cast<size_t>(v) * d) + c, acc);
   }
 }
 
@@ -1102,15 +1098,8 @@ extern "C" int dlb_embed_reduce_broadcast_peer(float *my_recv, const void *compa
   }
   if (cap_rows == 0) return DLB_OK;
   const Compact c = make_compact(const_cast<void *>(compact_ws), vocab);
-  const int col_blocks = ceil_div(d / 4, kBlock);
-  const int64_t items = static_cast<int64_t>(cap_rows) * col_blocks;
-  DLB_REQUIRE(items <= INT32_MAX, DLB_ERR_UNSUPPORTED, "embed_reduce_broadcast_peer: cap_rows=%d d=%d too large", cap_rows, d);
-  const unsigned grid = static_cast<unsigned>(items);
-  cudaStream_t st = as_stream(stream);
-  if (n_ranks <= 2) launch_pdl(reduce_broadcast_kernel<2>, grid, kBlock, 0, st, my_recv, c.used_rows, c.header, d, col_blocks, pt);
-  else if (n_ranks <= 4) launch_pdl(reduce_broadcast_kernel<4>, grid, kBlock, 0, st, my_recv, c.used_rows, c.header, d, col_blocks, pt);
-  else if (n_ranks <= 8) launch_pdl(reduce_broadcast_kernel<8>, grid, kBlock, 0, st, my_recv, c.used_rows, c.header, d, col_blocks, pt);
-  else launch_pdl(reduce_broadcast_kernel<kMaxPeers>, grid, kBlock, 0, st, my_recv, c.used_rows, c.header, d, col_blocks, pt);
+  const int grid = min(cap_rows, 16 * sm_count());
+  launch_pdl(reduce_broadcast_kernel, grid, kBlock, 0, as_stream(stream), my_recv, c.used_rows, c.header, d, pt);
   DLB_LAUNCH_CHECK("reduce_broadcast");
   return DLB_OK;
 }
