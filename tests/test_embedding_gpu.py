@@ -306,3 +306,36 @@ def test_peer_barrier_single_rank_and_timeout():
     assert int(status.item()) == 1 << 2
     assert int(other[2 * 16].item()) == 1      # the announcement to the absent rank was made
     assert float(probe.sum()) == 16.0          # the context is alive
+
+
+def test_peer_entry_points_reject_bad_arguments():
+    lib = capi.lib()
+    vocab, d, n = 50, 64, 100
+    ids = dev(zipf_ids(rng_for(72, 0), n, vocab))
+    dy = dev(rng_for(72, 1).standard_normal((n, d)).astype(np.float32))
+    plan = ops.embed_sort_tokens(ids, vocab, d)
+    compact = ops.embed_compact_plan(plan, n, plan, n, vocab, d)
+    recv = torch.zeros(2 * 25 * d, device="cuda")
+    table = torch.zeros(vocab, d, device="cuda")
+    good = ops._addr_array([recv.data_ptr(), recv.data_ptr()])
+    args = lambda ranks, me, cap, used, arr=good: (dy.data_ptr(), plan.data_ptr(), plan.numel(), compact.data_ptr(), arr,
+                                                   ranks, me, cap, used, n, vocab, d, capi.F32, None)
+    assert lib.dlb_embed_scatter_bwd_peer(*args(0, 0, 25, 50)) == capi.ERR_INVALID_ARG      # no ranks
+    assert lib.dlb_embed_scatter_bwd_peer(*args(17, 0, 25, 50)) == capi.ERR_INVALID_ARG     # more than 16 ranks
+    assert lib.dlb_embed_scatter_bwd_peer(*args(2, 2, 25, 50)) == capi.ERR_INVALID_ARG      # rank out of range
+    assert lib.dlb_embed_scatter_bwd_peer(*args(2, 0, 10, 50)) == capi.ERR_INVALID_ARG      # receive areas too small
+    assert lib.dlb_embed_scatter_bwd_peer(*args(2, 0, 25, 50, ops._addr_array([recv.data_ptr(), None]))) \
+        == capi.ERR_INVALID_ARG                                                             # a null receive area
+    tables = ops._addr_array([table.data_ptr(), table.data_ptr()])
+    assert lib.dlb_embed_reduce_broadcast_peer(recv.data_ptr(), compact.data_ptr(), tables, 2, 5, 25, vocab, d, None) \
+        == capi.ERR_INVALID_ARG
+    assert lib.dlb_embed_reduce_broadcast_peer(None, compact.data_ptr(), tables, 2, 0, 25, vocab, d, None) \
+        == capi.ERR_INVALID_ARG
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    one = ops._addr_array([flags.data_ptr()])
+    assert lib.dlb_peer_barrier(one, 1, 0, 4, 1, 100, status.data_ptr(), None) == capi.ERR_INVALID_ARG    # channel
+    assert lib.dlb_peer_barrier(one, 1, 0, 0, 1, 0, status.data_ptr(), None) == capi.ERR_INVALID_ARG      # timeout
+    assert lib.dlb_peer_barrier(one, 1, 0, 0, 1, 100, None, None) == capi.ERR_INVALID_ARG                 # status
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and float(recv.abs().sum()) == 0.0 and float(table.abs().sum()) == 0.0
