@@ -98,6 +98,7 @@ inline T ceil_div(T a, T b) {
 
 // -------------------------------------------------------------- device side
 constexpr int kWarp = 32;
+constexpr int kMaxPeers = 16;  // most ranks (GPUs of one node) the peer-memory entry points take
 
 // First statement of every kernel: allow the next kernel of the stream to be
 // scheduled early, then wait for everything launched before this kernel.

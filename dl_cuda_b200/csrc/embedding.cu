@@ -428,7 +428,6 @@ constexpr int kScatterPermCap = 1024;
 // r % n, which sums it.  A rank that has tokens for the row stores its partial sum straight into
 // the owner's receive area, laid out [source rank][r / n][d], through the owner's peer mapping;
 // rows without local tokens are not sent (the receive area is zero where nothing arrives).
-constexpr int kMaxPeers = 16;
 struct PeerOut {
   float *recv[kMaxPeers];  // every rank's receive area as mapped into this GPU's address space
   const int32_t *used;     // device word holding the number of used rows (the compact plan's header)

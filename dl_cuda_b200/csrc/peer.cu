@@ -19,7 +19,6 @@
 namespace dlb {
 namespace {
 
-constexpr int kMaxPeers = 16;
 constexpr int kChannels = 4;
 
 struct PeerFlags {

@@ -296,7 +296,8 @@ DLB_API int dlb_checkpoint_unpack(int n_groups, float *const *h_params, const in
 /* ---- multi-GPU: table gradient exchanged over peer memory (one node) ----------
  * No counterpart in the reference (it is single-GPU).  Alternative to the NCCL
  * all-reduce of the compacted rows: the scatter-add and the exchange are fused.
- * Used row number s (dlb_embed_compact_plan) belongs to rank s % n_ranks.
+ * Used row number s (dlb_embed_compact_plan) belongs to rank s % n_ranks;
+ * n_ranks is at most 16.
  *
  * dlb_embed_scatter_bwd_peer: dlb_embed_scatter_bwd_compact, except that each row
  * this rank has tokens for is stored straight into the OWNER's receive area
