@@ -18,6 +18,7 @@
 #include "loss.cuh"
 #include "optimizer.cuh"
 #include "positional_encoding.cuh"
+#include "sampling.cuh"
 #include "scheduler.cuh"
 #include "sequential.cuh"
 #include "transformer.cuh"
@@ -150,6 +151,22 @@ LM_API void lm_schedule(float lr_max, float lr_min, int warmup, int epochs, floa
   CosineAnnealingScheduler cosine(lr_max, lr_min, epochs);
   WarmupScheduler schedule(lr_max, warmup, &cosine);
   for (int e = 0; e < epochs; e++) h_lr[e] = schedule.get_lr(e);
+}
+
+// Token sampling (host only): `draws` tokens from one probability row with the given temperature,
+// top-k (0 = off) and top-p (1 = off), from std::mt19937(seed).  h_filtered receives the row after
+// temperature, top-k and top-p (what the draw is made from).
+LM_API void lm_sample(const float *h_probs, int n, float temperature, int top_k, float top_p, unsigned seed,
+                      int draws, int *h_tokens, float *h_filtered) {
+  const std::vector<float> probs(h_probs, h_probs + n);
+  std::mt19937 rng(seed);
+  for (int i = 0; i < draws; i++) h_tokens[i] = sampleWithStrategy(probs, temperature, top_k, top_p, rng);
+  std::vector<float> filtered(probs);
+  if (temperature != 1.0f)
+    for (float &p : filtered) p = powf(p, 1.0f / temperature);
+  if (top_k > 0) applyTopK(filtered, top_k);
+  if (top_p < 1.0f) applyTopP(filtered, top_p);
+  std::memcpy(h_filtered, filtered.data(), sizeof(float) * n);
 }
 
 // The training loop of the reference's character language model
