@@ -270,3 +270,25 @@ def test_reference_char_lm_example_links_and_matches(tmp_path):
     # each implementation reloads the other's checkpoint
     run_char_lm("native", tmp_path / "r.bin", 0, load=True)
     run_char_lm("ref", tmp_path / "n.bin", 0, load=True)
+
+
+def test_reference_xor_example_matches():
+    """run_xor of the reference's examples_api.cu (LinearLayer, ReLU, Sigmoid, Adam, binary cross entropy) on both
+    header sets: same loss log, and both learn XOR."""
+    logs = {}
+    for which in ("native", "ref"):
+        binary = CHAR_LM[which]
+        if not binary.exists():
+            pytest.skip(f"{binary.name} not built (needs the reference checkout at build time)")
+        res = subprocess.run([str(binary), "xor", "1500", "100"], capture_output=True, text=True, timeout=300)
+        if res.returncode == 2:
+            pytest.skip(f"{binary.name} predates the xor mode: rebuild")
+        assert res.returncode == 0, res.stdout + res.stderr
+        bce = np.array([float(m) for m in re.findall(r"BCE: ([0-9.]+)", res.stdout)])
+        pred = np.array([float(m) for m in re.findall(r"-> ([0-9.]+) \(expected", res.stdout)])
+        assert bce.size == 15 and pred.size == 4
+        logs[which] = (bce, pred)
+    (bce_n, pred_n), (bce_r, pred_r) = logs["native"], logs["ref"]
+    assert np.allclose(bce_n, bce_r, rtol=2e-3, atol=2e-5)
+    assert np.allclose(pred_n, pred_r, atol=2e-3)
+    assert np.all(np.abs(pred_n - np.array([0, 1, 1, 0])) < 0.1), "XOR not learned"
