@@ -235,7 +235,7 @@ def test_compacted_multi_rank_gradient(vocab, d, n, ranks, storage):
 
 @pytest.mark.parametrize("storage", ["fp32", "bf16"])
 @pytest.mark.parametrize("vocab,d,n,ranks", [(50, 64, 300, 2), (1000, 256, 5000, 4), (32000, 512, 16384, 8),
-                                             (97, 128, 4000, 3)])
+                                             (97, 128, 4000, 3), (50, 64, 300, 1), (300, 4096, 2000, 16)])
 def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, storage):
     """The peer-memory form of the table-gradient exchange, every rank's buffers on this one GPU and the
     ranks run one after the other (no barrier is needed then): each rank pushes the rows it has tokens for
