@@ -348,15 +348,11 @@ class Chain:
                 # rows no rank uses are zeroed locally, beside the exchange
                 self.side.wait_stream(torch.cuda.current_stream())
                 chk(lib.dlb_embed_expand_rows(None, p(self.ws_compact), p(self.table_grad), V, D, 1, self.side.cuda_stream))
-                small_on_side = os.environ.get("DLB_TMP_SMALL_AR") == "side"
-                if small_on_side:
-                    with torch.cuda.stream(self.side):
-                        self.dist.dist.all_reduce(self.small_grads)
                 self.zero_done.record(self.side)
                 px.barrier(0, stream=st)      # all partial rows have arrived
                 ops.embed_reduce_broadcast_peer(px.recv, self.ws_compact, px.grad_ptrs, px.rank, px.cap_rows, V, D, stream=st)
-                if not small_on_side:
-                    self.dist.dist.all_reduce(self.small_grads)
+                # (issued on the second stream instead, this all-reduce changed nothing: 0.60 ms either way on 8 GPUs)
+                self.dist.dist.all_reduce(self.small_grads)
                 torch.cuda.current_stream().wait_event(self.zero_done)
                 px.barrier(1, stream=st)      # every rank's table holds every reduced row; receive areas are zero again
                 mark()
