@@ -541,6 +541,36 @@ def kernel_sweep(peak):
     add("relu_fwd", cfg1, T1 * F1 * 8, time_op(lambda: ops.act_fwd(capi.RELU, x1, None, y=yf1, cache=c1), iters=50))
     add("relu_bwd", cfg1, T1 * F1 * 8, time_op(lambda: ops.act_bwd(capi.RELU, dyf1, c1, dx=dxf1), iters=50))
 
+    # The same seven calls as ONE CUDA graph: at these sizes the host's per-call cost dominates the figures
+    # above, a replayed graph shows what the GPU itself needs for the whole forward + backward chain.
+    def chain1():
+        ops.embed_sort_tokens(ids1, V1, D1, workspace=wse1)
+        ops.embed_gather_fwd(tab1, ids1, pe1, S1, out=out1)
+        ops.ln_residual_fwd(out1, b1, g1, be1, 1e-5, y=y1, xhat=xh1, inv_std=inv1)
+        ops.act_fwd(capi.RELU, x1, None, y=yf1, cache=c1)
+        ops.act_bwd(capi.RELU, dyf1, c1, dx=dxf1)
+        ops.ln_bwd(dy1, None, xh1, inv1, g1, dx=dx1, dgamma=dg1, dbeta=db1, workspace=ws1)
+        ops.embed_scatter_bwd(dx1, ids1, V1, wse1, grad=grad1)
+
+    chain_bytes = T1 * D1 * (16 + 12 + 8 + 4) + V1 * D1 * 4 + 2 * T1 * F1 * 8
+    try:
+        eager_ms = time_op(chain1, iters=50)
+        want = None
+        chain1()
+        want = grad1.clone()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            chain1()
+        grad1.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        if not torch.equal(grad1, want):
+            raise RuntimeError("graph replay differs from the eager chain")
+        add("chain_eager_7_calls", cfg1, chain_bytes, eager_ms)
+        add("chain_cuda_graph_replay", cfg1, chain_bytes, time_op(graph.replay, iters=50))
+    except Exception as exc:  # a capture problem must not cost the benchmark its headline
+        print(f"[bench] CUDA graph of the char-LM chain skipped: {type(exc).__name__}: {exc}", file=sys.stderr)
+
     # config 2: LN + residual, 65536 x 1024
     R, D = 65536, 1024
     a, b, dy = randn(R, D), randn(R, D), randn(R, D)
