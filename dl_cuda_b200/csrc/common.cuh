@@ -192,6 +192,13 @@ __device__ __forceinline__ float4 ld_const_f4(const float *p) {
   return __ldg(reinterpret_cast<const float4 *>(p));
 }
 
+// Nanoseconds of the GPU's wall clock, for bounding waits.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

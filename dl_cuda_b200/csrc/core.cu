@@ -57,7 +57,10 @@ extern "C" int dlb_pipeline_timeouts(unsigned int *h_count) {
   DLB_REQUIRE(h_count != nullptr, DLB_ERR_INVALID_ARG, "pipeline_timeouts: null pointer");
   unsigned int *p = dlb::wait_timeouts_counter();
   DLB_REQUIRE(p != nullptr, DLB_ERR_NO_DEVICE, "pipeline_timeouts: no CUDA device");
-  cudaError_t e = cudaMemcpy(h_count, p, sizeof(unsigned int), cudaMemcpyDeviceToHost);
+  // Every stream of the device, non-blocking ones included, has to drain first: a plain
+  // cudaMemcpy only orders itself after the legacy default stream.
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(h_count, p, sizeof(unsigned int), cudaMemcpyDeviceToHost);
   DLB_REQUIRE(e == cudaSuccess, DLB_ERR_CUDA, "pipeline_timeouts: %s", cudaGetErrorString(e));
   return DLB_OK;
 }

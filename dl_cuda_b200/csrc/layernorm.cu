@@ -412,12 +412,15 @@ int launch_bwd(const void *dy_a, const void *dy_b, const void *xhat, const float
   constexpr size_t kSmem = sizeof(float) * kRowsPerCta * TPR * VPT * E;
   static_assert(kSmem <= 48 * 1024, "slot accumulators must fit default dynamic smem");
   auto kern = ln_bwd_kernel<T, TPR, VPT>;
-  static int ctas_per_sm = 0;  // same for every device of one model
+  // One occupancy query per instantiation; racing first calls compute the same value.
+  static std::atomic<int> cached_ctas_per_sm{0};
+  int ctas_per_sm = cached_ctas_per_sm.load(std::memory_order_relaxed);
   if (ctas_per_sm == 0) {
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kBlock, kSmem) != cudaSuccess || n < 1)
       n = 1;
     ctas_per_sm = n;
+    cached_ctas_per_sm.store(n, std::memory_order_relaxed);
   }
   const int grid = bwd_grid(rows, kRowsPerCta, ctas_per_sm);
   launch_pdl(kern, grid, kBlock, kSmem, st, static_cast<const T *>(dy_a), static_cast<const T *>(dy_b),

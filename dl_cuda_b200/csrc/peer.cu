@@ -25,12 +25,6 @@ struct PeerFlags {
   uint32_t *flags[kMaxPeers];
 };
 
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
 __global__ void __launch_bounds__(32)
 peer_barrier_kernel(const __grid_constant__ PeerFlags pf, int n, int me, int channel, uint32_t epoch,
                     unsigned long long limit_ns, uint32_t *status) {

@@ -3,9 +3,11 @@
 // global -> shared that completes on an mbarrier (the TMA engine moves the
 // bytes; no thread holds them in registers while they are in flight).
 //
-// Every wait is bounded: after kWaitLimit polls it gives up, raises a flag that
-// the host can read (dlb_pipeline_timeouts) and lets the kernel run to its end
-// with garbage results instead of hanging the GPU.
+// Every wait is bounded by wall-clock time (%globaltimer): after kWaitLimitNs it
+// gives up, raises a flag that the host can read (dlb_pipeline_timeouts) and
+// lets the kernel run to its end with garbage results instead of hanging the
+// GPU.  The layer classes read the counter where they synchronise anyway
+// (gradient clipping, checkpoint writing) and fail loudly when it is non-zero.
 #pragma once
 
 #include "common.cuh"
@@ -16,7 +18,7 @@ namespace dlb {
 // by core.cu); kernels get it as a parameter.  Host side.
 unsigned int *wait_timeouts_counter();
 
-constexpr unsigned kWaitLimit = 1u << 14;  // polls; a poll suspends for up to a few microseconds
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // one second per wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -47,7 +49,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, volatile int *dead,
                                           unsigned int *timeouts) {
   const uint32_t addr = smem_u32(bar);
-  for (unsigned i = 0; i < kWaitLimit; i++) {
+  unsigned long long start = 0;
+  for (unsigned i = 0;; i++) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -58,6 +61,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, volati
         : "memory");
     if (done) return true;
     if (*dead) return false;
+    // The clock is read every 32nd poll only: a poll already suspends the thread for a while.
+    if ((i & 31u) == 31u) {
+      const unsigned long long now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > kWaitLimitNs) break;
+    }
   }
   *dead = 1;
   atomicAdd(timeouts, 1u);

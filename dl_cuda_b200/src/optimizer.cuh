@@ -135,5 +135,6 @@ inline float Sequential::clip_grad_norm(float max_norm) {
                                ws.count(), result.get(), nullptr));
   float norm = 0.0f;
   CUDA_CHECK(cudaMemcpy(&norm, result.get() + 1, sizeof(float), cudaMemcpyDeviceToHost));
+  dlb_require_no_pipeline_timeouts("clip_grad_norm");
   return norm;
 }

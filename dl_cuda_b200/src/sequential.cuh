@@ -38,6 +38,19 @@
     }                                                                                         \
   } while (0)
 
+// A bounded wait inside a pipelined kernel that gave up leaves wrong results behind without a
+// CUDA error.  Called where the host synchronises anyway (gradient clipping, checkpoint
+// writing), so that such a step is neither trained on nor saved.
+inline void dlb_require_no_pipeline_timeouts(const char *where) {
+  unsigned int gave_up = 0;
+  DLB_CHECK(dlb_pipeline_timeouts(&gave_up));
+  if (gave_up != 0) {
+    fprintf(stderr, "dlcuda_b200: %u pipeline wait(s) timed out before %s: results since then are invalid\n",
+            gave_up, where);
+    exit(EXIT_FAILURE);
+  }
+}
+
 struct ParamGroup {
   float *params;
   float *grads;
@@ -126,6 +139,7 @@ public:
   // The file is assembled on the device (one launch writes every group's size word and values
   // into one buffer), copied to pinned host memory in one transfer and written with one fwrite.
   bool save_weights(const std::string &path) {
+    dlb_require_no_pipeline_timeouts("save_weights");
     const GroupArrays g = group_arrays();
     const size_t body = dlb_checkpoint_body_bytes(static_cast<int>(g.sizes.size()), g.sizes.data());
     PinnedFile file(kHeaderBytes + body);

@@ -60,11 +60,13 @@ DLB_API const char *dlb_last_error(void);
  * load (every stream, every thread).  Used by benchmarks to report launches. */
 DLB_API uint64_t dlb_launch_count(void);
 
-/* The pipelined kernels wait on shared-memory barriers with a bounded number of
- * polls; a wait that gives up lets the kernel finish (with wrong results) and
- * bumps a per-device counter instead of hanging the GPU.  This call
- * synchronises the device and returns that counter: 0 means every result since
- * load is good.  No counterpart in the reference. */
+/* The pipelined kernels wait on shared-memory barriers for at most one second of
+ * wall-clock time each; a wait that gives up lets the kernel finish (with wrong
+ * results) and bumps a per-device counter instead of hanging the GPU.  This
+ * call synchronises the whole device (cudaDeviceSynchronize: every stream,
+ * non-blocking ones included) and returns that counter: 0 means every result
+ * since load is good.  The layer classes call it from clip_grad_norm and
+ * save_weights and exit when it is non-zero.  No counterpart in the reference. */
 DLB_API int dlb_pipeline_timeouts(unsigned int *h_count);
 
 /* ---- residual add -------------------------------------------------------
@@ -112,10 +114,13 @@ DLB_API int dlb_ln_bwd(const void *dy_a, const void *dy_b, const void *xhat,
  * array inside the library's device image (dlb_ln_bwd_noalloc_max_bytes()):
  * every GPU that loads the library holds it until the process exits.  Shapes
  * whose dlb_ln_bwd_workspace_bytes(rows, d) exceeds it (d > 2048 for up to
- * 262144 rows) are refused with DLB_ERR_UNSUPPORTED.  The call itself makes no
- * allocation of any kind.  The first call on a device looks up the array's
- * device address (cudaGetSymbolAddress) and caches it: make that first call
- * before any stream capture.  All calls share the one array and it keeps the
+ * 262144 rows) are refused with DLB_ERR_UNSUPPORTED.  The call itself asks for
+ * no memory: no cudaMalloc, no cudaFree, no allocating library routine.  The
+ * first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) and caches it; under CUDA's lazy module loading that
+ * first lookup is also the moment the driver materialises the library's device
+ * image, array included, on that GPU.  Make that first call before any stream
+ * capture.  All calls share the one array and it keeps the
  * last call's contents; nothing in it has to start at zero (every partial row
  * is written before it is read), but two calls that overlap on the GPU (two
  * streams, two host threads) race on it -- order them.

@@ -1,6 +1,6 @@
 """Layer norm with the residual folded in: CUDA path (through the C ABI) against
 the CPU oracle and, where the shim library is present, against the reference's
-own kernels.  Tolerance from the project brief: <= 1e-5 relative in fp32,
+own kernels.  Tolerances: <= 1e-5 relative in fp32,
 <= 1e-2 with bf16 storage (relative to max(|a|,|b|,rms))."""
 import numpy as np
 import pytest

@@ -1,13 +1,15 @@
 """dlb_ln_bwd_noalloc: the layer-norm backward for callers that cannot allocate device memory
 (its scratch is an array inside the library).  Called through the C ABI twice in a row and
-compared with dlb_ln_bwd, which takes a caller-provided workspace: both run the same kernels, so
-the results must carry the same bits.  Collected last on purpose."""
+compared with dlb_ln_bwd, which takes a caller-provided workspace (both run the same kernels, so
+the results must carry the same bits) and with the CPU oracle (<= 1e-5 relative for fp32 storage,
+<= 1e-2 for bf16).  Collected last on purpose."""
 import numpy as np
 import pytest
 import torch
 
-from conftest import rng_for
+from conftest import rel_err, rng_for
 from dl_cuda_b200 import capi, ops
+from oracle import cpu as oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -39,11 +41,20 @@ def test_noalloc_matches_the_workspace_entry_point_twice(rows, d, storage, two):
     inv_std = dev(g.uniform(0.5, 2.0, rows).astype(np.float32))
     gamma = dev(g.uniform(0.5, 1.5, d).astype(np.float32))
     want = ops.ln_bwd(dy_a, dy_b, xhat, inv_std, gamma)
+    # the oracle on exactly the values the kernels see (bf16 storage rounded first)
+    host = lambda t: None if t is None else t.float().cpu().numpy()
+    dx0, _, _ = oracle.ln_bwd(host(dy_a), host(dy_b), host(xhat), host(inv_std), host(gamma))
+    dg64, db64 = oracle.ln_param_grad_f64(host(dy_a), host(dy_b), host(xhat))
+    tol = 1e-2 if storage == "bf16" else 1e-5
     for _ in range(2):  # the built-in scratch keeps the previous call's contents: the second call must not care
         got = call_noalloc(dy_a, dy_b, xhat, inv_std, gamma)
         torch.cuda.synchronize()
         for a, b in zip(got, want):
             assert torch.equal(a, b)
+        if d > 1:
+            assert rel_err(host(got[0]), dx0) <= tol
+        assert rel_err(host(got[1]), dg64) <= 1e-5
+        assert rel_err(host(got[2]), db64) <= 1e-5
     # a different shape in between, then the first one again
     other = call_noalloc(xhat[: max(1, rows // 2)].contiguous(), None, xhat[: max(1, rows // 2)].contiguous(),
                          inv_std[: max(1, rows // 2)].contiguous(), gamma)
