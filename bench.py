@@ -385,24 +385,29 @@ class Chain:
 class ReferenceChain:
     """The same chain through the reference's own CUDA kernels (fp32 only, default stream)."""
 
-    def __init__(self, tokens, seq, d, f, vocab, seed):
+    def __init__(self, tokens, seq, d, f, vocab, seed, inputs=None):
         from oracle import ref
         self.ref = ref
         dev = torch.device("cuda", torch.cuda.current_device())
-        g = torch.Generator(device=dev)
-        g.manual_seed(seed)
-        randn = lambda *s: torch.randn(*s, generator=g, device=dev)
         T, D, F, V = tokens, d, f, vocab
         self.T, self.S, self.D, self.F, self.V = T, seq, D, F, V
-        self.table = randn(V, D) * 0.02
-        self.pe = ref.pe_table(seq, D).to(dev)
-        self.gamma = torch.rand(D, generator=g, device=dev) + 0.5
-        self.beta = randn(D) * 0.1
-        rng = np.random.Generator(np.random.Philox(key=seed))
-        self.h_ids = torch.from_numpy(zipf_ids(rng, T, V)).pin_memory()
-        self.ids = self.h_ids.to(dev)
-        self.attn_out, self.ff_out, self.dy, self.d_ff_in = randn(T, D), randn(T, D), randn(T, D), randn(T, D)
-        self.ff_pre, self.d_act = randn(T, F), randn(T, F)
+        self.bias1 = None  # the timed arm adds no bias: the reference does that inside its GEMM kernel
+        if inputs is None:
+            g = torch.Generator(device=dev)
+            g.manual_seed(seed)
+            randn = lambda *s: torch.randn(*s, generator=g, device=dev)
+            self.table = randn(V, D) * 0.02
+            self.pe = ref.pe_table(seq, D).to(dev)
+            self.gamma1 = self.gamma2 = torch.rand(D, generator=g, device=dev) + 0.5
+            self.beta1 = self.beta2 = randn(D) * 0.1
+            rng = np.random.Generator(np.random.Philox(key=seed))
+            self.h_ids = torch.from_numpy(zipf_ids(rng, T, V)).pin_memory()
+            self.ids = self.h_ids.to(dev)
+            self.attn_out, self.ff_out, self.dy, self.d_ff_in = randn(T, D), randn(T, D), randn(T, D), randn(T, D)
+            self.ff_pre, self.d_act = randn(T, F), randn(T, F)
+        else:
+            for name, value in inputs.items():
+                setattr(self, name, value)
         e = lambda *s: torch.empty(*s, device=dev)
         self.emb, self.x0, self.res, self.y1, self.xhat1, self.y2, self.xhat2 = (e(T, D) for _ in range(7))
         self.inv1, self.inv2 = e(T), e(T)
@@ -411,6 +416,20 @@ class ReferenceChain:
         self.small = e(4 * D + F)
         self.table_grad = e(V, D)
         self.h_result = torch.empty(4 * D + F).pin_memory()
+
+    @classmethod
+    def from_inputs(cls, chain: "Chain"):
+        """The reference chain on the inputs of a native chain (storage widened to fp32), with the FFN
+        bias added in a pass of its own: for comparing results, not for timing."""
+        f = lambda t: t.float()
+        inputs = dict(table=f(chain.table), pe=chain.pe, gamma1=chain.gamma1, beta1=chain.beta1,
+                      gamma2=chain.gamma2, beta2=chain.beta2, h_ids=chain.h_ids, ids=chain.ids,
+                      attn_out=f(chain.attn_out), ff_out=f(chain.ff_out), dy=f(chain.dy),
+                      d_ff_in=f(chain.d_ff_in), ff_pre=f(chain.ff_pre), d_act=f(chain.d_act))
+        self = cls(chain.T, chain.S, chain.D, chain.F, chain.V, seed=0, inputs=inputs)
+        self.bias1 = chain.bias1
+        self.pre = torch.empty_like(self.ff_pre)
+        return self
 
     def step(self, copy_inputs=False):
         r, D, F = self.ref, self.D, self.F
@@ -422,20 +441,24 @@ class ReferenceChain:
         r.lib().ref_pe_add(self.emb.data_ptr(), self.pe.data_ptr(), self.x0.data_ptr(), B, S, D)
         n = self.T * D
         r.lib().ref_residual_add(self.x0.data_ptr(), self.attn_out.data_ptr(), self.res.data_ptr(), n)
-        r.lib().ref_ln_fwd(self.res.data_ptr(), self.gamma.data_ptr(), self.beta.data_ptr(), self.y1.data_ptr(),
+        r.lib().ref_ln_fwd(self.res.data_ptr(), self.gamma1.data_ptr(), self.beta1.data_ptr(), self.y1.data_ptr(),
                            self.xhat1.data_ptr(), self.inv1.data_ptr(), self.T, D, 1e-5)
         # the bias add of the reference is the last line of its GEMM kernel: nothing extra to time
-        r.lib().ref_act_fwd(0, self.ff_pre.data_ptr(), self.act.data_ptr(), self.relu_cache.data_ptr(), self.T * F)
+        pre = self.ff_pre
+        if self.bias1 is not None:
+            r.lib().ref_bias_add(self.ff_pre.data_ptr(), self.bias1.data_ptr(), self.pre.data_ptr(), self.T, F)
+            pre = self.pre
+        r.lib().ref_act_fwd(0, pre.data_ptr(), self.act.data_ptr(), self.relu_cache.data_ptr(), self.T * F)
         r.lib().ref_residual_add(self.y1.data_ptr(), self.ff_out.data_ptr(), self.res.data_ptr(), n)
-        r.lib().ref_ln_fwd(self.res.data_ptr(), self.gamma.data_ptr(), self.beta.data_ptr(), self.y2.data_ptr(),
+        r.lib().ref_ln_fwd(self.res.data_ptr(), self.gamma2.data_ptr(), self.beta2.data_ptr(), self.y2.data_ptr(),
                            self.xhat2.data_ptr(), self.inv2.data_ptr(), self.T, D, 1e-5)
         s = self.small
-        r.lib().ref_ln_bwd(self.dy.data_ptr(), self.xhat2.data_ptr(), self.inv2.data_ptr(), self.gamma.data_ptr(),
+        r.lib().ref_ln_bwd(self.dy.data_ptr(), self.xhat2.data_ptr(), self.inv2.data_ptr(), self.gamma2.data_ptr(),
                            self.dx2.data_ptr(), s[2 * D:].data_ptr(), s[3 * D:].data_ptr(), self.T, D)
         r.lib().ref_act_bwd(0, self.d_act.data_ptr(), self.relu_cache.data_ptr(), self.d_pre.data_ptr(), self.T * F)
         r.lib().ref_bias_grad(self.d_pre.data_ptr(), s[4 * D:].data_ptr(), self.T, F)
         r.lib().ref_residual_add(self.dx2.data_ptr(), self.d_ff_in.data_ptr(), self.dsum.data_ptr(), n)
-        r.lib().ref_ln_bwd(self.dsum.data_ptr(), self.xhat1.data_ptr(), self.inv1.data_ptr(), self.gamma.data_ptr(),
+        r.lib().ref_ln_bwd(self.dsum.data_ptr(), self.xhat1.data_ptr(), self.inv1.data_ptr(), self.gamma1.data_ptr(),
                            self.dx1.data_ptr(), s[0:].data_ptr(), s[D:].data_ptr(), self.T, D)
         r.lib().ref_pe_bwd(self.dx1.data_ptr(), self.dpe.data_ptr(), n)
         code = r.lib().ref_embed_bwd(self.dpe.data_ptr(), self.ids.data_ptr(), self.table_grad.data_ptr(), self.T,
@@ -503,20 +526,84 @@ def time_op(fn, warmup=3, iters=10):
     return float(np.mean([evs[i].elapsed_time(evs[i + 1]) for i in range(iters)]))
 
 
-def kernel_sweep(peak):
-    """GB/s of each kernel on the large fp32 configurations (inputs far larger than L2)."""
+def rel_err_dev(got, want) -> float:
+    """max |got-want| / max(|got|, |want|, rms(want)) evaluated on the device in fp64, in slices."""
+    got, want = got.reshape(-1), want.reshape(-1)
+    n, step = want.numel(), 1 << 26
+    sq = 0.0
+    for i in range(0, n, step):
+        w = want[i:i + step].double()
+        sq += float((w * w).sum())
+    rms = max((sq / max(n, 1)) ** 0.5, 1e-30)
+    worst = 0.0
+    for i in range(0, n, step):
+        g, w = got[i:i + step].double(), want[i:i + step].double()
+        denom = torch.maximum(torch.maximum(g.abs(), w.abs()), torch.full_like(w, rms))
+        worst = max(worst, float(((g - w).abs() / denom).max()))
+    return worst
+
+
+def same_bits(a, b) -> bool:
+    return a.shape == b.shape and bool(torch.equal(a.contiguous().view(torch.int32), b.contiguous().view(torch.int32)))
+
+
+def kernel_sweep(peak, with_reference=False):
+    """GB/s of each kernel on the large fp32 configurations (inputs far larger than L2).  With
+    `with_reference` (a baseline leg: it runs the shim around the reference's own kernels) every
+    entry of configs 2-4 also carries the time of the reference's kernels for the same op on the
+    same inputs, the speed-up, and the largest relative error between the two results."""
     from dl_cuda_b200 import capi, ops
+    ref = None
+    if with_reference:
+        from oracle import ref as ref_mod
+        ref = ref_mod if ref_mod.available() else None
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev)
     g.manual_seed(1234)
     randn = lambda *s: torch.randn(*s, generator=g, device=dev)
     out = []
 
-    def add(name, cfg, nbytes, ms):
+    def add(name, cfg, nbytes, ms, ref_fn=None, compare=None, exact=None):
         gbs = nbytes / ms / 1e6
-        out.append({"kernel": name, "config": cfg, "ms": round(ms, 4), "bytes": int(nbytes),
-                    "gbs": round(gbs, 1), "frac_measured": round(gbs / peak, 4),
-                    "frac_nominal": round(gbs / NOMINAL_HBM_GBS, 4)})
+        entry = {"kernel": name, "config": cfg, "ms": round(ms, 4), "bytes": int(nbytes),
+                 "gbs": round(gbs, 1), "frac_measured": round(gbs / peak, 4),
+                 "frac_nominal": round(gbs / NOMINAL_HBM_GBS, 4)}
+        if ref is not None and ref_fn is not None:
+            ref_ms = time_op(ref_fn, warmup=1, iters=3)
+            entry["ref_ms"] = round(ref_ms, 4)
+            entry["speedup_vs_ref"] = round(ref_ms / ms, 2)
+            if compare is not None:
+                errs = compare()
+                entry["max_rel_err_vs_ref"] = max(errs.values())
+                entry["err_vs_ref"] = {k: float(f"{v:.3g}") for k, v in errs.items()}
+                entry["bit_exact_vs_ref"] = all(v == 0.0 for v in errs.values())
+            if exact is not None:
+                # reductions: this library and the reference each against the sum in fp64 (the reference adds
+                # its terms one by one in fp32, so its own distance from the exact sum bounds any agreement)
+                mine, theirs = exact()
+                entry["err_vs_fp64"] = {k: float(f"{v:.3g}") for k, v in mine.items()}
+                entry["ref_err_vs_fp64"] = {k: float(f"{v:.3g}") for k, v in theirs.items()}
+        out.append(entry)
+
+    bits = lambda a, b: 0.0 if same_bits(a, b) else max(rel_err_dev(a, b), 1e-30)
+
+    def colsum64(*factors):
+        """Column sums of the element-wise product of 2-D tensors, accumulated in fp64 in row slices."""
+        acc = torch.zeros(factors[0].shape[1], dtype=torch.float64, device=dev)
+        for r0 in range(0, factors[0].shape[0], 4096):
+            prod = factors[0][r0:r0 + 4096].double()
+            for f in factors[1:]:
+                prod = prod * f[r0:r0 + 4096].double()
+            acc += prod.sum(0)
+        return acc
+
+    def ln_exact(dy_a, dy_b):
+        def run():
+            dsum = dy_a if dy_b is None else dy_a + dy_b  # one rounding, as both implementations do
+            g64, b64 = colsum64(dsum, xhat), colsum64(dsum)
+            return ({"dgamma": rel_err_dev(dg, g64), "dbeta": rel_err_dev(db, b64)},
+                    {"dgamma": rel_err_dev(dg_r, g64), "dbeta": rel_err_dev(db_r, b64)})
+        return run
 
     # config 1: char-LM shapes (batch 32 x seq 64, d_model 64, vocab 65, FFN 2048 x 256): launch-latency
     # bound (every tensor fits L2), so the time per call is what matters; GB/s only for information
@@ -530,16 +617,30 @@ def kernel_sweep(peak):
     ids1 = torch.randint(0, V1, (T1,), generator=g, device=dev, dtype=torch.int32)
     pe1, out1, grad1 = ops.pe_table(S1, D1).to(dev), torch.empty(T1, D1, device=dev), torch.empty(V1, D1, device=dev)
     wse1 = ops.embed_workspace(T1, V1, D1, dev)
-    x1, dyf1 = randn(T1, F1), randn(T1, F1)
-    yf1, dxf1, c1 = torch.empty_like(x1), torch.empty_like(x1), ops.act_cache(capi.RELU, x1)
+    x1, dyf1, bias1 = randn(T1, F1), randn(T1, F1), randn(F1) * 0.1
+    yf1, dxf1, dbias1 = torch.empty_like(x1), torch.empty_like(x1), torch.empty(F1, device=dev)
+    wsa1 = ops.act_bwd_workspace(capi.RELU, T1, F1, dev)
     cfg1 = "char-LM shapes 2048x64 / V65 / 2048x256 fp32"
-    add("ln_residual_fwd", cfg1, T1 * D1 * 16, time_op(lambda: ops.ln_residual_fwd(a1, b1, g1, be1, 1e-5, y=y1, xhat=xh1, inv_std=inv1), iters=50))
-    add("ln_bwd", cfg1, T1 * D1 * 12, time_op(lambda: ops.ln_bwd(dy1, None, xh1, inv1, g1, dx=dx1, dgamma=dg1, dbeta=db1, workspace=ws1), iters=50))
-    add("embed_gather_pe_fwd", cfg1, T1 * D1 * 8, time_op(lambda: ops.embed_gather_fwd(tab1, ids1, pe1, S1, out=out1), iters=50))
-    add("embed_sort_tokens", cfg1, 0, time_op(lambda: ops.embed_sort_tokens(ids1, V1, D1, workspace=wse1), iters=50))
-    add("embed_scatter_bwd", cfg1, T1 * D1 * 4 + V1 * D1 * 4, time_op(lambda: ops.embed_scatter_bwd(dy1, ids1, V1, wse1, grad=grad1), iters=50))
-    add("relu_fwd", cfg1, T1 * F1 * 8, time_op(lambda: ops.act_fwd(capi.RELU, x1, None, y=yf1, cache=c1), iters=50))
-    add("relu_bwd", cfg1, T1 * F1 * 8, time_op(lambda: ops.act_bwd(capi.RELU, dyf1, c1, dx=dxf1), iters=50))
+    it = dict(iters=50)
+    add("residual_add", cfg1, T1 * D1 * 12, time_op(lambda: ops.residual_add(a1, b1, out=y1), **it))
+    add("ln_residual_fwd", cfg1, T1 * D1 * 16, time_op(lambda: ops.ln_residual_fwd(a1, b1, g1, be1, 1e-5, y=y1, xhat=xh1, inv_std=inv1), **it))
+    add("ln_bwd", cfg1, T1 * D1 * 12, time_op(lambda: ops.ln_bwd(dy1, None, xh1, inv1, g1, dx=dx1, dgamma=dg1, dbeta=db1, workspace=ws1), **it))
+    add("ln_bwd_two_grads", cfg1, T1 * D1 * 16, time_op(lambda: ops.ln_bwd(dy1, b1, xh1, inv1, g1, dx=dx1, dgamma=dg1, dbeta=db1, workspace=ws1), **it))
+    add("embed_gather_pe_fwd", cfg1, T1 * D1 * 8, time_op(lambda: ops.embed_gather_fwd(tab1, ids1, pe1, S1, out=out1), **it))
+    add("embed_gather_fwd", cfg1, T1 * D1 * 8, time_op(lambda: ops.embed_gather_fwd(tab1, ids1, None, 0, out=out1), **it))
+    add("pe_add_fwd", cfg1, T1 * D1 * 8, time_op(lambda: ops.pe_add_fwd(a1.view(T1 // S1, S1, D1), pe1, out=y1.view(T1 // S1, S1, D1)), **it))
+    add("pe_add_bwd", cfg1, T1 * D1 * 8, time_op(lambda: ops.pe_add_bwd(dy1, dx=dx1), **it))
+    add("embed_sort_tokens", cfg1, 0, time_op(lambda: ops.embed_sort_tokens(ids1, V1, D1, workspace=wse1), **it))
+    add("embed_scatter_bwd", cfg1, T1 * D1 * 4 + V1 * D1 * 4, time_op(lambda: ops.embed_scatter_bwd(dy1, ids1, V1, wse1, grad=grad1), **it))
+    for kind, name in ((capi.RELU, "relu"), (capi.SIGMOID, "sigmoid"), (capi.TANH, "tanh")):
+        c1 = ops.act_cache(kind, x1)
+        cache_b = T1 * F1 // 8 if kind == capi.RELU else T1 * F1 * 4
+        add(f"bias_{name}_fwd", cfg1, T1 * F1 * 8 + cache_b, time_op(lambda: ops.act_fwd(kind, x1, bias1, y=yf1, cache=c1), **it))
+        add(f"{name}_bwd", cfg1, T1 * F1 * 8 + cache_b, time_op(lambda: ops.act_bwd(kind, dyf1, c1, dx=dxf1), **it))
+        add(f"{name}_bwd_dbias", cfg1, T1 * F1 * 8 + cache_b, time_op(lambda: ops.act_bwd(kind, dyf1, c1, dx=dxf1, dbias=dbias1, want_dbias=True, workspace=wsa1), **it))
+    wsb1 = torch.empty(max(capi.lib().dlb_bias_grad_workspace_bytes(T1, F1), 16), dtype=torch.uint8, device=dev)
+    add("bias_grad", cfg1, T1 * F1 * 4, time_op(lambda: ops.bias_grad(dyf1, dbias=dbias1, workspace=wsb1), **it))
+    c1 = ops.act_cache(capi.RELU, x1)
 
     # The same seven calls as ONE CUDA graph: at these sizes the host's per-call cost dominates the figures
     # above, a replayed graph shows what the GPU itself needs for the whole forward + backward chain.
@@ -578,13 +679,27 @@ def kernel_sweep(peak):
     y, xhat, inv = torch.empty_like(a), torch.empty_like(a), torch.empty(R, device=dev)
     dx, dg, db = torch.empty_like(a), torch.empty(D, device=dev), torch.empty(D, device=dev)
     ws = ops.ln_bwd_workspace(R, D, dev)
+    if ref is not None:
+        s_r, y_r, xhat_r, inv_r = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a), torch.empty(R, device=dev)
+        dx_r, dg_r, db_r = torch.empty_like(a), torch.empty(D, device=dev), torch.empty(D, device=dev)
+    cfg2 = "65536x1024 fp32"
     ms = time_op(lambda: ops.ln_residual_fwd(a, b, gamma, beta, 1e-5, y=y, xhat=xhat, inv_std=inv))
-    add("ln_residual_fwd", "65536x1024 fp32", R * D * 16 + R * 4 + 2 * D * 4, ms)
+    add("ln_residual_fwd", cfg2, R * D * 16 + R * 4 + 2 * D * 4, ms,
+        lambda: ref.ln_fwd(ref.residual_add(a, b, out=s_r), gamma, beta, 1e-5, y=y_r, xhat=xhat_r, inv_std=inv_r),
+        lambda: {"y": rel_err_dev(y, y_r), "xhat": rel_err_dev(xhat, xhat_r), "inv_std": rel_err_dev(inv, inv_r)})
     ms = time_op(lambda: ops.ln_bwd(dy, None, xhat, inv, gamma, dx=dx, dgamma=dg, dbeta=db, workspace=ws))
-    add("ln_bwd", "65536x1024 fp32", R * D * 12 + R * 4 + 3 * D * 4, ms)
+    add("ln_bwd", cfg2, R * D * 12 + R * 4 + 3 * D * 4, ms,
+        lambda: ref.ln_bwd(dy, xhat, inv, gamma, dx=dx_r, dgamma=dg_r, dbeta=db_r),
+        lambda: {"dx": rel_err_dev(dx, dx_r), "dgamma": rel_err_dev(dg, dg_r), "dbeta": rel_err_dev(db, db_r)},
+        ln_exact(dy, None))
     ms = time_op(lambda: ops.ln_bwd(dy, b, xhat, inv, gamma, dx=dx, dgamma=dg, dbeta=db, workspace=ws))
-    add("ln_bwd_two_grads", "65536x1024 fp32", R * D * 16 + R * 4 + 3 * D * 4, ms)
+    add("ln_bwd_two_grads", cfg2, R * D * 16 + R * 4 + 3 * D * 4, ms,
+        lambda: ref.ln_bwd(ref.residual_add(dy, b, out=s_r), xhat, inv, gamma, dx=dx_r, dgamma=dg_r, dbeta=db_r),
+        lambda: {"dx": rel_err_dev(dx, dx_r), "dgamma": rel_err_dev(dg, dg_r), "dbeta": rel_err_dev(db, db_r)},
+        ln_exact(dy, b))
     del a, b, dy, y, xhat, dx
+    if ref is not None:
+        del s_r, y_r, xhat_r, dx_r
 
     # config 3: embedding + PE, vocab 32000 x 4096, 16 x 2048 Zipf tokens
     V, D, B, S = 32000, 4096, 16, 2048
@@ -597,13 +712,23 @@ def kernel_sweep(peak):
     outb, dyb = torch.empty(T, D, device=dev), randn(T, D)
     grad = torch.empty(V, D, device=dev)
     wse = ops.embed_workspace(T, V, D, dev)
+    if ref is not None:
+        emb_r, out_r, dpe_r, grad_r = torch.empty_like(outb), torch.empty_like(outb), torch.empty_like(outb), torch.empty_like(grad)
     ms = time_op(lambda: ops.embed_gather_fwd(table, ids, pe, S, out=outb))
-    add("embed_gather_pe_fwd", f"V32000 D4096 T32768 zipf1.1 ({U} distinct)", (U + T) * D * 4 + S * D * 4 + T * 4, ms)
+    add("embed_gather_pe_fwd", f"V32000 D4096 T32768 zipf1.1 ({U} distinct)", (U + T) * D * 4 + S * D * 4 + T * 4, ms,
+        lambda: ref.pe_add(ref.embed_fwd(table, ids, out=emb_r).view(B, S, D), pe, out=out_r.view(B, S, D)),
+        lambda: {"out": bits(outb, out_r)})
     ms = time_op(lambda: ops.embed_sort_tokens(ids, V, D, workspace=wse))
     add("embed_sort_tokens", "T32768", 0, ms)
     ms = time_op(lambda: ops.embed_scatter_bwd(dyb, ids, V, wse, grad=grad))
-    add("embed_scatter_bwd", "V32000 D4096 T32768 zipf1.1", T * D * 4 + V * D * 4 + T * 4, ms)
+    add("embed_scatter_bwd", "V32000 D4096 T32768 zipf1.1", T * D * 4 + V * D * 4 + T * 4, ms,
+        lambda: ref.embed_bwd(ref.pe_bwd(dyb, dx=dpe_r), ids, V, grad=grad_r),
+        lambda: {"grad": rel_err_dev(grad, grad_r)},
+        lambda: (lambda e64: ({"grad": rel_err_dev(grad, e64)}, {"grad": rel_err_dev(grad_r, e64)}))(
+            torch.zeros(V, D, dtype=torch.float64, device=dev).index_add_(0, ids.long(), dyb.double())))
     del table, outb, dyb, grad
+    if ref is not None:
+        del emb_r, out_r, dpe_r, grad_r
 
     # config 4: bias + activation, 32768 x 16384 (2 GiB per buffer)
     R, C = 32768, 16384
@@ -614,13 +739,25 @@ def kernel_sweep(peak):
     dbias = torch.empty(C, device=dev)
     wsa = ops.act_bwd_workspace(capi.RELU, R, C, dev)
     n = R * C
+    if ref is not None:
+        # the reference adds the bias inside its GEMM kernel: its activation kernels start from the biased value
+        pre_r = ref.bias_add(x, bias)
+        y_r, cache_r, dx_r, dbias_r = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x), torch.empty(C, device=dev)
+    cfg4 = "32768x16384 fp32"
     for kind, name in ((capi.RELU, "relu"), (capi.SIGMOID, "sigmoid"), (capi.TANH, "tanh")):
         cache_b = n // 8 if kind == capi.RELU else n * 4
         ms = time_op(lambda: ops.act_fwd(kind, x, bias, y=yb, cache=cache))
-        add(f"bias_{name}_fwd", "32768x16384 fp32", n * 8 + cache_b + C * 4, ms)
+        add(f"bias_{name}_fwd", cfg4, n * 8 + cache_b + C * 4, ms,
+            lambda: ref.act_fwd(kind, pre_r, y=y_r, cache=cache_r),
+            lambda: {"y": bits(yb, y_r)})
         ms = time_op(lambda: ops.act_bwd(kind, dyy, cache, dx=dxb, dbias=dbias, want_dbias=True, workspace=wsa))
-        add(f"{name}_bwd_dbias", "32768x16384 fp32", n * 8 + cache_b + C * 4, ms)
+        add(f"{name}_bwd_dbias", cfg4, n * 8 + cache_b + C * 4, ms,
+            lambda: ref.bias_grad(ref.act_bwd(kind, dyy, cache_r, dx=dx_r), dbias=dbias_r),
+            lambda: {"dx": bits(dxb, dx_r), "dbias": rel_err_dev(dbias, dbias_r)},
+            lambda: (lambda b64: ({"dbias": rel_err_dev(dbias, b64)}, {"dbias": rel_err_dev(dbias_r, b64)}))(colsum64(dx_r)))
     del x, dyy, yb, dxb, cache
+    if ref is not None:
+        del pre_r, y_r, cache_r, dx_r
 
     # beyond the named path (what comes next): GELU epilogue and the optimizer path on the parameters of
     # the chain (embedding table 32000x4096 plus the small groups), one launch for all groups
@@ -645,23 +782,114 @@ def kernel_sweep(peak):
     return out
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch from the ncu captures
-# summarised under profiles/, taken on a quarter-size case (8192 or 16384 rows) and scaled by rows:
-# traffic of these streaming kernels grows in proportion to the rows.  Bytes per token row.
-NCU_TRAFFIC_PER_ROW = {
-    "relu_fwd": (268.512768e6 + 230.742528e6) / 8192,   # profiles/act_relu_kernels_bf16_8192x16384.txt
-    "relu_bwd": (286.164736e6 + 246.704896e6) / 8192,
-    "ln1_fwd": (268.486656e6 + 216.835328e6) / 16384,   # profiles/ln_fwd_kernel_bf16_16384x4096.txt
-    "ln2_fwd": (268.486656e6 + 216.835328e6) / 16384,
-    "ln2_bwd": (268.583424e6 + 98.576896e6) / 16384,    # profiles/ln_bwd_pipe_kernel_bf16_16384x4096.txt
+def reference_kernel_sweep():
+    """The reference's own kernels, op by op, on the large fp32 configurations (the launch geometry and
+    cache copies of the reference's layer classes); nothing of this library runs here."""
+    from oracle import ref
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    randn = lambda *s: torch.randn(*s, generator=g, device=dev)
+    out = []
+
+    def add(name, cfg, fn):
+        out.append({"kernel": name, "config": cfg, "ms": round(time_op(fn, warmup=1, iters=3), 4)})
+
+    R, D = 65536, 1024
+    a, b, dy = randn(R, D), randn(R, D), randn(R, D)
+    gamma, beta = torch.rand(D, generator=g, device=dev) + 0.5, randn(D) * 0.1
+    s_r, y, xhat, inv = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a), torch.empty(R, device=dev)
+    dx, dg, db = torch.empty_like(a), torch.empty(D, device=dev), torch.empty(D, device=dev)
+    cfg = "65536x1024 fp32"
+    add("ln_residual_fwd", cfg, lambda: ref.ln_fwd(ref.residual_add(a, b, out=s_r), gamma, beta, 1e-5, y=y, xhat=xhat, inv_std=inv))
+    add("ln_bwd", cfg, lambda: ref.ln_bwd(dy, xhat, inv, gamma, dx=dx, dgamma=dg, dbeta=db))
+    add("ln_bwd_two_grads", cfg, lambda: ref.ln_bwd(ref.residual_add(dy, b, out=s_r), xhat, inv, gamma, dx=dx, dgamma=dg, dbeta=db))
+    del a, b, dy, s_r, y, xhat, dx
+
+    V, D, B, S = 32000, 4096, 16, 2048
+    T = B * S
+    table = randn(V, D) * 0.02
+    ids = torch.from_numpy(zipf_ids(np.random.Generator(np.random.Philox(key=1236)), T, V)).to(dev)
+    pe = ref.pe_table(S, D).to(dev)
+    emb, outb, dpe, dyb = (torch.empty(T, D, device=dev) for _ in range(4))
+    dyb.normal_(generator=g)
+    grad = torch.empty(V, D, device=dev)
+    cfg = "V32000 D4096 T32768 zipf1.1"
+    add("embed_gather_pe_fwd", cfg, lambda: ref.pe_add(ref.embed_fwd(table, ids, out=emb).view(B, S, D), pe, out=outb.view(B, S, D)))
+    add("embed_scatter_bwd", cfg, lambda: ref.embed_bwd(ref.pe_bwd(dyb, dx=dpe), ids, V, grad=grad))
+    del table, emb, outb, dpe, dyb, grad
+
+    R, C = 32768, 16384
+    pre, dyy = randn(R, C) * 2.0, randn(R, C)
+    y, cache, dx, dbias = torch.empty_like(pre), torch.empty_like(pre), torch.empty_like(pre), torch.empty(C, device=dev)
+    cfg = "32768x16384 fp32"
+    for kind, name in ((0, "relu"), (1, "sigmoid"), (2, "tanh")):
+        add(f"bias_{name}_fwd", cfg, lambda: ref.act_fwd(kind, pre, y=y, cache=cache))
+        add(f"{name}_bwd_dbias", cfg, lambda: ref.bias_grad(ref.act_bwd(kind, dyy, cache, dx=dx), dbias=dbias))
+    return out
+
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch, read at run time from the ncu
+# summaries under profiles/ (captures of a quarter-size case, or of the full embedding case) and scaled
+# by token rows: the traffic of these streaming kernels grows in proportion to the rows.
+# (chain op, storage) -> (summary file, kernel-name fragments whose traffic adds up, rows of the captured case)
+PROFILE_TRAFFIC = {
+    ("embed_gather_pe", "bf16"): ("embedding_kernels_bf16_V32000_D4096_T32768.txt", ["embed_gather"], 32768),
+    ("ln1_fwd", "bf16"): ("ln_fwd_kernel_bf16_16384x4096.txt", ["ln_fwd_kernel"], 16384),
+    ("ln2_fwd", "bf16"): ("ln_fwd_kernel_bf16_16384x4096.txt", ["ln_fwd_kernel"], 16384),
+    ("relu_fwd", "bf16"): ("act_relu_kernels_bf16_8192x16384.txt", ["act_fwd_kernel"], 8192),
+    ("relu_bwd", "bf16"): ("act_relu_kernels_bf16_8192x16384.txt", ["act_bwd_kernel"], 8192),
+    ("ln2_bwd", "bf16"): ("ln_bwd_pipe_kernel_bf16_16384x4096.txt", ["ln_bwd_pipe_kernel"], 16384),
+    ("ln1_bwd", "bf16"): ("ln_bwd_pipe_kernel_two_grads_bf16_16384x4096.txt", ["ln_bwd_pipe_kernel"], 16384),
+    ("embed_scatter", "bf16"): ("embedding_kernels_bf16_V32000_D4096_T32768.txt",
+                                ["scatter_rows_kernel", "combine_long_kernel"], 32768),
+    ("embed_gather_pe", "fp32"): ("embedding_kernels_fp32_V32000_D4096_T32768.txt", ["embed_gather"], 32768),
+    ("embed_scatter", "fp32"): ("embedding_kernels_fp32_V32000_D4096_T32768.txt",
+                                ["scatter_rows_kernel", "combine_long_kernel"], 32768),
 }
-NCU_TRAFFIC_NOTE = ("ncu dram__bytes_read+write of a quarter-size capture (profiles/*.txt) scaled by rows; writes still "
-                    "in L2 when the kernel ends are not counted by ncu, so it can read below the algorithmic bytes")
+NCU_TRAFFIC_NOTE = ("ncu dram__bytes_read+write per launch, parsed from profiles/*.txt (a quarter-size or full-size "
+                    "capture) and scaled by rows; writes still in L2 when the kernel ends are not counted by ncu, "
+                    "so it can read below the algorithmic bytes")
+_UNIT_BYTES = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9, "Tbyte": 1e12}
 
 
-def ncu_traffic(op, rows):
-    per_row = NCU_TRAFFIC_PER_ROW.get(op)
-    return None if per_row is None else int(per_row * rows)
+def parse_profile(path):
+    """[(kernel name, {"dram read": bytes, "dram write": bytes, "duration": us})] of one summary file."""
+    kernels = []
+    for line in Path(path).read_text().splitlines():
+        if line.startswith("kernel:"):
+            kernels.append((line.split(":", 1)[1].strip(), {}))
+            continue
+        if not kernels or not line.startswith("  "):
+            continue
+        parts = line.split()
+        for key in ("dram read", "dram write", "duration"):
+            words = key.split()
+            if parts[:len(words)] == words and len(parts) == len(words) + 2:
+                value, unit = float(parts[-2]), parts[-1]
+                if key == "duration":
+                    kernels[-1][1][key] = value * {"ns": 1e-3, "us": 1.0, "ms": 1e3}.get(unit, 1.0)
+                elif unit in _UNIT_BYTES:
+                    kernels[-1][1][key] = value * _UNIT_BYTES[unit]
+    return kernels
+
+
+def ncu_traffic(op, storage, rows):
+    """DRAM bytes per launch of a chain op on `rows` token rows, or None where no capture covers it."""
+    entry = PROFILE_TRAFFIC.get((op, storage))
+    if entry is None:
+        return None
+    file, fragments, captured_rows = entry
+    path = ROOT / "profiles" / file
+    if not path.exists():
+        return None
+    total = 0.0
+    for fragment in fragments:
+        hits = [m for name, m in parse_profile(path) if fragment in name and "dram read" in m and "dram write" in m]
+        if not hits:
+            return None
+        total += hits[0]["dram read"] + hits[0]["dram write"]
+    return int(total / captured_rows * rows)
 
 
 # --------------------------------------------------------------------------- small cases for ncu
@@ -745,6 +973,24 @@ def run_timed(step, dist: Dist, steps, warmup):
     return dist.max_float(start.elapsed_time(stop))
 
 
+REPEATS = 7  # timed regions of K steps each; the median is reported
+
+
+def run_repeats(step, dist: Dist, steps, repeats=REPEATS):
+    """`repeats` back-to-back timed regions of `steps` steps (each: barrier + synchronize on both sides,
+    CUDA events, max over ranks).  Returns the per-step times in ms, sorted."""
+    return sorted(run_timed(step, dist, steps, 0) / steps for _ in range(repeats))
+
+
+def capi_timeouts() -> int:
+    from dl_cuda_b200 import capi
+    return capi.pipeline_timeouts()
+
+
+def median(values):
+    return float(np.median(values))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -756,7 +1002,9 @@ def main():
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: how the embedding-table gradient is exchanged (default: the library's peer-memory kernels)")
     ap.add_argument("--skip-kernels", action="store_true", help="skip the per-kernel fp32 sweep")
-    ap.add_argument("--skip-cpu", action="store_true", help="skip the host baseline")
+    ap.add_argument("--skip-cpu", action="store_true",
+                    help="skip the baseline legs (the single-threaded host loops and the reference-kernel columns)")
+    ap.add_argument("--skip-fp32-chain", action="store_true", help="N=1: skip the fp32-storage run of the chain")
     ap.add_argument("--case", default=None, help="run one small kernel case (for ncu) and exit: " + ", ".join(PROFILE_CASES))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -789,9 +1037,9 @@ def main():
     launches0 = lib.dlb_launch_count()
     sampler = ClockSampler(torch.cuda.current_device())
     with sampler:
-        total_ms = run_timed(chain.step, dist, args.steps, 0)
-    launches = lib.dlb_launch_count() - launches0
-    ms_per_step = total_ms / args.steps
+        step_ms = run_repeats(chain.step, dist, args.steps)
+    launches = (lib.dlb_launch_count() - launches0) // REPEATS
+    ms_per_step = median(step_ms)
     tokens_per_s = args.tokens / (ms_per_step / 1e3)
 
     # the same K steps once more with an event after every op: per-op device time
@@ -817,12 +1065,17 @@ def main():
         gbs = op_bytes[name] / op_ms[name] / 1e6 if op_ms[name] > 0 and op_bytes[name] else None
         ops_report.append({"op": name, "ms": round(op_ms[name], 4), "bytes": int(op_bytes[name]),
                            "gbs": None if gbs is None else round(gbs, 1),
-                           "frac": None if gbs is None else round(gbs / peak, 4)})
+                           "frac": None if gbs is None else round(gbs / peak, 4),
+                           "ncu_traffic": ncu_traffic(name, args.dtype, tokens_local) if n == 1 or "embed" not in name
+                           else None})
     dominant = max((o for o in ops_report if o["gbs"]), key=lambda o: o["ms"])
 
     # end to end: ids from pinned host memory in, parameter gradients out, every step
-    e2e_ms = run_timed(lambda: chain.step(copy_inputs=True), dist, args.steps, args.warmup) / args.steps
+    run_timed(lambda: chain.step(copy_inputs=True), dist, args.warmup, 0)
+    e2e_all = run_repeats(lambda: chain.step(copy_inputs=True), dist, args.steps)
+    e2e_ms = median(e2e_all)
     e2e = {"value": args.tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+           "value_min": args.tokens / (e2e_all[-1] / 1e3), "value_max": args.tokens / (e2e_all[0] / 1e3),
            "h2d_bytes_per_step": int(chain.h_ids.numel() * 4 * n),
            "d2h_bytes_per_step": int(chain.h_result.numel() * 4 * n),
            "what": "per step: token ids copied from pinned host memory, the chain through the C ABI, "
@@ -832,6 +1085,9 @@ def main():
         "metric": "tokens/s", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "impl": "native",
+        "value_min": args.tokens / (step_ms[-1] / 1e3), "value_max": args.tokens / (step_ms[0] / 1e3),
+        "repeats": REPEATS, "ms_per_step_all": [round(v, 4) for v in step_ms],
+        "timing": f"median of {REPEATS} timed regions of {args.steps} steps each (gpu_launches: per region)",
         "config": {"workload": "transformer-block non-GEMM chain fwd+bwd (embed+PE, LN+residual x2, bias+ReLU, "
                                "scatter-add), token-sharded",
                    "batch": BATCH, "seq_len": SEQ, "d_model": D_MODEL, "d_ff": D_FF, "vocab": VOCAB,
@@ -842,7 +1098,8 @@ def main():
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": dominant["frac"],
                      "frac_of_nominal_8000": round(dominant["gbs"] / NOMINAL_HBM_GBS, 4),
                      "algorithmic_bytes": dominant["bytes"],
-                     "traffic": ncu_traffic(dominant["op"], tokens_local), "traffic_source": NCU_TRAFFIC_NOTE},
+                     "traffic": ncu_traffic(dominant["op"], args.dtype, tokens_local),
+                     "traffic_source": NCU_TRAFFIC_NOTE},
         "chain_ops": ops_report, "chain_ops_ms_per_step": round(marked_ms, 4),
         "chain_ops_note": "per-op times come from a second pass of the same K steps with a CUDA event after "
                           "every op (ops serialised on one stream); the headline pass has no events and "
@@ -858,9 +1115,31 @@ def main():
                 raise SystemExit(f"peer barrier wait gave up (channel mask {gave_up}): the measurement is void")
     del chain
     torch.cuda.empty_cache()
+    if n == 1 and args.dtype == "bf16" and not args.skip_fp32_chain:
+        # The like-for-like figure against the reference arm (which is fp32: the reference has no bf16):
+        # the same chain with fp32 storage, same steps and warm-up.
+        chain32 = Chain(tokens_local, SEQ, D_MODEL, D_FF, VOCAB, torch.float32, seed=1234, dist=dist)
+        run_timed(chain32.step, dist, args.warmup, 0)
+        ms32_all = run_repeats(chain32.step, dist, args.steps)
+        ms32 = median(ms32_all)
+        bytes32 = sum(chain32.bytes_per_op().values())
+        run_timed(lambda: chain32.step(copy_inputs=True), dist, args.warmup, 0)
+        e2e32 = median(run_repeats(lambda: chain32.step(copy_inputs=True), dist, args.steps))
+        result["chain_fp32"] = {"ms_per_step": round(ms32, 4), "value": args.tokens / (ms32 / 1e3), "unit": "tokens/s",
+                                "value_min": args.tokens / (ms32_all[-1] / 1e3),
+                                "value_max": args.tokens / (ms32_all[0] / 1e3),
+                                "e2e_value": args.tokens / (e2e32 / 1e3),
+                                "chain_bytes_per_step": int(bytes32), "chain_gbs": round(bytes32 / ms32 / 1e6, 1),
+                                "what": "the same chain with fp32 storage: the figure to hold against the reference "
+                                        "arm, whose kernels are fp32"}
+        if lib.dlb_launch_count() and capi_timeouts():
+            raise SystemExit("a pipeline wait gave up during the fp32 chain: the measurement is void")
+        del chain32
+        torch.cuda.empty_cache()
     if dist.rank == 0 and n == 1:
         if not args.skip_kernels:
-            result["kernels_fp32"] = kernel_sweep(peak)
+            # with the baseline legs on, the reference's own kernels are timed beside each large-config kernel
+            result["kernels_fp32"] = kernel_sweep(peak, with_reference=not args.skip_cpu)
         if not args.skip_cpu:
             result["cpu_baseline"] = cpu_baseline()
     dist.barrier()
@@ -892,6 +1171,10 @@ def main_reference(args, dist: Dist):
     ms = total_ms / args.steps
     e2e_ms = run_timed(lambda: chain.step(copy_inputs=True), one, args.steps, 1) / args.steps
     value = args.tokens / (ms / 1e3)
+    h2d, d2h = int(chain.h_ids.numel() * 4), int(chain.h_result.numel() * 4)
+    del chain
+    torch.cuda.empty_cache()
+    sweep = None if args.skip_kernels else reference_kernel_sweep()
     print(json.dumps({
         "impl": "reference", "metric": "tokens/s", "value": value, "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -902,11 +1185,14 @@ def main_reference(args, dist: Dist):
                    "global_tokens": args.tokens, "ids": "zipf(1.1)",
                    "l2": "inputs larger than L2"},
         "e2e": {"value": args.tokens / (e2e_ms / 1e3), "unit": "tokens/s",
-                "h2d_bytes_per_step": int(chain.h_ids.numel() * 4), "d2h_bytes_per_step": int(chain.h_result.numel() * 4)},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": 0, "kind": "reference",
                          "sample": "the reference's CUDA kernels built for sm_100 on the same B200 "
                                    "(the reference has no CPU implementation of this path)"},
         "clocks": sampler.summary(),
+        "kernels_fp32_reference": sweep,
+        "kernels_note": "per-op times of the reference's kernels on the large fp32 configurations; the bias add is "
+                        "inside the reference's GEMM kernel and is not timed",
     }))
 
 
