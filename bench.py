@@ -226,10 +226,12 @@ class Chain:
         self.zero_done = torch.cuda.Event()
         if dist.active:
             Tg = T * dist.world
+            self.Tg = Tg
             self.ids_all = torch.empty(Tg, dtype=torch.int32, device=dev)
             self.ws_global = ops.embed_workspace(Tg, V, D, dev)
-            self.ws_compact = ops.embed_compact_workspace(V, dev)
+            self.rank_plan = ops.embed_rank_plan_workspace(V, T, D, dev)
             self.h_used = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self.bwd_done = torch.cuda.Event()
             # Table-gradient exchange: the library's fused scatter-add + peer-memory exchange, or (asked for, or when
             # symmetric memory cannot be set up) NCCL's all-reduce of the compacted rows.
             self.peer = None
@@ -237,17 +239,20 @@ class Chain:
             if exchange == "peer":
                 try:
                     from dl_cuda_b200.sharding import PeerExchange
-                    self.peer = PeerExchange(dist.dist, V, D, min(V, Tg), dev)
-                    # One barrier on each channel before anything depends on it; the verdict is shared, so
-                    # either every rank uses the peer exchange or none does.
-                    self.peer.barrier(0)
-                    self.peer.barrier(1)
-                    verdict = torch.tensor([self.peer.timed_out()], dtype=torch.int32, device=dev)
+                    self.peer = PeerExchange(dist.dist, V, D, min(V, Tg), dev, tokens_per_rank=T,
+                                             small_n=self.small_grads.numel())
+                    # One barrier before anything depends on the flags; the verdict is shared, so either every
+                    # rank uses the peer exchange or none does.
+                    self.peer.barrier()
+                    verdict = torch.tensor([self.peer.timed_out()], dtype=torch.int64, device=dev)
                     dist.dist.all_reduce(verdict, op=dist.dist.ReduceOp.MAX)
                     if int(verdict.item()) != 0:
                         raise RuntimeError("the peer barrier did not complete on every rank")
                     self.table_grad = self.peer.table_grad()
-                    self.exchange_note = "scatter-add fused with a peer-memory exchange (owner-reduce, broadcast into the dense tables)"
+                    self.ids_all = self.peer.ids_all[:Tg]
+                    self.exchange_note = ("scatter-add fused with a peer-memory exchange: rows one rank alone has tokens "
+                                          "for go straight into every rank's dense table, shared rows to their owner, "
+                                          "which adds them in rank order and stores the sum into every table")
                 except Exception as exc:  # no symmetric memory on this box / build
                     self.peer = None
                     print(f"[bench] peer exchange unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
@@ -271,11 +276,15 @@ class Chain:
             "ln2_bwd": T * D * 3 * e + T * 4 + 3 * D * 4,
             "ln1_bwd": T * D * 4 * e + T * 4 + 3 * D * 4,
             # N > 1: only the rows used by some rank are written (the dense expansion is timed with the all-reduce)
-            "embed_scatter": T * D * e + (int(self.h_used[0]) if self.dist.active else V) * D * 4 + T * 4,
+            "embed_scatter": T * D * e + (self.used_rows() if self.dist.active else V) * D * 4 + T * 4,
             "allreduce": 0,
         }
 
-    def step(self, marks=None, copy_inputs=False):
+    def used_rows(self) -> int:
+        """Table rows some rank refers to, from the rank plan of the last step (synchronises)."""
+        return int(self.rank_plan[:4].view(torch.int32)[0].item())
+
+    def step(self, marks=None, copy_inputs=False, capture=None):
         lib, capi, st = self.lib, self.capi, torch.cuda.current_stream().cuda_stream
         p = lambda t: t.data_ptr()
         T, D, F, V, S, code = self.T, self.D, self.F, self.V, self.S, self.code
@@ -292,21 +301,28 @@ class Chain:
         mark()
         # The sorted-segment plan depends on the ids alone and is needed only by the last kernel of
         # backward: in the headline pass it is built on a side stream, beside the forward kernels.
-        plan_stream = self.side if marks is None else torch.cuda.current_stream()
+        main = torch.cuda.current_stream()
+        plan_stream = self.side if marks is None else main
         pst = plan_stream.cuda_stream
-        if self.dist.active:
-            # every rank needs every rank's ids to number the table rows used anywhere
-            self.dist.dist.all_gather_into_tensor(self.ids_all, self.ids)
         if marks is None:
-            self.side.wait_stream(torch.cuda.current_stream())
-        chk(lib.dlb_embed_sort_tokens(p(self.ids), p(self.ws_embed), self.ws_embed.numel(), T, V, D, pst))
-        if self.dist.active:
-            Tg = self.ids_all.numel()
-            chk(lib.dlb_embed_sort_tokens(p(self.ids_all), p(self.ws_global), self.ws_global.numel(), Tg, V, D, pst))
-            chk(lib.dlb_embed_compact_plan(p(self.ws_global), Tg, p(self.ws_embed), T, p(self.ws_compact),
-                                           self.ws_compact.numel(), V, D, pst))
-            with torch.cuda.stream(plan_stream):
-                self.h_used.copy_(self.ws_compact[:4].view(torch.int32)[:1], non_blocking=True)
+            self.side.wait_stream(main)
+        if not self.dist.active:
+            chk(lib.dlb_embed_sort_tokens(p(self.ids), p(self.ws_embed), self.ws_embed.numel(), T, V, D, pst))
+        else:
+            # Every rank needs every rank's ids: one sort of the gathered list gives the numbering of the rows
+            # used anywhere and each rank's tokens of them.  The gather is also the point where every rank is
+            # known to be done with the previous step's tables.
+            if self.peer is not None:
+                self.peer.gather_ids(self.ids, stream=pst)
+            else:
+                with torch.cuda.stream(plan_stream):
+                    self.dist.dist.all_gather_into_tensor(self.ids_all, self.ids)
+            chk(lib.dlb_embed_sort_tokens(p(self.ids_all), p(self.ws_global), self.ws_global.numel(), self.Tg, V, D, pst))
+            chk(lib.dlb_embed_rank_plan(p(self.ws_global), self.Tg, T, self.dist.world, self.dist.rank,
+                                        p(self.rank_plan), self.rank_plan.numel(), V, D, pst))
+            if self.peer is None:
+                with torch.cuda.stream(plan_stream):
+                    self.h_used.copy_(self.rank_plan[:4].view(torch.int32)[:1], non_blocking=True)
         self.plan_ready.record(plan_stream)
         mark()
         chk(lib.dlb_embed_gather_fwd(p(self.table), p(self.ids), p(self.pe), S, p(self.x0), T, V, D, code, st))
@@ -328,57 +344,84 @@ class Chain:
         chk(lib.dlb_ln_bwd(p(self.dx2), p(self.d_ff_in), p(self.xhat1), p(self.inv1), p(self.gamma1), p(self.dx1),
                            p(self.dgamma1), p(self.dbeta1), p(self.ws_ln), self.ws_ln.numel(), T, D, code, st))
         mark()
+        if capture is not None:
+            capture["small_local"] = self.small_grads.clone()
         if marks is None:
-            torch.cuda.current_stream().wait_event(self.plan_ready)
+            main.wait_event(self.plan_ready)
         if not self.dist.active:
             chk(lib.dlb_embed_scatter_bwd(p(self.dx1), p(self.ids), p(self.table_grad), p(self.ws_embed),
                                           self.ws_embed.numel(), T, V, D, code, st))
             mark()
+        elif self.peer is not None:
+            px, ops = self.peer, self.ops
+            # rows no rank uses are zeroed locally, beside the exchange (which is bound by NVLink, not HBM)
+            self.bwd_done.record(main)
+            self.side.wait_event(self.bwd_done)
+            chk(lib.dlb_embed_expand_rows(None, p(self.rank_plan), T, p(self.table_grad), V, D, 1, self.side.cuda_stream))
+            self.zero_done.record(self.side)
+            # No host wait and no library call between the kernels: the launch is sized from an upper bound, the
+            # kernels read the exact row count, announce their stores and wait for the other ranks themselves.
+            pushed, done = px.next_epoch(px.CH_PUSHED), px.next_epoch(px.CH_DONE)
+            ops.embed_scatter_bwd_peer(self.dx1, self.ws_global, self.Tg, self.rank_plan, T, px.group, self.small_grads,
+                                       min(V, self.Tg), V, px.CH_PUSHED, pushed, stream=st)
+            mark()
+            ops.embed_reduce_broadcast_peer(self.rank_plan, T, px.group, self.small_grads, V, D, px.CH_PUSHED, pushed,
+                                            px.CH_DONE, done, stream=st)
+            main.wait_event(self.zero_done)
+            px.wait(px.CH_DONE, stream=st)  # every rank's table holds every row
         else:
-            # Compacted form: only the rows some rank uses are summed, all-reduced and expanded.
-            if self.peer is not None:
-                px, ops = self.peer, self.ops
-                # no host wait: the launch is sized from an upper bound, the kernels read the exact count
-                torch.cuda.current_stream().wait_event(self.plan_ready)
-                used = min(V, self.ids_all.numel())
-                # every rank pushes the rows it has tokens for into their owners' receive areas
-                ops.embed_scatter_bwd_peer(self.dx1, self.ws_embed, self.ws_compact, px.recv_ptrs, px.rank, px.cap_rows,
-                                           used, V, stream=st)
-                mark()
-                # rows no rank uses are zeroed locally, beside the exchange
-                self.side.wait_stream(torch.cuda.current_stream())
-                chk(lib.dlb_embed_expand_rows(None, p(self.ws_compact), p(self.table_grad), V, D, 1, self.side.cuda_stream))
-                self.zero_done.record(self.side)
-                px.barrier(0, stream=st)      # all partial rows have arrived
-                ops.embed_reduce_broadcast_peer(px.recv, self.ws_compact, px.grad_ptrs, px.rank, px.cap_rows, V, D, stream=st)
-                # (issued on the second stream instead, this all-reduce changed nothing: 0.60 ms either way on 8 GPUs)
-                self.dist.dist.all_reduce(self.small_grads)
-                torch.cuda.current_stream().wait_event(self.zero_done)
-                px.barrier(1, stream=st)      # every rank's table holds every reduced row; receive areas are zero again
-                mark()
-                if copy_inputs:
-                    self.h_result.copy_(self.small_grads, non_blocking=True)
-                    torch.cuda.current_stream().synchronize()
-                    return float(self.h_result[0])
-                return None
-            self.plan_ready.synchronize()  # the row count is a host argument of the calls below
+            # Compacted form through NCCL: only the rows some rank uses are summed, all-reduced and expanded.
+            self.plan_ready.synchronize()  # the row count is a host argument of the all-reduce
             used = int(self.h_used[0])
-            chk(lib.dlb_embed_scatter_bwd_compact(p(self.dx1), p(self.ws_embed), self.ws_embed.numel(),
-                                                  p(self.ws_compact), p(self.compact_rows), used, T, V, D, code, st))
+            chk(lib.dlb_embed_scatter_bwd_compact(p(self.dx1), p(self.ws_global), self.Tg, p(self.rank_plan), T,
+                                                  self.dist.rank, p(self.compact_rows), used, V, D, code, st))
             mark()
             # zero the unused rows of the dense gradient beside the all-reduce
-            self.side.wait_stream(torch.cuda.current_stream())
-            chk(lib.dlb_embed_expand_rows(None, p(self.ws_compact), p(self.table_grad), V, D, 1, self.side.cuda_stream))
+            self.side.wait_stream(main)
+            chk(lib.dlb_embed_expand_rows(None, p(self.rank_plan), T, p(self.table_grad), V, D, 1, self.side.cuda_stream))
             self.zero_done.record(self.side)
             allreduce_param_grads(self.dist.dist, self.small_grads, self.compact_rows[:used])
-            torch.cuda.current_stream().wait_event(self.zero_done)
-            chk(lib.dlb_embed_expand_rows(p(self.compact_rows), p(self.ws_compact), p(self.table_grad), V, D, 2, st))
+            main.wait_event(self.zero_done)
+            chk(lib.dlb_embed_expand_rows(p(self.compact_rows), p(self.rank_plan), T, p(self.table_grad), V, D, 2, st))
         mark()
         if copy_inputs:
             self.h_result.copy_(self.small_grads, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            main.synchronize()
             return float(self.h_result[0])
         return None
+
+    def verify(self):
+        """N > 1, untimed: one step, then every rank checks its dense table gradient and its reduced small
+        gradients against the single-rank result of ALL tokens (the other ranks' gradients and ids are
+        gathered here only for the check), and that every rank holds the same bits as rank 0."""
+        d, ops, lib = self.dist.dist, self.ops, self.lib
+        captured = {}
+        self.step(capture=captured)
+        torch.cuda.synchronize()
+        T, D, V, Tg = self.T, self.D, self.V, self.Tg
+        dx_all = torch.empty(Tg, D, dtype=self.dtype, device=self.dx1.device)
+        d.all_gather_into_tensor(dx_all, self.dx1)
+        ids_all = torch.empty(Tg, dtype=torch.int32, device=self.dx1.device)
+        d.all_gather_into_tensor(ids_all, self.ids)
+        plan = ops.embed_sort_tokens(ids_all, V, D)
+        want = ops.embed_scatter_bwd(dx_all, ids_all, V, plan)
+        err_table = rel_err_dev(self.table_grad, want)
+        del want, dx_all
+        small_all = torch.empty(self.dist.world, self.small_grads.numel(), device=self.dx1.device)
+        d.all_gather_into_tensor(small_all, captured["small_local"])
+        err_small = rel_err_dev(self.small_grads, small_all.double().sum(0))
+        mine = torch.cat([self.table_grad.reshape(-1), self.small_grads])
+        theirs = mine.clone()
+        d.broadcast(theirs, src=0)
+        same = torch.tensor([1 if same_bits(mine, theirs) else 0], dtype=torch.int32, device=mine.device)
+        d.all_reduce(same, op=d.ReduceOp.MIN)
+        worst = torch.tensor([err_table, err_small], dtype=torch.float64, device=mine.device)
+        d.all_reduce(worst, op=d.ReduceOp.MAX)
+        gave_up = self.peer.timed_out() if self.peer is not None else 0
+        return {"max_rel_err_table_grad": float(worst[0]), "max_rel_err_small_grads": float(worst[1]),
+                "ranks_bit_identical": bool(int(same.item())), "status_bits": gave_up,
+                "against": "the single-rank gradient of all tokens (same kernels, one GPU's association)",
+                "tolerance": 3e-5}
 
 
 # --------------------------------------------------------------------------- the chain (reference kernels)
@@ -1030,6 +1073,18 @@ def main():
                   exchange=args.exchange)
     lib = chain.lib
 
+    parity = None
+    if dist.active:
+        # Untimed: one step checked against the single-rank gradient of all tokens, on every rank.
+        parity = chain.verify()
+        ok = (parity["max_rel_err_table_grad"] <= parity["tolerance"] and parity["max_rel_err_small_grads"] <= parity["tolerance"]
+              and parity["ranks_bit_identical"] and parity["status_bits"] == 0)
+        if not ok:
+            if dist.rank == 0:
+                print(json.dumps({"impl": "native", "n_gpus": n, "parity_check": parity, "error": "parity check failed"}))
+            dist.finish()
+            raise SystemExit(3)
+
     # device-resident run: the headline `value` (no events between the kernels)
     for _ in range(args.warmup):
         chain.step()
@@ -1107,12 +1162,16 @@ def main():
         "chain_bytes_per_step": int(sum(op_bytes.values()) * n),
         "chain_gbs": round(sum(op_bytes.values()) * n / ms_per_step / 1e6, 1),
     }
+    if capi_timeouts():
+        raise SystemExit("a pipeline wait gave up during the run: the measurement is void")
     if dist.active:
         result["config"]["table_grad_exchange"] = chain.exchange_note
+        result["parity_check"] = parity
         if chain.peer is not None:
             gave_up = chain.peer.timed_out()
             if gave_up:
-                raise SystemExit(f"peer barrier wait gave up (channel mask {gave_up}): the measurement is void")
+                raise SystemExit(f"peer exchange status {gave_up:#x} (a wait gave up or the receive area was too small): "
+                                 "the measurement is void")
     del chain
     torch.cuda.empty_cache()
     if n == 1 and args.dtype == "bf16" and not args.skip_fp32_chain:

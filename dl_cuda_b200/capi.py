@@ -26,6 +26,7 @@ SIGNATURES = {
     "dlb_last_error": (C.c_char_p, []),
     "dlb_launch_count": (C.c_uint64, []),
     "dlb_pipeline_timeouts": (_i, [_p]),
+    "dlb_set_option": (_i, [C.c_char_p, _i]),
     "dlb_residual_add": (_i, [_p, _p, _p, _i64, _i, _p]),
     "dlb_ln_residual_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _p]),
     "dlb_ln_bwd_workspace_bytes": (_sz, [_i, _i]),
@@ -39,10 +40,10 @@ SIGNATURES = {
     "dlb_embed_workspace_bytes": (_sz, [_i, _i, _i]),
     "dlb_embed_sort_tokens": (_i, [_p, _p, _sz, _i, _i, _i, _p]),
     "dlb_embed_scatter_bwd": (_i, [_p, _p, _p, _p, _sz, _i, _i, _i, _i, _p]),
-    "dlb_embed_compact_workspace_bytes": (_sz, [_i]),
-    "dlb_embed_compact_plan": (_i, [_p, _i, _p, _i, _p, _sz, _i, _i, _p]),
-    "dlb_embed_scatter_bwd_compact": (_i, [_p, _p, _sz, _p, _p, _i, _i, _i, _i, _i, _p]),
-    "dlb_embed_expand_rows": (_i, [_p, _p, _p, _i, _i, _i, _p]),
+    "dlb_embed_rank_plan_bytes": (_sz, [_i, _i, _i]),
+    "dlb_embed_rank_plan": (_i, [_p, _i, _i, _i, _i, _p, _sz, _i, _i, _p]),
+    "dlb_embed_scatter_bwd_compact": (_i, [_p, _p, _i, _p, _i, _i, _p, _i, _i, _i, _i, _p]),
+    "dlb_embed_expand_rows": (_i, [_p, _p, _i, _p, _i, _i, _i, _p]),
     "dlb_act_cache_bytes": (_sz, [_i, _i64, _i]),
     "dlb_act_fwd": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _i, _p]),
     "dlb_act_bwd_workspace_bytes": (_sz, [_i, _i64, _i64]),
@@ -56,10 +57,12 @@ SIGNATURES = {
     "dlb_checkpoint_body_bytes": (_sz, [_i, _p]),
     "dlb_checkpoint_pack": (_i, [_i, _p, _p, _p, _sz, _p]),
     "dlb_checkpoint_unpack": (_i, [_i, _p, _p, _p, _sz, _p]),
-    "dlb_embed_scatter_bwd_peer": (_i, [_p, _p, _sz, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
-    "dlb_embed_reduce_broadcast_peer": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "dlb_embed_scatter_bwd_peer": (_i, [_p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, C.c_uint32, _p]),
+    "dlb_embed_reduce_broadcast_peer": (_i, [_p, _i, _p, _p, _i, _i, _i, C.c_uint32, _i, C.c_uint32, _p]),
     "dlb_peer_flags_bytes": (_sz, []),
     "dlb_peer_barrier": (_i, [_p, _i, _i, _i, C.c_uint32, _i, _p, _p]),
+    "dlb_peer_wait": (_i, [_p, _i, _i, _i, C.c_uint32, _i, _p, _p]),
+    "dlb_peer_put": (_i, [_p, _sz, _p, _p, _i, _i, _i, C.c_uint32, _i, _i, _p, _p]),
     "dlb_gemm_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i, _i,
                           _i64, _i64, _i64, _i64, _i64, _i64, _f, _i, _p]),
     "dlb_softmax_fwd": (_i, [_p, _p, _i64, _i, _i, _p]),
@@ -69,6 +72,16 @@ SIGNATURES = {
     "dlb_ce_from_ids_fwd": (_i, [_p, _p, _p, _i, _i, _f, _p]),
     "dlb_ce_from_ids_bwd": (_i, [_p, _p, _p, _i, _i, _f, _p]),
 }
+
+
+MAX_PEERS = 16
+
+
+class PeerGroup(C.Structure):
+    """dlb_peer_group of include/dlcuda_b200.h: the buffers of every rank as mapped on this GPU."""
+    _fields_ = [("n_ranks", _i), ("my_rank", _i), ("cap_rows", _i), ("small_n", _i), ("timeout_ms", _i),
+                ("reserved", _i), ("flags", _p * MAX_PEERS), ("recv", _p * MAX_PEERS), ("grad", _p * MAX_PEERS),
+                ("small", _p * MAX_PEERS), ("status", _p)]
 
 
 class DlbError(RuntimeError):
@@ -99,6 +112,11 @@ def lib() -> C.CDLL:
 def check(status: int) -> None:
     if status != OK:
         raise DlbError(status, lib().dlb_last_error().decode() or lib().dlb_status_string(status).decode())
+
+
+def set_option(name: str, value: int) -> None:
+    """Kernel-variant override for measurements (0 = heuristic); see dlb_set_option in the header."""
+    check(lib().dlb_set_option(name.encode(), int(value)))
 
 
 def pipeline_timeouts() -> int:

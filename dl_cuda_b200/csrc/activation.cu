@@ -75,7 +75,8 @@ struct Tiling {
 // column sums to write and reduce, so backward uses narrow CTAs (64 vectors wide, 4 rows deep):
 // the same number of CTAs then makes 4x fewer partial rows (measured at 32768 x 16384 bf16:
 // 374 us with 256-wide CTAs, 351 us with 64-wide ones).
-Tiling make_tiling(int64_t rows, int64_t ncv, int ctas_per_sm, int tx_cap = kBlock) {
+// max_gy > 0 bounds the CTA rows (= partial rows of a fused bias gradient).
+Tiling make_tiling(int64_t rows, int64_t ncv, int ctas_per_sm, int tx_cap = kBlock, int64_t gy_cap = 0) {
   Tiling t;
   int tx = 2;  // never 1: fp32 ReLU pairs adjacent lanes to build one mask byte
   while (tx < tx_cap && tx < ncv) tx *= 2;
@@ -86,6 +87,7 @@ Tiling make_tiling(int64_t rows, int64_t ncv, int ctas_per_sm, int tx_cap = kBlo
   const int64_t max_gy = ceil_div<int64_t>(rows, step);
   int64_t gy = ceil_div<int64_t>(static_cast<int64_t>(sm_count()) * ctas_per_sm, gx);
   if (gy > max_gy) gy = max_gy;
+  if (gy_cap > 0 && gy > gy_cap) gy = gy_cap;
   if (gy > 65535) gy = 65535;
   if (gy < 1) gy = 1;
   t.rows_per_cta = ceil_div<int64_t>(ceil_div<int64_t>(rows, gy), step) * step;
@@ -383,7 +385,15 @@ int act_bwd_typed(const void *dy, const void *cache, void *dx, float *dbias, flo
       vc = kFlatCols;
       vr = ceil_div<int64_t>(n, vc);
     }
-    const Tiling t = make_tiling(vr, vc / E, 64, dbias != nullptr ? 64 : kBlock);
+    // A CTA row of the grid costs one partial row of column sums (written, then read by the second
+    // stage): with few data rows keep those to a few percent of the payload (one per 64 data rows).
+    int64_t gy_cap = 0;
+    if (dbias != nullptr) {
+      gy_cap = vr / 64 > 32 ? vr / 64 : 32;
+      const int want = get_option("act_bwd_partial_rows");
+      if (want > 0) gy_cap = want;
+    }
+    const Tiling t = make_tiling(vr, vc / E, 64, dbias != nullptr ? 64 : kBlock, gy_cap);
     if (n + vc * 4 * kBlock < INT32_MAX)
       launch_pdl(act_bwd_kernel<T, KIND, int>, t.grid, t.block, 0, st, 
         static_cast<const T *>(dy), cache, static_cast<T *>(dx), dbias ? partial : nullptr, vr, vc,

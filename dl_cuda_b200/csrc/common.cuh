@@ -21,6 +21,7 @@ namespace dlb {
 void set_error(const char *fmt, ...);
 extern std::atomic<uint64_t> g_launches;
 int sm_count();  // SMs of the current device (cached per device)
+int get_option(const char *name);  // value set through dlb_set_option, 0 if unset
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
@@ -98,7 +99,7 @@ inline T ceil_div(T a, T b) {
 
 // -------------------------------------------------------------- device side
 constexpr int kWarp = 32;
-constexpr int kMaxPeers = 16;  // most ranks (GPUs of one node) the peer-memory entry points take
+constexpr int kMaxPeers = DLB_MAX_PEERS;  // most ranks (GPUs of one node) the peer-memory entry points take
 
 // First statement of every kernel: allow the next kernel of the stream to be
 // scheduled early, then wait for everything launched before this kernel.

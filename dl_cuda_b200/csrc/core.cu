@@ -34,6 +34,28 @@ int sm_count() {
   return n;
 }
 
+// Tuning options (dlb_set_option): 0 = the built-in heuristic decides.
+namespace {
+struct Option {
+  const char *name;
+  std::atomic<int> value;
+};
+Option g_options[] = {
+    {"gather_rows_in_flight", {0}},     // 4 or 8 table rows loaded per thread before the first store
+    {"ln_bwd_pipe", {0}},               // 1: never the bulk-copy pipeline, 2: whenever the shape allows
+    {"ln_bwd_pipe_threads", {0}},       // column threads per CTA: 128, 256 or 512
+    {"ln_bwd_pipe_ctas_per_sm", {0}},   // 1 or 2
+    {"ln_bwd_pipe_rows_per_tile", {0}}, // 1, 2, 4 or 8
+    {"act_bwd_partial_rows", {0}},      // upper bound of the partial rows of a fused bias gradient
+};
+}  // namespace
+
+int get_option(const char *name) {
+  for (Option &o : g_options)
+    if (strcmp(o.name, name) == 0) return o.value.load(std::memory_order_relaxed);
+  return 0;
+}
+
 __device__ unsigned int g_wait_timeouts = 0;
 
 unsigned int *wait_timeouts_counter() {
@@ -65,7 +87,19 @@ extern "C" int dlb_pipeline_timeouts(unsigned int *h_count) {
   return DLB_OK;
 }
 
-extern "C" int dlb_version(void) { return 100; }
+extern "C" int dlb_set_option(const char *name, int value) {
+  DLB_REQUIRE(name != nullptr, DLB_ERR_INVALID_ARG, "set_option: null name");
+  for (dlb::Option &o : dlb::g_options) {
+    if (strcmp(o.name, name) == 0) {
+      o.value.store(value, std::memory_order_relaxed);
+      return DLB_OK;
+    }
+  }
+  dlb::set_error("set_option: unknown option '%s'", name);
+  return DLB_ERR_INVALID_ARG;
+}
+
+extern "C" int dlb_version(void) { return 101; }
 
 extern "C" const char *dlb_status_string(int status) {
   switch (status) {

@@ -1,0 +1,532 @@
+// The sorted-segment sum behind every form of the embedding-table gradient
+// (dense single-GPU, compacted for an all-reduce, routed over peer memory).
+//
+// Input: a list of token indices sorted by table row ("perm") and, per output
+// row, its range of that list.  One launch:
+//   * rows with at most kSubLen tokens are summed in ascending token order and
+//     written once (zeros where no token refers to the row: no memset);
+//   * a row with more tokens is cut into sub-segments of kSubLen tokens, each
+//     summed by its own thread group into a scratch row; a second kernel
+//     (combine_long_kernel, many CTAs per row) adds a row's scratch rows:
+//     kCombineSlices contiguous slices of the sub-segments are summed in order,
+//     then the slice sums in order.  (Letting the CTA that stores a row's last
+//     sub-segment add them in the same launch was tried: one CTA cannot keep
+//     enough loads in flight for a row of 150 sub-segments, 220 against 156 us.)
+// Every addition's order is a function of the ids alone, so two runs give the
+// same bits whatever the scheduling; there are no floating-point atomics.
+#pragma once
+
+#include "common.cuh"
+
+namespace dlb {
+
+constexpr int kEmbBlock = 256;
+constexpr int kSubLen = 32;        // tokens per sub-segment of a long row
+constexpr int kCombineSlices = 8;  // slices the sub-segment sums of a long row are added in
+constexpr int kScatterRowsPerCta = 16;
+constexpr int kScatterPermCap = 1024;
+
+inline size_t align_up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+// ---- the plan dlb_embed_sort_tokens leaves in its workspace ---------------------------------------
+constexpr int kSortItems = 8;                      // keys per thread of a radix pass
+constexpr int kSortTile = kEmbBlock * kSortItems;  // 2048 tokens per CTA
+constexpr int kDigits = 256;
+
+struct Plan {
+  uint32_t *keys[2];
+  int32_t *vals[2];
+  int32_t *block_hist;
+  int32_t *seg_start;   // [V+1]
+  int32_t *long_row;    // [max_long]
+  int32_t *long_first;  // [max_long+1]
+  int32_t *meta;        // {n_long, n_sub}
+  float *scratch;       // [max_sub][d]
+  int passes, nblocks, max_long, max_sub;
+  size_t bytes;
+};
+
+inline Plan make_plan(void *workspace, int num_tokens, int vocab, int d) {
+  Plan p{};
+  int bits = 1;
+  while (bits < 32 && (static_cast<uint64_t>(1) << bits) < static_cast<uint64_t>(vocab)) bits++;
+  p.passes = (bits + 7) / 8;
+  p.nblocks = ceil_div(num_tokens, kSortTile);
+  // A long row has more than kSubLen tokens, so there are fewer than T/kSubLen of
+  // them, and their sub-segments number at most T/kSubLen + (number of long rows).
+  p.max_long = num_tokens / kSubLen + 1;
+  p.max_sub = 2 * (num_tokens / kSubLen) + 2;
+  char *base = static_cast<char *>(workspace);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    char *ptr = base ? base + off : nullptr;
+    off += align_up256(bytes);
+    return ptr;
+  };
+  const size_t tok = sizeof(int32_t) * static_cast<size_t>(num_tokens);
+  p.keys[0] = reinterpret_cast<uint32_t *>(take(tok));
+  p.keys[1] = reinterpret_cast<uint32_t *>(take(tok));
+  p.vals[0] = reinterpret_cast<int32_t *>(take(tok));
+  p.vals[1] = reinterpret_cast<int32_t *>(take(tok));
+  p.block_hist = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * kDigits * p.nblocks));
+  p.seg_start = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * (static_cast<size_t>(vocab) + 1)));
+  p.long_row = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * p.max_long));
+  p.long_first = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * (p.max_long + 1)));
+  p.meta = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * 4));
+  p.scratch = reinterpret_cast<float *>(take(sizeof(float) * static_cast<size_t>(p.max_sub) * d));
+  p.bytes = off;
+  return p;
+}
+
+// ---- flags between the GPUs of one node (see peer.cu) --------------------------------------------
+constexpr int kPeerChannels = 4;
+
+// Announces `epoch` on `channel` to every rank once ALL CTAs of the grid have passed this point:
+// each CTA fences its (peer) stores and counts itself; the last one stores the flags with release
+// semantics at system scope and puts the counter back to zero.  Every CTA of the grid must call it.
+struct PeerSignal {
+  uint32_t *flags[kMaxPeers];  // every rank's flag words [kPeerChannels][kMaxPeers]
+  int32_t *done;               // device counter, zero at launch
+  int n, me, channel;
+  uint32_t epoch;
+};
+
+__device__ __forceinline__ void signal_when_grid_done(const PeerSignal &s) {
+  if (s.done == nullptr) return;
+  __threadfence_system();  // every thread: its own stores to peer memory have been performed
+  __syncthreads();
+  if (threadIdx.x == 0 && threadIdx.y == 0) {
+    __threadfence_system();
+    const int total = static_cast<int>(gridDim.x * gridDim.y * gridDim.z);
+    const int old = atomicAdd(s.done, 1);
+    if (old == total - 1) {
+      atomicExch(s.done, 0);
+      __threadfence_system();
+      for (int r = 0; r < s.n; r++) {
+        uint32_t *theirs = s.flags[r] + s.channel * kMaxPeers + s.me;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(s.epoch) : "memory");
+      }
+    }
+  }
+}
+
+// Waits (whole CTA) until every rank has announced `epoch` on `channel` in this rank's flag words.
+// Bounded by wall-clock time: when it runs out bit `channel` of *status is set and the wait ends.
+__device__ __forceinline__ void wait_for_peers(const uint32_t *my_flags, int n, int channel, uint32_t epoch,
+                                               unsigned long long limit_ns, uint32_t *status) {
+  const int t = threadIdx.y * blockDim.x + threadIdx.x;
+  if (my_flags != nullptr && t < n) {
+    const uint32_t *mine = my_flags + channel * kMaxPeers + t;
+    const unsigned long long start = global_ns();
+    for (;;) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (static_cast<int32_t>(seen - epoch) >= 0) break;
+      if (global_ns() - start > limit_ns) {
+        atomicOr(status, 1u << channel);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+}
+
+// ---- where an output row goes ------------------------------------------------------------------
+// Peer routing: output row r is a slot of the list of table rows some rank uses.  If this rank is
+// the only one with tokens for it (src_mask[r] has just this rank's bit) the finished row is stored
+// into row used_rows[r] of EVERY rank's dense table; otherwise the partial sum goes to the receive
+// area of the slot's owner (rank r % n), laid out [source rank][r / n][d].
+struct PeerRoute {
+  float *recv[kMaxPeers];
+  float *grad[kMaxPeers];
+  const int32_t *used_rows;
+  const uint32_t *src_mask;
+  uint32_t *status;  // bit 31: a slot did not fit the receive area (cap too small)
+  int n, me, cap;
+};
+
+struct ScatterArgs {
+  const int32_t *perm;         // token indices sorted by table row
+  const int32_t *seg_b, *seg_e;  // output row r takes perm[seg_b[r] .. seg_e[r])
+  const int32_t *long_row;     // rows with more than kSubLen tokens (as indices into long_b/long_e) ...
+  const int32_t *long_first;   // ... and the running count of their sub-segments
+  const int32_t *long_b, *long_e;  // range of a long row, indexed by long_row[] entries
+  const int32_t *long_out;     // output row of a long row (indexed likewise), or null: the entry itself
+  const int32_t *meta;         // {number of long rows, number of sub-segments}
+  float *scratch;              // [sub-segments][d]
+  float *out;                  // local output [out_rows][d] (unused with peer routing)
+  const int32_t *out_rows_dev; // device word holding the exact number of output rows, or null
+  int out_rows;                // number of output rows, or an upper bound when out_rows_dev is given
+  int tok_offset;              // subtracted from every perm value (a rank's first token)
+  int d, sub_groups, rows_cta;
+};
+
+template <typename T, int KV, typename Tok>
+__device__ __forceinline__ void sum_tokens(const T *dy, Tok tok, int b, int e, int d, int cv0, int tx, int ncv,
+                                           float (&acc)[KV][Store<T>::kPerVec]) {
+  using S = Store<T>;
+  constexpr int E = S::kPerVec;
+#pragma unroll
+  for (int k = 0; k < KV; k++)
+#pragma unroll
+    for (int q = 0; q < E; q++) acc[k][q] = 0.f;
+  // UNR token rows in flight per step; the additions stay in token order.
+  constexpr int UNR = KV >= 2 ? 2 : 4;
+  int j = b;
+  for (; j + UNR <= e; j += UNR) {
+    uint4 v[UNR][KV];
+#pragma unroll
+    for (int u = 0; u < UNR; u++) {
+      const size_t r = static_cast<size_t>(tok(j + u)) * d;
+#pragma unroll
+      for (int k = 0; k < KV; k++) {
+        const int cv = cv0 + k * tx;
+        if (cv < ncv) v[u][k] = ld_stream(dy + r + static_cast<size_t>(cv) * E);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; u++)
+#pragma unroll
+      for (int k = 0; k < KV; k++) {
+        if (cv0 + k * tx < ncv) {
+          float f[E];
+          S::unpack(v[u][k], f);
+#pragma unroll
+          for (int q = 0; q < E; q++) acc[k][q] += f[q];
+        }
+      }
+  }
+  for (; j < e; j++) {
+    const size_t r0 = static_cast<size_t>(tok(j)) * d;
+#pragma unroll
+    for (int k = 0; k < KV; k++) {
+      const int cv = cv0 + k * tx;
+      if (cv < ncv) {
+        float f0[E];
+        S::unpack(ld_stream(dy + r0 + static_cast<size_t>(cv) * E), f0);
+#pragma unroll
+        for (int q = 0; q < E; q++) acc[k][q] += f0[q];
+      }
+    }
+  }
+}
+
+// One row (this thread's KV vectors of it) to dst.  E == 8 (bf16 input): 32-byte stores.
+template <int E, int KV>
+__device__ __forceinline__ void store_row(float *dst, int cv0, int tx, int ncv, const float (&acc)[KV][E]) {
+#pragma unroll
+  for (int k = 0; k < KV; k++) {
+    const int cv = cv0 + k * tx;
+    if (cv < ncv) {
+      if constexpr (E == 8) {
+        // dst rows are 32-byte aligned (checked on the host: base and d*4 are)
+        st_stream32(dst + static_cast<size_t>(cv) * E, acc[k]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < E / 4; q++) {
+          const uint4 o = make_uint4(__float_as_uint(acc[k][4 * q]), __float_as_uint(acc[k][4 * q + 1]),
+                                     __float_as_uint(acc[k][4 * q + 2]), __float_as_uint(acc[k][4 * q + 3]));
+          st_stream(dst + static_cast<size_t>(cv) * E + 4 * q, o);
+        }
+      }
+    }
+  }
+}
+
+// Output row r, wherever it belongs.  has_tokens: this rank has tokens for r (peer routing sends
+// nothing otherwise; local output writes the zeros).
+template <bool PEER, int E, int KV>
+__device__ __forceinline__ void emit_row(const ScatterArgs &a, const PeerRoute &pr, int r, int cv0, int tx, int ncv,
+                                         const float (&acc)[KV][E]) {
+  if constexpr (!PEER) {
+    store_row<E, KV>(a.out + static_cast<size_t>(r) * a.d, cv0, tx, ncv, acc);
+  } else {
+    const uint32_t mask = ld_co(pr.src_mask + r);
+    if (mask == (1u << pr.me)) {
+      const size_t off = static_cast<size_t>(ld_co(pr.used_rows + r)) * a.d;
+#pragma unroll 1
+      for (int q = 0; q < pr.n; q++) store_row<E, KV>(pr.grad[q] + off, cv0, tx, ncv, acc);
+    } else {
+      const int j = r / pr.n;
+      if (j >= pr.cap) {
+        atomicOr(pr.status, 1u << 31);
+        return;
+      }
+      store_row<E, KV>(pr.recv[r % pr.n] + (static_cast<size_t>(pr.me) * pr.cap + j) * a.d, cv0, tx, ncv, acc);
+    }
+  }
+}
+
+// blockDim = (tx, ty), tx*ty = kEmbBlock.  grid.x = sub_groups + row CTAs; grid.y tiles columns when
+// a row has more than tx*KV vectors.  The sub-segment groups come first so that the heaviest work
+// starts first.  A row CTA takes groups of rows_cta consecutive output rows (group index strides
+// by the number of row CTAs): it fetches their ranges and the token list they share (consecutive
+// rows are consecutive in the sorted list) into shared memory once, then each thread row walks
+// its rows, so the only dependent global access left per row is the dy load itself.
+// SMALL (peer routing): `small` (small_n floats, a multiple of 4) is copied into slot `me` of every
+// rank's small_recv.  (`sig` is announced by combine_long_kernel, which always follows.)
+struct SmallPush {
+  const float *src;
+  float *dst[kMaxPeers];  // every rank's [n ranks][small_n] area
+  int small_n;
+};
+
+template <typename T, int KV, bool PEER>
+__global__ void __launch_bounds__(kEmbBlock, KV >= 4 ? 1 : 3)
+scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a, const __grid_constant__ PeerRoute pr,
+                    const __grid_constant__ SmallPush sp, const __grid_constant__ PeerSignal sig) {
+  pdl_prologue();
+  using S = Store<T>;
+  constexpr int E = S::kPerVec;
+  __shared__ int s_b[kEmbBlock], s_e[kEmbBlock];
+  __shared__ int s_perm[kScatterPermCap];
+  const int tx = blockDim.x, ty = blockDim.y;
+  const int d = a.d;
+  const int ncv = d / E;
+  const int cv0 = blockIdx.y * (tx * KV) + threadIdx.x;
+  const int tid = threadIdx.y * tx + threadIdx.x;
+  const int tok_offset = a.tok_offset;
+  float acc[KV][E];
+
+  if constexpr (PEER) {
+    if (sp.src != nullptr) {
+      const int n4 = sp.small_n / 4;
+      const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+      const int ctas = gridDim.x * gridDim.y;
+      for (int i = cta * kEmbBlock + tid; i < n4; i += ctas * kEmbBlock) {
+        const float4 v = *reinterpret_cast<const float4 *>(sp.src + 4 * static_cast<size_t>(i));
+        for (int q = 0; q < pr.n; q++)
+          __stcs(reinterpret_cast<float4 *>(sp.dst[q] + static_cast<size_t>(pr.me) * sp.small_n) + i, v);
+      }
+    }
+  }
+
+  if (static_cast<int>(blockIdx.x) < a.sub_groups) {
+    // ------------------------------------------------ sub-segments of long rows
+    const int n_long = ld_co(a.meta), n_sub = ld_co(a.meta + 1);
+    for (int base = blockIdx.x * ty; base < n_sub; base += a.sub_groups * ty) {
+      const int idx = base + threadIdx.y;
+      int lo = 0;
+      if (idx < n_sub) {
+        int hi = n_long;  // last long row whose first sub-segment is <= idx
+        while (hi - lo > 1) {
+          const int mid = (lo + hi) >> 1;
+          if (ld_co(a.long_first + mid) <= idx) lo = mid; else hi = mid;
+        }
+        const int li = ld_co(a.long_row + lo);
+        const int b = ld_co(a.long_b + li) + (idx - ld_co(a.long_first + lo)) * kSubLen;
+        const int e = min(ld_co(a.long_e + li), b + kSubLen);
+        sum_tokens<T, KV>(dy, [&](int j) { return ld_co(a.perm + j) - tok_offset; }, b, e, d, cv0, tx, ncv, acc);
+        store_row<E, KV>(a.scratch + static_cast<size_t>(idx) * d, cv0, tx, ncv, acc);
+      }
+    }
+  } else {
+    // ------------------------------------------------ rows with at most kSubLen tokens
+    const int out_rows = a.out_rows_dev != nullptr ? min(a.out_rows, ld_co(a.out_rows_dev)) : a.out_rows;
+    const int row_ctas = gridDim.x - a.sub_groups;
+    const int rows_cta = a.rows_cta;
+    for (int v_first = (blockIdx.x - a.sub_groups) * rows_cta; v_first < out_rows; v_first += row_ctas * rows_cta) {
+      const int nrows = min(rows_cta, out_rows - v_first);
+      for (int i = tid; i < nrows; i += kEmbBlock) {
+        s_b[i] = ld_co(a.seg_b + v_first + i);
+        s_e[i] = ld_co(a.seg_e + v_first + i);
+      }
+      __syncthreads();
+      // Ranges of consecutive rows are consecutive in the sorted list, except that (rank plans) a row
+      // this rank has no token for carries an empty range anywhere: take the span of the non-empty ones.
+      int p0 = 0, np = kScatterPermCap + 1;
+      {
+        int first = -1, last = -1;
+        for (int i = 0; i < nrows; i++) {
+          if (s_e[i] > s_b[i]) {
+            if (first < 0) first = i;
+            last = i;
+          }
+        }
+        if (first >= 0) {
+          p0 = s_b[first];
+          np = s_e[last] - p0;
+        } else {
+          np = 0;
+        }
+      }
+      const bool staged = np >= 0 && np <= kScatterPermCap;
+      if (staged)
+        for (int i = tid; i < np; i += kEmbBlock) s_perm[i] = ld_co(a.perm + p0 + i) - tok_offset;
+      __syncthreads();
+      // Rows with no token or one token (nearly all of them): U rows at a time, every load of the U
+      // rows issued before the first store, so that U*KV 16-byte loads per thread are in flight.  A
+      // row's sum is still 0.0f + dy (the same bits as the general path below).
+      constexpr int U = KV >= 4 ? 2 : 4;
+      for (int rl0 = threadIdx.y; rl0 < nrows; rl0 += ty * U) {
+        uint4 v[U][KV];
+        int state[U];  // -1: not mine or handled below, 0: empty row, 1: one token
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+          const int rl = rl0 + u * ty;
+          state[u] = -1;
+          if (rl < nrows) {
+            const int b = s_b[rl], cnt = s_e[rl] - b;
+            if (cnt <= 1) state[u] = cnt;
+            if (cnt == 1) {
+              const int t = staged ? s_perm[b - p0] : ld_co(a.perm + b) - tok_offset;
+              const T *src = dy + static_cast<size_t>(t) * d;
+#pragma unroll
+              for (int k = 0; k < KV; k++) {
+                const int cv = cv0 + k * tx;
+                if (cv < ncv) v[u][k] = ld_stream(src + static_cast<size_t>(cv) * E);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+          if (state[u] < 0) continue;
+          if (PEER && state[u] == 0) continue;  // nothing to send for a row without local tokens
+#pragma unroll
+          for (int k = 0; k < KV; k++) {
+#pragma unroll
+            for (int q = 0; q < E; q++) acc[k][q] = 0.f;
+            if (state[u] == 1 && cv0 + k * tx < ncv) {
+              float f[E];
+              S::unpack(v[u][k], f);
+#pragma unroll
+              for (int q = 0; q < E; q++) acc[k][q] += f[q];
+            }
+          }
+          emit_row<PEER, E, KV>(a, pr, v_first + rl0 + u * ty, cv0, tx, ncv, acc);
+        }
+      }
+      // Rows with 2..kSubLen tokens.
+      for (int rl = threadIdx.y; rl < nrows; rl += ty) {
+        const int b = s_b[rl], e = s_e[rl];
+        if (e - b < 2 || e - b > kSubLen) continue;  // long rows are written by the sub-segment groups
+        // one instance of the loop for both sources of the token list (two cost 40 more registers)
+        sum_tokens<T, KV>(dy, [&](int j) { return staged ? s_perm[j - p0] : ld_co(a.perm + j) - tok_offset; }, b, e, d,
+                          cv0, tx, ncv, acc);
+        emit_row<PEER, E, KV>(a, pr, v_first + rl, cv0, tx, ncv, acc);
+      }
+      __syncthreads();  // the staging arrays are refilled by the next group
+    }
+  }
+}
+
+// out[row,:] of every long row = the sum of its scratch rows.  A work item is (long row, block of
+// 32 float4 column vectors); CTAs loop over the items.  Each of the CTA's kCombineSlices warps adds
+// one contiguous slice of the row's sub-segments in order (512 contiguous bytes per sub-segment),
+// then the slice sums are added in warp order through shared memory.  With peer routing this is the
+// last kernel of the pushing phase: its last CTA announces `sig`.
+static_assert(kCombineSlices * 32 == kEmbBlock, "one warp per slice");
+
+template <bool PEER>
+__global__ void __launch_bounds__(kEmbBlock)
+combine_long_kernel(const __grid_constant__ ScatterArgs a, const __grid_constant__ PeerRoute pr,
+                    const __grid_constant__ PeerSignal sig) {
+  pdl_prologue();
+  __shared__ float4 part[kCombineSlices][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int d = a.d;
+  const int nvec = d / 4;
+  const int ncb = (nvec + 31) / 32;  // column blocks per row
+  const int items = ld_co(a.meta) * ncb;
+  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    const int row = item / ncb, c = ((item % ncb) * 32 + lane) * 4;
+    const int s0 = ld_co(a.long_first + row), s1 = ld_co(a.long_first + row + 1);
+    const int per = (s1 - s0 + kCombineSlices - 1) / kCombineSlices;
+    const int b = min(s1, s0 + warp * per), e = min(s1, b + per);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < d) {
+#pragma unroll 8
+      for (int sgm = b; sgm < e; sgm++) {
+        const float4 p = __ldcs(reinterpret_cast<const float4 *>(a.scratch + static_cast<size_t>(sgm) * d + c));
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+      }
+    }
+    __syncthreads();  // part[] of the previous item has been read
+    part[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && c < d) {
+      float4 r = part[0][lane];
+#pragma unroll
+      for (int k = 1; k < kCombineSlices; k++) {
+        const float4 p = part[k][lane];
+        r.x += p.x; r.y += p.y; r.z += p.z; r.w += p.w;
+      }
+      const int li = ld_co(a.long_row + row);
+      const int out_row = a.long_out != nullptr ? ld_co(a.long_out + li) : li;
+      if constexpr (!PEER) {
+        __stcs(reinterpret_cast<float4 *>(a.out + static_cast<size_t>(out_row) * d + c), r);
+      } else {
+        const uint32_t mask = ld_co(pr.src_mask + out_row);
+        if (mask == (1u << pr.me)) {
+          const size_t off = static_cast<size_t>(ld_co(pr.used_rows + out_row)) * d + c;
+          for (int q = 0; q < pr.n; q++) __stcs(reinterpret_cast<float4 *>(pr.grad[q] + off), r);
+        } else if (out_row / pr.n < pr.cap) {
+          __stcs(reinterpret_cast<float4 *>(pr.recv[out_row % pr.n] +
+                                            (static_cast<size_t>(pr.me) * pr.cap + out_row / pr.n) * d + c),
+                 r);
+        } else {
+          atomicOr(pr.status, 1u << 31);
+        }
+      }
+    }
+  }
+  if constexpr (PEER) signal_when_grid_done(sig);
+}
+
+struct BlockShape {
+  int tx, ty;
+};
+inline BlockShape shape_for(int ncv) {
+  int tx = 1;
+  while (tx < kEmbBlock && tx < ncv) tx *= 2;
+  return {tx, kEmbBlock / tx};
+}
+
+// Launches the scatter for storage type T.  `max_sub` bounds the number of sub-segments the plan
+// can hold; `row_ctas` = 0 means one CTA per group of rows.  a.sub_groups / a.rows_cta are set here.
+template <typename T>
+int launch_scatter_rows(const void *dy, ScatterArgs a, int max_sub, int row_ctas, const PeerRoute *peer,
+                        const SmallPush *small, const PeerSignal *sig, cudaStream_t st) {
+  constexpr int E = Store<T>::kPerVec;
+  const int ncv = a.d / E;
+  const BlockShape bs = shape_for(ncv);
+  const int need = ceil_div(ncv, bs.tx);
+  // Four vectors per thread only for bf16 input: with fp32 input that variant needs 122 registers (2 CTAs
+  // per SM) and two column halves of two vectors each are faster (V 32000, D 4096: 201 against 226 us).
+  const int kv = (need >= 4 && E == 8) ? 4 : (need >= 2 ? 2 : 1);
+  // Sub-segment groups loop over the sub-segments, so a few hundred CTAs cover any count.
+  a.sub_groups = min(ceil_div(max_sub, bs.ty), 4 * sm_count());
+  a.rows_cta = bs.ty > kScatterRowsPerCta ? bs.ty : kScatterRowsPerCta;
+  if (peer != nullptr && a.rows_cta > 8 && bs.ty <= 8) a.rows_cta = 8;  // few rows carry tokens: more, smaller groups
+  const int groups = ceil_div(a.out_rows, a.rows_cta);
+  const int row_groups = row_ctas > 0 ? min(groups, row_ctas) : groups;
+  dim3 grid(a.sub_groups + row_groups, ceil_div(ncv, bs.tx * kv));
+  const PeerRoute no_route{};
+  const SmallPush no_small{};
+  const PeerSignal no_signal{};
+  auto go = [&](auto kern) {
+    launch_pdl(kern, grid, dim3(bs.tx, bs.ty), 0, st, static_cast<const T *>(dy), a, peer ? *peer : no_route,
+               small ? *small : no_small, sig ? *sig : no_signal);
+  };
+  if (peer != nullptr) {
+    if (kv == 4) go(scatter_rows_kernel<T, 4, true>);
+    else if (kv == 2) go(scatter_rows_kernel<T, 2, true>);
+    else go(scatter_rows_kernel<T, 1, true>);
+  } else {
+    if (kv == 4) go(scatter_rows_kernel<T, 4, false>);
+    else if (kv == 2) go(scatter_rows_kernel<T, 2, false>);
+    else go(scatter_rows_kernel<T, 1, false>);
+  }
+  DLB_LAUNCH_CHECK("scatter_rows");
+  const int cgrid = 8 * sm_count();  // 8 CTAs fit an SM; each loops over (long row, column block) items
+  if (peer != nullptr)
+    launch_pdl(combine_long_kernel<true>, cgrid, kEmbBlock, 0, st, a, *peer, sig ? *sig : no_signal);
+  else
+    launch_pdl(combine_long_kernel<false>, cgrid, kEmbBlock, 0, st, a, no_route, no_signal);
+  DLB_LAUNCH_CHECK("combine_long");
+  return DLB_OK;
+}
+
+}  // namespace dlb

@@ -311,7 +311,14 @@ PipeShape pick_pipe_shape(int rows, int d, bool two_grads, bool aligned) {
   if (!aligned || d % E != 0) return p;
   const int ncv = d / E;
   if (ncv < 128) return p;
-  const int ct = ncv >= 256 ? 256 : 128;
+  // Column threads per CTA, measured on B200: bf16 rows of 512 vectors and more run best with 512
+  // threads, one vector each, one CTA per SM (32768 x 4096: 133 against 138 us); fp32 rows of 256
+  // vectors with 128 threads, two vectors each (65536 x 1024: 128 against 140 us).
+  int ct = ncv >= 256 ? 256 : 128;
+  if (E == 8 && ncv >= 512) ct = 512;
+  if (E == 4 && ncv == 256) ct = 128;
+  const int want_ct = get_option("ln_bwd_pipe_threads");
+  if ((want_ct == 128 || want_ct == 256 || want_ct == 512) && want_ct <= ncv) ct = want_ct;
   int kv = 1;
   while (kv * ct < ncv) kv *= 2;
   if (kv > 4) return p;
@@ -321,8 +328,15 @@ PipeShape pick_pipe_shape(int rows, int d, bool two_grads, bool aligned) {
   int rt = rt_max;
   while (rt > 1 && rt * row_bytes > 40 * 1024) rt /= 2;
   if (kv == 1 && rt < 2) rt = 2;
+  if (ct == 512 && kv == 1 && !two_grads && 4 * row_bytes <= 64 * 1024) rt = 4;  // 64 KB stages, three of them
+  const int want_rt = get_option("ln_bwd_pipe_rows_per_tile");
+  if ((want_rt == 1 || want_rt == 2 || want_rt == 4 || want_rt == 8) && want_rt <= rt_max && !(kv == 1 && want_rt < 2))
+    rt = want_rt;
   int max_stages = kPipeMaxStages;
   int ctas = (kv <= 2 || sizeof(T) == 4) ? 2 : 1;  // all but the widest bf16 variant fit two CTAs per SM in registers
+  if (ct == 512) ctas = 1;  // 576 threads: one CTA per SM keeps 18 warps and the whole ring
+  const int want_ctas = get_option("ln_bwd_pipe_ctas_per_sm");
+  if (want_ctas == 1) ctas = 1;
   PipeLayout &L = p.layout;
   L.op_bytes = static_cast<unsigned>(static_cast<size_t>(rt) * d * sizeof(T));
   L.stage_bytes = L.op_bytes * (two_grads ? 3 : 2);
@@ -342,7 +356,9 @@ PipeShape pick_pipe_shape(int rows, int d, bool two_grads, bool aligned) {
   L.bar_off = L.stats_off + static_cast<unsigned>(sizeof(float4)) * kPipeMaxStages * rt;
   L.total = L.bar_off + static_cast<unsigned>(sizeof(uint64_t)) * 4 * kPipeMaxStages + 64;
   // Worth it only when every CTA gets a few tiles.
-  if (ceil_div(rows, rt) < 2 * sm_count() * ctas) return p;
+  const int mode = get_option("ln_bwd_pipe");
+  if (mode == 1) return p;
+  if (mode != 2 && ceil_div(rows, rt) < 2 * sm_count() * ctas) return p;
   p.ct = ct;
   p.kv = kv;
   p.rt = rt;
@@ -354,7 +370,7 @@ template <typename T, int CT, int KV, int RT>
 int launch_ln_bwd_pipe(const PipeShape &p, const void *dy_a, const void *dy_b, const void *xhat,
                        const float *inv_std, const float *gamma, void *dx, float *partial,
                        int *n_partial, int rows, int d, cudaStream_t st) {
-  constexpr int MINB = (KV <= 2 || sizeof(T) == 4) ? 2 : 1;
+  constexpr int MINB = (CT <= 256 && (KV <= 2 || sizeof(T) == 4)) ? 2 : 1;
   auto kern = ln_bwd_pipe_kernel<T, CT, KV, RT, MINB>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(p.layout.total));
@@ -373,6 +389,7 @@ int launch_ln_bwd_pipe(const PipeShape &p, const void *dy_a, const void *dy_b, c
 // (CT, KV, RT) combinations pick_pipe_shape can return.
 #define DLB_PIPE_CASES(M)                                         \
   M(128, 1, 2) M(128, 1, 4) M(128, 1, 8) M(128, 2, 1) M(128, 2, 2) M(128, 2, 4) M(128, 4, 1) M(128, 4, 2) \
-  M(256, 1, 2) M(256, 1, 4) M(256, 1, 8) M(256, 2, 1) M(256, 2, 2) M(256, 2, 4) M(256, 4, 1) M(256, 4, 2)
+  M(256, 1, 2) M(256, 1, 4) M(256, 1, 8) M(256, 2, 1) M(256, 2, 2) M(256, 2, 4) M(256, 4, 1) M(256, 4, 2) \
+  M(512, 1, 2) M(512, 1, 4) M(512, 1, 8) M(512, 2, 1) M(512, 2, 2) M(512, 2, 4)
 
 }  // namespace dlb

@@ -120,31 +120,35 @@ def embed_scatter_bwd(dy, ids, vocab, workspace, grad=None):
     return grad
 
 
-def embed_compact_workspace(vocab, device):
-    return _workspace(capi.lib().dlb_embed_compact_workspace_bytes(vocab), device)
+def embed_rank_plan_workspace(vocab, tokens_per_rank, d, device):
+    return _workspace(capi.lib().dlb_embed_rank_plan_bytes(vocab, tokens_per_rank, d), device)
 
 
-def embed_compact_plan(global_plan, global_tokens, local_plan, local_tokens, vocab, d, compact_ws=None, stream=None):
-    """Numbers the table rows any rank uses; compact_ws[:4].view(int32)[0] is their count (device)."""
-    compact_ws = embed_compact_workspace(vocab, global_plan.device) if compact_ws is None else compact_ws
-    check(capi.lib().dlb_embed_compact_plan(ptr(global_plan), global_tokens, ptr(local_plan), local_tokens,
-                                            ptr(compact_ws), compact_ws.numel(), vocab, d,
-                                            current_stream() if stream is None else stream))
-    return compact_ws
+def embed_rank_plan(global_plan, global_tokens, tokens_per_rank, n_ranks, my_rank, vocab, d, rank_plan=None, stream=None):
+    """Numbers the table rows any rank uses and finds this rank's tokens of each, from the plan of the
+    gathered ids; rank_plan[:4].view(int32)[0] is the number of used rows (device)."""
+    if rank_plan is None:
+        rank_plan = embed_rank_plan_workspace(vocab, tokens_per_rank, d, global_plan.device)
+    check(capi.lib().dlb_embed_rank_plan(ptr(global_plan), global_tokens, tokens_per_rank, n_ranks, my_rank,
+                                         ptr(rank_plan), rank_plan.numel(), vocab, d,
+                                         current_stream() if stream is None else stream))
+    return rank_plan
 
 
-def embed_scatter_bwd_compact(dy, local_plan, compact_ws, compact_rows, used_rows, vocab, stream=None):
-    _need_cuda(dy, local_plan, compact_ws, compact_rows)
-    n, d = dy.shape
-    check(capi.lib().dlb_embed_scatter_bwd_compact(ptr(dy), ptr(local_plan), local_plan.numel(), ptr(compact_ws),
-                                                   ptr(compact_rows), used_rows, n, vocab, d, dtype_of(dy),
-                                                   current_stream() if stream is None else stream))
+def embed_scatter_bwd_compact(dy, global_plan, global_tokens, rank_plan, tokens_per_rank, my_rank, compact_rows, vocab,
+                              stream=None):
+    """compact_rows [max_rows, d]: the first `used` rows receive this rank's sums."""
+    _need_cuda(dy, global_plan, rank_plan, compact_rows)
+    d = dy.shape[1]
+    check(capi.lib().dlb_embed_scatter_bwd_compact(ptr(dy), ptr(global_plan), global_tokens, ptr(rank_plan),
+                                                   tokens_per_rank, my_rank, ptr(compact_rows), compact_rows.shape[0],
+                                                   vocab, d, dtype_of(dy), current_stream() if stream is None else stream))
     return compact_rows
 
 
-def embed_expand_rows(compact_rows, compact_ws, grad, what=3, stream=None):
+def embed_expand_rows(compact_rows, rank_plan, tokens_per_rank, grad, what=3, stream=None):
     vocab, d = grad.shape
-    check(capi.lib().dlb_embed_expand_rows(ptr(compact_rows), ptr(compact_ws), ptr(grad), vocab, d, what,
+    check(capi.lib().dlb_embed_expand_rows(ptr(compact_rows), ptr(rank_plan), tokens_per_rank, ptr(grad), vocab, d, what,
                                            current_stream() if stream is None else stream))
     return grad
 
@@ -310,19 +314,33 @@ def _addr_array(addresses):
     return (ctypes.c_void_p * len(addresses))(*addresses)
 
 
-def embed_scatter_bwd_peer(dy, local_plan, compact_ws, peer_recv, my_rank, cap_rows, used_rows, vocab, stream=None):
-    """peer_recv: device addresses (ints) of every rank's receive area as mapped on this GPU."""
-    n, d = dy.shape
-    check(capi.lib().dlb_embed_scatter_bwd_peer(ptr(dy), ptr(local_plan), local_plan.numel(), ptr(compact_ws),
-                                                _addr_array(peer_recv), len(peer_recv), my_rank, cap_rows,
-                                                used_rows, n, vocab, d, dtype_of(dy),
-                                                current_stream() if stream is None else stream))
+def peer_group(n_ranks, my_rank, cap_rows, flags, recv, grad, status, small=None, small_n=0, timeout_ms=2000):
+    """A capi.PeerGroup from lists of device addresses (ints), one per rank, as mapped on this GPU."""
+    import ctypes
+    g = capi.PeerGroup()
+    g.n_ranks, g.my_rank, g.cap_rows, g.small_n, g.timeout_ms = n_ranks, my_rank, cap_rows, small_n, timeout_ms
+    for q in range(n_ranks):
+        g.flags[q], g.recv[q], g.grad[q] = flags[q], recv[q], grad[q]
+        g.small[q] = small[q] if small is not None else None
+    g.status = ptr(status)
+    g._keepalive = status
+    return g
 
 
-def embed_reduce_broadcast_peer(my_recv, compact_ws, peer_grad, my_rank, cap_rows, vocab, d, stream=None):
-    """peer_grad: device addresses (ints) of every rank's dense [vocab, d] gradient as mapped on this GPU."""
-    check(capi.lib().dlb_embed_reduce_broadcast_peer(ptr(my_recv), ptr(compact_ws), _addr_array(peer_grad),
-                                                     len(peer_grad), my_rank, cap_rows, vocab, d,
+def embed_scatter_bwd_peer(dy, global_plan, global_tokens, rank_plan, tokens_per_rank, group, small, max_rows, vocab,
+                           channel, epoch, stream=None):
+    import ctypes
+    d = dy.shape[1]
+    check(capi.lib().dlb_embed_scatter_bwd_peer(ptr(dy), ptr(global_plan), global_tokens, ptr(rank_plan), tokens_per_rank,
+                                                ctypes.byref(group), ptr(small), max_rows, vocab, d, dtype_of(dy),
+                                                channel, epoch, current_stream() if stream is None else stream))
+
+
+def embed_reduce_broadcast_peer(rank_plan, tokens_per_rank, group, small_out, vocab, d, wait_channel, wait_epoch,
+                                signal_channel, signal_epoch, stream=None):
+    import ctypes
+    check(capi.lib().dlb_embed_reduce_broadcast_peer(ptr(rank_plan), tokens_per_rank, ctypes.byref(group), ptr(small_out),
+                                                     vocab, d, wait_channel, wait_epoch, signal_channel, signal_epoch,
                                                      current_stream() if stream is None else stream))
 
 
@@ -330,6 +348,19 @@ def peer_barrier(peer_flags, my_rank, channel, epoch, status, timeout_ms=2000, s
     """peer_flags: device addresses (ints) of every rank's flag words; status: uint32/int32 device tensor [1]."""
     check(capi.lib().dlb_peer_barrier(_addr_array(peer_flags), len(peer_flags), my_rank, channel, epoch, timeout_ms,
                                       ptr(status), current_stream() if stream is None else stream))
+
+
+def peer_wait(peer_flags, my_rank, channel, epoch, status, timeout_ms=2000, stream=None):
+    check(capi.lib().dlb_peer_wait(_addr_array(peer_flags), len(peer_flags), my_rank, channel, epoch, timeout_ms,
+                                   ptr(status), current_stream() if stream is None else stream))
+
+
+def peer_put(src, peer_dst, peer_flags, my_rank, channel, epoch, status, wait=True, timeout_ms=2000, stream=None):
+    """Copies `src` into slot my_rank of every rank's buffer (peer_dst: device addresses), announces, waits."""
+    nbytes = src.numel() * src.element_size()
+    check(capi.lib().dlb_peer_put(ptr(src), nbytes, _addr_array(peer_dst), _addr_array(peer_flags), len(peer_flags),
+                                  my_rank, channel, epoch, int(wait), timeout_ms, ptr(status),
+                                  current_stream() if stream is None else stream))
 
 
 # --- checkpoint staging ---------------------------------------------------------------------

@@ -32,46 +32,73 @@ def allreduce_param_grads(dist, small_grads, table_grad) -> None:
 
 
 class PeerExchange:
-    """Buffers of the peer-memory exchange of the embedding-table gradient, one object per rank.
+    """Buffers and step counters of the peer-memory exchange of the embedding-table gradient, one
+    object per rank.
 
-    Three symmetric allocations (torch.distributed._symmetric_memory: the same buffer on every rank,
-    each mapped into every rank's address space): the receive area [world][cap_rows][d] fp32 that
-    peers push partial rows into, the dense [vocab, d] gradient that owners broadcast reduced rows
-    into, and the flag words of the barrier.  The kernels and the barrier are the library's own
-    (dlb_embed_scatter_bwd_peer, dlb_embed_reduce_broadcast_peer, dlb_peer_barrier); torch only
-    allocates and exchanges the memory handles.
+    Symmetric allocations (torch.distributed._symmetric_memory: the same buffer on every rank, each
+    mapped into every rank's address space): the receive area [world][cap_rows][d] fp32 that peers push
+    shared rows into, the dense [vocab, d] gradient that finished rows are stored into, the area the
+    small parameter gradients of every rank land in, the gathered token ids of all ranks, and the flag
+    words.  The kernels, the flags and the waits are the library's own (dlb_peer_put,
+    dlb_embed_scatter_bwd_peer, dlb_embed_reduce_broadcast_peer, dlb_peer_wait); torch only allocates
+    the memory and exchanges its handles.
+
+    Channels: 0 = partial rows pushed, 1 = tables complete, 2 = token ids gathered, 3 = set-up barrier.
     """
 
-    def __init__(self, dist, vocab, d, max_used_rows, device):
+    CH_PUSHED, CH_DONE, CH_IDS, CH_SETUP = 0, 1, 2, 3
+
+    def __init__(self, dist, vocab, d, max_used_rows, device, tokens_per_rank=0, small_n=0, timeout_ms=2000):
         import torch
         import torch.distributed._symmetric_memory as symm
-        from . import capi
+        from . import capi, ops
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
         self.vocab, self.d = vocab, d
         self.cap_rows = (max_used_rows + self.world - 1) // self.world
+        self.small_n = small_n
+        self.timeout_ms = timeout_ms
         group = dist.group.WORLD
-        self.recv = symm.empty(self.world * self.cap_rows * d, dtype=torch.float32, device=device)
-        self.grad = symm.empty(vocab * d, dtype=torch.float32, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        self.recv = symm.empty(self.world * self.cap_rows * d, **f32)
+        self.grad = symm.empty(vocab * d, **f32)
         self.flags = symm.empty(capi.lib().dlb_peer_flags_bytes() // 4, dtype=torch.int32, device=device)
-        self.recv.zero_()
+        self.small = symm.empty(max(self.world * small_n, 4), **f32)
+        self.ids_all = symm.empty(max(self.world * tokens_per_rank, 4), dtype=torch.int32, device=device)
         self.flags.zero_()
-        self._handles = [symm.rendezvous(t, group) for t in (self.recv, self.grad, self.flags)]
-        self.recv_ptrs = [int(p) for p in self._handles[0].buffer_ptrs]
-        self.grad_ptrs = [int(p) for p in self._handles[1].buffer_ptrs]
-        self.flag_ptrs = [int(p) for p in self._handles[2].buffer_ptrs]
+        buffers = (self.recv, self.grad, self.flags, self.small, self.ids_all)
+        self._handles = [symm.rendezvous(t, group) for t in buffers]
+        ptrs = [[int(p) for p in h.buffer_ptrs] for h in self._handles]
+        self.recv_ptrs, self.grad_ptrs, self.flag_ptrs, self.small_ptrs, self.ids_ptrs = ptrs
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.group = ops.peer_group(self.world, self.rank, self.cap_rows, self.flag_ptrs, self.recv_ptrs,
+                                    self.grad_ptrs, self.status, self.small_ptrs if small_n else None, small_n,
+                                    timeout_ms)
         self.epoch = [0, 0, 0, 0]
         torch.cuda.synchronize(device)
-        dist.barrier()  # every receive area and flag word is zero before anyone writes
+        dist.barrier()  # every flag word is zero before anyone writes
 
     def table_grad(self):
         return self.grad.view(self.vocab, self.d)
 
-    def barrier(self, channel, stream=None, timeout_ms=2000):
-        from . import ops
+    def next_epoch(self, channel) -> int:
         self.epoch[channel] += 1
-        ops.peer_barrier(self.flag_ptrs, self.rank, channel, self.epoch[channel], self.status, timeout_ms, stream)
+        return self.epoch[channel]
+
+    def barrier(self, channel=CH_SETUP, stream=None):
+        from . import ops
+        ops.peer_barrier(self.flag_ptrs, self.rank, channel, self.next_epoch(channel), self.status, self.timeout_ms, stream)
+
+    def wait(self, channel, stream=None):
+        """Waits for the announcement a kernel made with the channel's current epoch."""
+        from . import ops
+        ops.peer_wait(self.flag_ptrs, self.rank, channel, self.epoch[channel], self.status, self.timeout_ms, stream)
+
+    def gather_ids(self, ids, stream=None):
+        """All-gather of this rank's token ids into ids_all on every rank (one kernel: push, announce, wait)."""
+        from . import ops
+        ops.peer_put(ids, self.ids_ptrs, self.flag_ptrs, self.rank, self.CH_IDS, self.next_epoch(self.CH_IDS),
+                     self.status, True, self.timeout_ms, stream)
 
     def timed_out(self) -> int:
-        """Bit mask of barrier channels whose wait gave up (synchronises)."""
-        return int(self.status.item())
+        """Status bits (synchronises): bit c = a wait on channel c gave up; bit 31 = cap_rows too small."""
+        return int(self.status.item()) & 0xffffffff

@@ -60,6 +60,19 @@ DLB_API const char *dlb_last_error(void);
  * load (every stream, every thread).  Used by benchmarks to report launches. */
 DLB_API uint64_t dlb_launch_count(void);
 
+/* Kernel-variant overrides for measurements: where a kernel exists in more than one form,
+ * the heuristic's choice can be replaced so that both forms are timed in one process on the
+ * same buffers.  value 0 gives the choice back to the heuristic; an override that does not
+ * fit a call's shape is ignored for that call.  Results are the same whatever the choice.
+ *   "gather_rows_in_flight"      4 | 8   table rows a thread loads before its first store
+ *   "ln_bwd_pipe"                1 never the bulk-copy pipeline | 2 whenever the shape allows
+ *   "ln_bwd_pipe_threads"        128 | 256 | 512 column threads per CTA
+ *   "ln_bwd_pipe_ctas_per_sm"    1 | 2
+ *   "ln_bwd_pipe_rows_per_tile"  1 | 2 | 4 | 8
+ *   "act_bwd_partial_rows"       upper bound of the partial rows of a fused bias gradient
+ * Process-wide, not synchronised with calls in flight.  No counterpart in the reference. */
+DLB_API int dlb_set_option(const char *name, int value);
+
 /* The pipelined kernels wait on shared-memory barriers for at most one second of
  * wall-clock time each; a wait that gives up lets the kernel finish (with wrong
  * results) and bumps a per-device counter instead of hanging the GPU.  This
@@ -177,35 +190,37 @@ DLB_API int dlb_embed_scatter_bwd(const void *dy, const int32_t *ids,
                                   size_t workspace_bytes, int num_tokens,
                                   int vocab, int d, int dtype, void *stream);
 
-/* Multi-GPU form of the table gradient (token rows sharded over ranks; the reference has
- * no multi-GPU path, so these have no counterpart there -- they serve the all-reduce of
- * what src/embedding.cuh:82-92 produces).  Instead of all-reducing the dense [vocab, d]
- * gradient, every rank numbers the table rows that ANY rank refers to ("used" rows, in
- * ascending id -- the same numbering on every rank), scatter-adds its own tokens into a
- * compact [used, d] buffer (zeros for rows only other ranks use), all-reduces that, and
- * expands it into the dense gradient:
- *   dlb_embed_sort_tokens on the gathered ids of all ranks  -> global plan
- *   dlb_embed_sort_tokens on this rank's ids                -> local plan
- *   dlb_embed_compact_plan(global, local)                   -> compact workspace; its
- *       first int32 (device memory) is the number of used rows
- *   dlb_embed_scatter_bwd_compact(dy, local plan, compact)  -> compact_rows [used, d]
- *   all-reduce compact_rows[0 .. used*d)
- *   dlb_embed_expand_rows(compact_rows, compact, grad, what): what&1 zero the rows no
- *       rank uses, what&2 copy the used rows (the zeroing needs only the compact plan,
- *       so it can run beside the all-reduce).
- * used_rows passed to the scatter must be the value read from the compact workspace. */
-DLB_API size_t dlb_embed_compact_workspace_bytes(int vocab);
-DLB_API int dlb_embed_compact_plan(const void *global_plan, int global_tokens,
-                                   const void *local_plan, int local_tokens,
-                                   void *compact_ws, size_t compact_bytes, int vocab,
-                                   int d, void *stream);
-DLB_API int dlb_embed_scatter_bwd_compact(const void *dy, void *local_plan,
-                                          size_t local_plan_bytes, const void *compact_ws,
-                                          float *compact_rows, int used_rows,
-                                          int local_tokens, int vocab, int d, int dtype,
-                                          void *stream);
-DLB_API int dlb_embed_expand_rows(const float *compact_rows, const void *compact_ws,
-                                  float *grad, int vocab, int d, int what, void *stream);
+/* Multi-GPU form of the table gradient (token rows sharded over the ranks of one node; the
+ * reference has no multi-GPU path, so these have no counterpart there -- they serve the
+ * all-reduce of what src/embedding.cuh:82-92 produces).  Every rank gathers the ids of all
+ * ranks (rank r holds tokens [r*tokens_per_rank, (r+1)*tokens_per_rank) of the gathered
+ * list; the last rank may hold fewer) and sorts them once:
+ *   dlb_embed_sort_tokens on the gathered ids  -> global plan (the same on every rank)
+ *   dlb_embed_rank_plan(global plan, my_rank)  -> rank plan: the table rows ANY rank
+ *       refers to ("used" rows) numbered 0..used-1 in ascending id ("slots", the same
+ *       numbering on every rank), per slot this rank's tokens and the set of ranks that
+ *       have tokens for it.  No second sort: a stable sort leaves each rank's tokens of a
+ *       row contiguous.  The first int32 of the rank plan (device memory) is `used`.
+ * Instead of all-reducing the dense [vocab, d] gradient, either
+ *   dlb_embed_scatter_bwd_compact -> [used, d] buffer of this rank's sums (zeros for rows
+ *       only other ranks use); all-reduce its first used*d floats; then
+ *   dlb_embed_expand_rows(compact_rows, rank plan, grad, what): what&1 zero the rows no
+ *       rank uses, what&2 copy the used rows (the zeroing needs only the plan, so it can
+ *       run beside the all-reduce);
+ * or the peer-memory exchange further down.  max_rows bounds the rows written (pass
+ * min(vocab, all tokens) or the exact count); the exact count is read on the device, so
+ * the host need not wait for the plan. */
+DLB_API size_t dlb_embed_rank_plan_bytes(int vocab, int tokens_per_rank, int d);
+DLB_API int dlb_embed_rank_plan(const void *global_plan, int global_tokens, int tokens_per_rank,
+                                int n_ranks, int my_rank, void *rank_plan, size_t rank_plan_bytes,
+                                int vocab, int d, void *stream);
+DLB_API int dlb_embed_scatter_bwd_compact(const void *dy, const void *global_plan, int global_tokens,
+                                          void *rank_plan, int tokens_per_rank, int my_rank,
+                                          float *compact_rows, int max_rows, int vocab, int d,
+                                          int dtype, void *stream);
+DLB_API int dlb_embed_expand_rows(const float *compact_rows, const void *rank_plan,
+                                  int tokens_per_rank, float *grad, int vocab, int d, int what,
+                                  void *stream);
 
 /* ---- bias + activation epilogues -------------------------------------------
  * Forward: pre = x + (bias ? bias[col] : 0); y = act(pre) over [rows,cols].
@@ -299,52 +314,86 @@ DLB_API int dlb_checkpoint_unpack(int n_groups, float *const *h_params, const in
                                   const void *d_body, size_t body_bytes, void *stream);
 
 /* ---- multi-GPU: table gradient exchanged over peer memory (one node) ----------
- * No counterpart in the reference (it is single-GPU).  Alternative to the NCCL
- * all-reduce of the compacted rows: the scatter-add and the exchange are fused.
- * Used row number s (dlb_embed_compact_plan) belongs to rank s % n_ranks;
- * n_ranks is at most 16.
+ * No counterpart in the reference (it is single-GPU).  Alternative to the all-reduce of
+ * the compacted rows: the scatter-add, the exchange and the expansion into the dense
+ * table are fused into two kernels that signal and wait through flag words themselves.
  *
- * dlb_embed_scatter_bwd_peer: dlb_embed_scatter_bwd_compact, except that each row
- * this rank has tokens for is stored straight into the OWNER's receive area
- * (h_peer_recv[owner], laid out [n_ranks sources][cap_rows][d] fp32, zero where
- * nothing arrives) through the peer mapping; rows without local tokens send
- * nothing.  h_peer_recv is a HOST array of n_ranks device addresses valid on the
- * calling GPU (its own area at index my_rank).  used_rows may be the exact
- * number of used rows or any upper bound of it (e.g. min(vocab, all tokens)):
- * it only sizes the launch, the kernels read the exact count from the plan on
- * the device, so the host need not wait for the plan.
+ * Every rank allocates, in memory that all ranks of the node have mapped (CUDA IPC,
+ * cuMem fabric handles, torch symmetric memory ...):
+ *   flags  dlb_peer_flags_bytes() bytes, zero before the first use
+ *   recv   [n_ranks sources][cap_rows][d] fp32, the partial rows other ranks push
+ *          (cap_rows * n_ranks must cover the used rows; no initial contents required)
+ *   grad   the dense [vocab, d] fp32 table gradient (the result)
+ *   small  [n_ranks][small_n] fp32 (optional): every rank's small parameter gradients
+ * and fills a dlb_peer_group with the addresses of all ranks' buffers AS MAPPED ON THE
+ * CALLING GPU (its own at index my_rank) plus a device status word of its own.
  *
- * dlb_embed_reduce_broadcast_peer: for every row this rank owns, adds the n_ranks
- * partial sums of its receive area in rank order (reproducible), puts the
- * receive rows back to zero, and stores the sum into that row of EVERY rank's
- * dense [vocab, d] gradient (h_peer_grad, peer mappings): reduction, broadcast
- * and dense expansion in one pass.  Rows no rank uses are zeroed locally with
- * dlb_embed_expand_rows(what = 1).
+ * dlb_embed_scatter_bwd_peer: sums this rank's tokens per used row.  A row that ONLY this
+ * rank has tokens for is final: it is stored straight into row v of every rank's grad.
+ * A row several ranks share goes to the receive area of the slot's owner (slot % n_ranks)
+ * at recv[my_rank][slot / n_ranks].  Rows without local tokens send nothing.  If `small`
+ * is given, its small_n floats are copied to small[q][my_rank] on every rank q.  When the
+ * last CTA has issued its stores the kernel announces (signal_channel, signal_epoch).
  *
- * Between the two calls, and after the second, all ranks must meet in
- * dlb_peer_barrier, so that a rank reads what its peers wrote only after they
- * wrote it.  The receive areas start zeroed (caller), followed by one barrier. */
-DLB_API int dlb_embed_scatter_bwd_peer(const void *dy, void *local_plan, size_t local_plan_bytes,
-                                       const void *compact_ws, float *const *h_peer_recv,
-                                       int n_ranks, int my_rank, int cap_rows, int used_rows,
-                                       int local_tokens, int vocab, int d, int dtype,
-                                       void *stream);
-DLB_API int dlb_embed_reduce_broadcast_peer(float *my_recv, const void *compact_ws,
-                                            float *const *h_peer_grad, int n_ranks, int my_rank,
-                                            int cap_rows, int vocab, int d, void *stream);
+ * dlb_embed_reduce_broadcast_peer: waits (bounded by timeout_ms) until every rank has
+ * announced (wait_channel, wait_epoch); for each slot it owns that several ranks share it
+ * adds the partial rows in rank order and stores the sum into row v of every rank's grad;
+ * if small_out is given it receives the rank-order sum of the n_ranks small buffers (the
+ * same bits on every rank).  Then it announces (signal_channel, signal_epoch); follow it
+ * with dlb_peer_wait on that channel: after it every rank's table is complete.
+ *
+ * Rows no rank uses are zeroed locally: dlb_embed_expand_rows(what = 1), any stream.
+ * Epochs per channel grow by one per use, the same on all ranks.  A rank may start the
+ * next step's dlb_embed_scatter_bwd_peer only when every rank is done with the tables of
+ * this step (its consumer has run): the all-gather of the next step's ids (dlb_peer_put
+ * with wait, stream-ordered after the consumer) is that barrier.  Status bits: bit c =
+ * a wait on channel c gave up; bit 31 = cap_rows was too small for a slot (row dropped). */
+#define DLB_MAX_PEERS 16
+typedef struct dlb_peer_group {
+  int n_ranks;                    /* 1..DLB_MAX_PEERS */
+  int my_rank;
+  int cap_rows;                   /* rows per source rank in a receive area */
+  int small_n;                    /* floats per small-gradient buffer, a multiple of 4 (0: none) */
+  int timeout_ms;                 /* bound of every wait inside the kernels, 1..10000 */
+  int reserved;
+  uint32_t *flags[DLB_MAX_PEERS]; /* per rank, as mapped on the calling GPU */
+  float *recv[DLB_MAX_PEERS];
+  float *grad[DLB_MAX_PEERS];
+  float *small[DLB_MAX_PEERS];    /* may be NULL when small_n == 0 */
+  uint32_t *status;               /* this rank's device status word (zero before the first use) */
+} dlb_peer_group;
 
-/* Barrier between the ranks' streams over peer-mapped flags.  Every rank owns
- * dlb_peer_flags_bytes() bytes of zero-initialised memory that all ranks have
- * mapped (h_peer_flags: HOST array of n_ranks device addresses).  The call
- * enqueues one small kernel: it announces `epoch` to every rank and waits until
- * every rank has announced it.  Per channel (0..3) epochs must be 1, 2, 3, ... in
- * call order, the same on all ranks.  The wait gives up after timeout_ms: bit
- * `channel` of *d_status (device memory) is then set and the kernel returns; the
- * caller checks it after synchronising.  One rank per GPU. */
+DLB_API int dlb_embed_scatter_bwd_peer(const void *dy, const void *global_plan, int global_tokens,
+                                       void *rank_plan, int tokens_per_rank,
+                                       const dlb_peer_group *peers, const float *small, int max_rows,
+                                       int vocab, int d, int dtype, int signal_channel,
+                                       uint32_t signal_epoch, void *stream);
+DLB_API int dlb_embed_reduce_broadcast_peer(void *rank_plan, int tokens_per_rank,
+                                            const dlb_peer_group *peers, float *small_out, int vocab,
+                                            int d, int wait_channel, uint32_t wait_epoch,
+                                            int signal_channel, uint32_t signal_epoch, void *stream);
+
+/* Flags between the ranks' streams.  Every rank owns dlb_peer_flags_bytes() bytes of
+ * zero-initialised memory that all ranks have mapped (h_peer_flags: HOST array of n_ranks
+ * device addresses).  Per channel (0..3) epochs must be 1, 2, 3, ... in call order, the
+ * same on all ranks.  Every wait gives up after timeout_ms: bit `channel` of *d_status
+ * (device memory) is then set and the kernel returns; the caller checks it after
+ * synchronising.  One rank per GPU: kernels that wait for one another must never share one.
+ *   dlb_peer_barrier  announces `epoch` to every rank and waits until every rank has.
+ *   dlb_peer_wait     the waiting half alone (the announcement came from a kernel).
+ *   dlb_peer_put      an all-gather by pushes: copies `bytes` (a multiple of 16) from src
+ *                     into h_peer_dst[q] + my_rank*bytes on every rank q, announces, and
+ *                     with wait != 0 waits for every rank's announcement, so that this
+ *                     rank's gathered buffer is complete when the kernel ends. */
 DLB_API size_t dlb_peer_flags_bytes(void);
 DLB_API int dlb_peer_barrier(uint32_t *const *h_peer_flags, int n_ranks, int my_rank,
                              int channel, uint32_t epoch, int timeout_ms, uint32_t *d_status,
                              void *stream);
+DLB_API int dlb_peer_wait(uint32_t *const *h_peer_flags, int n_ranks, int my_rank, int channel,
+                          uint32_t epoch, int timeout_ms, uint32_t *d_status, void *stream);
+DLB_API int dlb_peer_put(const void *src, size_t bytes, void *const *h_peer_dst,
+                         uint32_t *const *h_peer_flags, int n_ranks, int my_rank, int channel,
+                         uint32_t epoch, int wait, int timeout_ms, uint32_t *d_status, void *stream);
 
 /* ---- pass-through dense ops (fp32 only, correctness implementations) ----------
  * The matrix products, row softmax and loss kernels that the reference's

@@ -1,9 +1,10 @@
 """Worker of tests/test_multi_gpu.py: one process per GPU (torchrun), NCCL for the plumbing.
 
 Every rank holds a shard of the tokens.  The table gradient is computed through the peer-memory exchange
-(dlb_embed_scatter_bwd_peer -> dlb_peer_barrier -> dlb_embed_reduce_broadcast_peer -> dlb_peer_barrier) three
-steps in a row with fresh ids and gradients, and checked on every rank against the dense single-rank
-gradient of ALL tokens (gathered here only for the check).  Prints "PEER_EXCHANGE_OK <rank>" on success.
+(dlb_peer_put of the ids -> one sort -> dlb_embed_rank_plan -> dlb_embed_scatter_bwd_peer ->
+dlb_embed_reduce_broadcast_peer -> dlb_peer_wait) three steps in a row with fresh ids and gradients, and
+checked on every rank against the dense single-rank gradient of ALL tokens (gathered here only for the
+check); so are the small gradients that ride along.  Prints "PEER_EXCHANGE_OK <rank>" on success.
 """
 import os
 import sys
@@ -26,40 +27,45 @@ def main():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
-    vocab, d, per_rank = 4000, 512, 3000
+    vocab, d, per_rank, small_n = 4000, 512, 3000, 1024
     total = per_rank * world
-    px = PeerExchange(dist, vocab, d, min(vocab, total), dev)
+    px = PeerExchange(dist, vocab, d, min(vocab, total), dev, tokens_per_rank=per_rank, small_n=small_n)
+    px.barrier()
     table = px.table_grad()
     side = torch.cuda.Stream()
     for step in range(3):
         ids_all = torch.from_numpy(zipf_ids(rng_for(500 + step, 0), total, vocab).astype(np.int32)).to(dev)
         dy_all = torch.from_numpy(rng_for(500 + step, 1).standard_normal((total, d)).astype(np.float32)).to(dev)
+        small_all = torch.from_numpy(rng_for(500 + step, 2).standard_normal((world, small_n)).astype(np.float32)).to(dev)
         ids, dy = ids_all[rank * per_rank:(rank + 1) * per_rank].contiguous(), dy_all[rank * per_rank:(rank + 1) * per_rank].contiguous()
-        gathered = torch.empty(total, dtype=torch.int32, device=dev)
-        dist.all_gather_into_tensor(gathered, ids)
-        assert torch.equal(gathered, ids_all)
-        local_plan = ops.embed_sort_tokens(ids, vocab, d)
-        global_plan = ops.embed_sort_tokens(gathered, vocab, d)
-        compact = ops.embed_compact_plan(global_plan, total, local_plan, per_rank, vocab, d)
-        used = int(compact[:4].view(torch.int32)[0].item())
+        small = small_all[rank].clone()
         table.fill_(float(3 + step))  # stale contents must vanish
-        torch.cuda.synchronize()
-        dist.barrier()                # nobody pushes rows into a table that is still being filled
-        ops.embed_scatter_bwd_peer(dy, local_plan, compact, px.recv_ptrs, rank, px.cap_rows,
-                                   used if step == 0 else min(vocab, total), vocab)
+        # The gather of the ids is the barrier that keeps a fast rank from storing rows into a table its
+        # owner is still filling (or, in training, still reading): it is stream-ordered after the fill.
+        px.gather_ids(ids)
+        gathered = px.ids_all[:total]
+        global_plan = ops.embed_sort_tokens(gathered, vocab, d)
+        rank_plan = ops.embed_rank_plan(global_plan, total, per_rank, world, rank, vocab, d)
         side.wait_stream(torch.cuda.current_stream())
-        ops.embed_expand_rows(None, compact, table, what=1, stream=side.cuda_stream)
-        px.barrier(0)
-        ops.embed_reduce_broadcast_peer(px.recv, compact, px.grad_ptrs, rank, px.cap_rows, vocab, d)
+        ops.embed_expand_rows(None, rank_plan, per_rank, table, what=1, stream=side.cuda_stream)
+        pushed, done = px.next_epoch(px.CH_PUSHED), px.next_epoch(px.CH_DONE)
+        ops.embed_scatter_bwd_peer(dy, global_plan, total, rank_plan, per_rank, px.group, small, min(vocab, total), vocab,
+                                   px.CH_PUSHED, pushed)
+        ops.embed_reduce_broadcast_peer(rank_plan, per_rank, px.group, small, vocab, d, px.CH_PUSHED, pushed,
+                                        px.CH_DONE, done)
         torch.cuda.current_stream().wait_stream(side)
-        px.barrier(1)
+        px.wait(px.CH_DONE)
         torch.cuda.synchronize()
-        assert px.timed_out() == 0, "a barrier wait gave up"
+        assert px.timed_out() == 0, "a wait gave up or the receive area was too small"
+        assert torch.equal(gathered, ids_all)
         want = torch.zeros(vocab, d, device=dev)
-        ops.embed_scatter_bwd(dy_all, ids_all, vocab, global_plan, grad=want)
+        ops.embed_scatter_bwd(dy_all, ids_all, vocab, ops.embed_sort_tokens(ids_all, vocab, d), grad=want)
         err = rel_err(table.cpu().numpy(), want.cpu().numpy())
         assert err <= 3e-5, (step, rank, err)
-        assert float(px.recv.abs().sum()) == 0.0, "receive area must be zero again"
+        want_small = small_all[0].clone()
+        for r in range(1, world):
+            want_small = want_small + small_all[r]
+        assert torch.equal(small, want_small), (step, rank)
         # every rank holds the same bits
         mine = table.clone()
         dist.broadcast(mine, src=0)

@@ -10,8 +10,8 @@ Tolerances: bit-exact fp32 for gather + PE and the activation epilogues; <= 1e-5
 relative (|a-b| / max(|a|, |b|, rms)) for layer norm and the scatter-add; sums of c fp32
 terms (column sums over c = R rows, table rows with c tokens) against the reference's
 one-by-one fp32 accumulation max(1e-5, 4*sqrt(c)*2^-24) (that accumulation is itself that
-far from the exact sum) and <= 1e-5 against the fp64 sum for the column sums;
-<= 1e-2 with bf16 storage.
+far from the exact sum) and <= 1e-5 against the fp64 sum (column sums: rms of the
+vector; table rows: rms of the row); <= 1e-2 with bf16 storage.
 """
 import numpy as np
 import pytest
@@ -48,6 +48,19 @@ def rel_l2_dev(got, want) -> float:
         num += float(((g - w) ** 2).sum())
         den += float((w * w).sum())
     return (num / max(den, 1e-300)) ** 0.5
+
+
+def rel_err_rows_dev(got, want) -> float:
+    """rel_err with the rms of each ROW of `want` as the floor of the denominator: a table gradient is
+    mostly zero rows beside a few rows that sum thousands of terms, so the rms of the whole tensor says
+    nothing about the scale of either kind.  A zero row must be matched exactly."""
+    worst = 0.0
+    for r0 in range(0, want.shape[0], 4096):
+        g, w = got[r0:r0 + 4096].double(), want[r0:r0 + 4096].double()
+        rms = (w * w).mean(dim=1, keepdim=True).sqrt()
+        denom = torch.maximum(torch.maximum(g.abs(), w.abs()), rms).clamp_min(1e-300)
+        worst = max(worst, float(((g - w).abs() / denom).max()))
+    return worst
 
 
 def randn(gen, *shape, scale=1.0):
@@ -119,9 +132,10 @@ def test_cfg3_embedding_v32000_d4096_zipf_vs_reference_kernels():
     # hottest row (thousands of N(0,1) terms, partial sums of magnitude ~50) that running sum is itself
     # ~sqrt(c) * 2^-24 * 50 from the exact value and differs from run to run, so "within 1e-5 of the
     # reference" is only meaningful where the reference is exact: rows with one token (same bits) and rows
-    # with a few tokens (<= 1e-5).  Everywhere the yardstick is the sum in fp64: this library must be within
-    # max(1e-5, 4 * sqrt(c_max) * 2^-24) of it (the bound used for the column sums) and no further from it
-    # than the reference is.
+    # with a few tokens (<= 1e-5).  Everywhere the yardstick is the sum in fp64: against it this library
+    # must be within 1e-5 of every element relative to the scale of the element's own row, and, in the
+    # measure that uses the rms of the whole table (which is mostly zero rows, so it overstates the error
+    # of the hot rows), no further away than the reference itself is.
     counts = torch.bincount(ids.long(), minlength=V)
     one = counts == 1
     assert same_bits(grad[one], grad_r[one]), "rows with one token carry the token's gradient bits"
@@ -130,7 +144,7 @@ def test_cfg3_embedding_v32000_d4096_zipf_vs_reference_kernels():
     assert float(grad[counts == 0].abs().max()) == 0.0
     exact = torch.zeros(V, D, dtype=torch.float64, device="cuda").index_add_(0, ids.long(), dy.double())
     err, err_r = rel_err_dev(grad, exact), rel_err_dev(grad_r, exact)
-    assert err <= max(FP32_TOL, 4.0 * float(counts.max()) ** 0.5 * 2.0 ** -24), (err, err_r)
+    assert rel_err_rows_dev(grad, exact) <= FP32_TOL
     assert err <= max(err_r, FP32_TOL), (err, err_r)
     del grad_r, exact
     # twice, from a fresh plan: the same bits
@@ -198,7 +212,7 @@ def test_activation_beyond_2_31_elements_bf16(kind):
             tc = y[sl].float()  # backward works from the cached (bf16) output
             want_dx = dy[sl].float() * (1.0 - tc * tc)
             assert rel_err_dev(dx[sl].float(), want_dx) <= BF16_TOL
-        db64 += dx[sl].double().sum(0)
+        db64 += want_dx.double().sum(0)  # the bias gradient sums dx before it is rounded to bf16
     assert rel_err_dev(dbias, db64) <= FP32_TOL
 
 
@@ -260,7 +274,7 @@ def test_cfg5_bf16_chain_vs_fp32_reference_chain():
     assert rel_err_dev(chain.table_grad[few], grad_r[few]) <= FP32_TOL
     exact = torch.zeros(V, D, dtype=torch.float64, device="cuda").index_add_(0, chain.ids.long(), chain.dx1.double())
     err, err_r = rel_err_dev(chain.table_grad, exact), rel_err_dev(grad_r, exact)
-    assert err <= max(FP32_TOL, 4.0 * float(counts.max()) ** 0.5 * 2.0 ** -24), (err, err_r)
+    assert rel_err_rows_dev(chain.table_grad, exact) <= FP32_TOL
     assert err <= max(err_r, FP32_TOL), (err, err_r)
     del grad_r, exact
     assert capi.pipeline_timeouts() == 0

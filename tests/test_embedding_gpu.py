@@ -195,12 +195,19 @@ def test_plan_and_scatter_back_to_back_without_host_syncs():
         assert bits_equal(got, want), f"batch {rep}"
 
 
+def shard(n, ranks, r):
+    """Token range of rank r when n tokens are dealt ceil(n / ranks) per rank (the last may get fewer)."""
+    per = (n + ranks - 1) // ranks
+    return per, min(n, r * per), min(n, (r + 1) * per)
+
+
 @pytest.mark.parametrize("vocab,d,n,ranks,storage", [(2000, 256, 4096, 2, "fp32"), (32000, 512, 8192, 4, "bf16"),
-                                                     (50, 64, 3000, 3, "fp32"), (300, 4096, 640, 8, "bf16")])
+                                                     (50, 64, 3000, 3, "fp32"), (300, 4096, 640, 8, "bf16"),
+                                                     (97, 128, 4001, 5, "fp32")])
 def test_compacted_multi_rank_gradient(vocab, d, n, ranks, storage):
-    """The multi-GPU form of the table gradient with the ranks emulated on one GPU: each rank
-    scatter-adds its token shard into the compact [used, d] buffer, the buffers are summed
-    (the all-reduce), and the expansion must equal the single-rank dense gradient."""
+    """The multi-GPU form of the table gradient with the ranks emulated on one GPU: from ONE sort of all
+    ranks' ids each rank finds its own tokens, scatter-adds them into the compact [used, d] buffer, the
+    buffers are summed (the all-reduce), and the expansion must equal the single-rank dense gradient."""
     dt = torch.bfloat16 if storage == "bf16" else torch.float32
     ids = zipf_ids(rng_for(61, 0), n, vocab)
     dy = dev(rng_for(61, 1).standard_normal((n, d)).astype(np.float32), dt)
@@ -209,28 +216,79 @@ def test_compacted_multi_rank_gradient(vocab, d, n, ranks, storage):
     global_plan = ops.embed_sort_tokens(tids, vocab, d)
     used_host = int(np.unique(ids).size)
     total = None
-    per = n // ranks
-    compact_ws = None
+    rank_plan = None
     for r in range(ranks):
-        lo, hi = r * per, (n if r == ranks - 1 else (r + 1) * per)
-        ids_r, dy_r = tids[lo:hi].contiguous(), dy[lo:hi].contiguous()
-        local_plan = ops.embed_sort_tokens(ids_r, vocab, d)
-        compact_ws = ops.embed_compact_plan(global_plan, n, local_plan, hi - lo, vocab, d)
-        used = int(compact_ws[:4].view(torch.int32)[0].item())
+        per, lo, hi = shard(n, ranks, r)
+        dy_r = dy[lo:hi].contiguous() if hi > lo else dy[:1].contiguous()
+        rank_plan = ops.embed_rank_plan(global_plan, n, per, ranks, r, vocab, d)
+        used = int(rank_plan[:4].view(torch.int32)[0].item())
         assert used == used_host
-        rows = torch.full((used, d), 9.0, device="cuda")  # stale contents must vanish
-        ops.embed_scatter_bwd_compact(dy_r, local_plan, compact_ws, rows, used, vocab)
-        total = rows if total is None else total + rows
+        rows = torch.full((min(vocab, n), d), 9.0, device="cuda")  # stale contents must vanish
+        ops.embed_scatter_bwd_compact(dy_r, global_plan, n, rank_plan, per, r, rows, vocab)
+        assert float(rows[used:].min()) == 9.0 if used < rows.shape[0] else True  # nothing beyond the used rows
+        total = rows[:used].clone() if total is None else total + rows[:used]
     grad = torch.full((vocab, d), 5.0, device="cuda")
-    ops.embed_expand_rows(total, compact_ws, grad, what=1)   # zero the unused rows (can overlap the all-reduce)
-    ops.embed_expand_rows(total, compact_ws, grad, what=2)   # then copy the reduced rows
+    ops.embed_expand_rows(total, rank_plan, per, grad, what=1)   # zero the unused rows (can overlap the all-reduce)
+    ops.embed_expand_rows(total, rank_plan, per, grad, what=2)   # then copy the reduced rows
     assert rel_err(grad.cpu().numpy(), dense.cpu().numpy()) <= 1e-5
     unused = np.setdiff1d(np.arange(vocab), ids)
     if unused.size:
         assert float(grad[torch.from_numpy(unused).cuda()].abs().sum()) == 0.0
     both = torch.full((vocab, d), 5.0, device="cuda")
-    ops.embed_expand_rows(total, compact_ws, both, what=3)
+    ops.embed_expand_rows(total, rank_plan, per, both, what=3)
     assert torch.equal(both, grad)
+
+
+def test_rank_plan_against_numpy():
+    """Slots, local ranges and source masks of the rank plan, restated with numpy."""
+    vocab, d, n, ranks = 500, 64, 6000, 4
+    ids = zipf_ids(rng_for(63, 0), n, vocab)
+    ids[17] = vocab + 3  # an id outside the table belongs to no row
+    tids = dev(ids)
+    global_plan = ops.embed_sort_tokens(tids, vocab, d)
+    order = np.argsort(ids, kind="stable")
+    inside = ids[order] < vocab
+    used_rows = np.unique(ids[ids < vocab])
+    for r in range(ranks):
+        per, lo, hi = shard(n, ranks, r)
+        plan = ops.embed_rank_plan(global_plan, n, per, ranks, r, vocab, d)
+        ints = plan.view(torch.int32).cpu().numpy()
+        used = int(ints[0])
+        assert used == used_rows.size
+        stride = ((vocab * 4 + 255) // 256) * 64  # int32 words per [V] array (256-byte aligned)
+        base = 64                                 # the header takes 256 bytes
+        slot_map, used_list = ints[base:base + vocab], ints[base + stride:base + stride + used]
+        row_begin = ints[base + 2 * stride:base + 2 * stride + used]
+        row_end = ints[base + 3 * stride:base + 3 * stride + used]
+        src_mask = ints[base + 4 * stride:base + 4 * stride + used]
+        assert np.array_equal(used_list, used_rows)
+        assert np.array_equal(slot_map[used_rows], np.arange(used)) and np.all(np.delete(slot_map, used_rows) == -1)
+        for slot in range(0, used, 7):
+            v = used_rows[slot]
+            toks = order[inside & (ids[order] == v)]
+            assert src_mask[slot] == sum(1 << int(q) for q in np.unique(toks // per))
+            mine = toks[(toks >= lo) & (toks < hi)]
+            assert row_end[slot] - row_begin[slot] == mine.size
+            if mine.size:
+                pos = np.flatnonzero(order == mine[0])[0]
+                assert row_begin[slot] == pos
+                assert np.array_equal(order[row_begin[slot]:row_end[slot]], mine)
+
+
+class EmulatedRanks:
+    """Every rank's peer buffers on this one GPU (the "mappings" are the plain addresses)."""
+
+    def __init__(self, ranks, vocab, d, cap, small_n):
+        z = lambda k: torch.zeros(k, device="cuda")
+        self.recv = [torch.full((ranks * cap * d,), 3.0, device="cuda") for _ in range(ranks)]  # needs no zeroing
+        self.tables = [torch.full((vocab, d), 5.0, device="cuda") for _ in range(ranks)]
+        self.flags = [torch.zeros(capi.lib().dlb_peer_flags_bytes() // 4, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+        self.small = [z(max(ranks * small_n, 4)) for _ in range(ranks)]
+        self.status = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+        addr = lambda ts: [t.data_ptr() for t in ts]
+        self.groups = [ops.peer_group(ranks, r, cap, addr(self.flags), addr(self.recv), addr(self.tables), self.status[r],
+                                      addr(self.small) if small_n else None, small_n, timeout_ms=1000)
+                       for r in range(ranks)]
 
 
 @pytest.mark.parametrize("storage", ["fp32", "bf16"])
@@ -238,10 +296,11 @@ def test_compacted_multi_rank_gradient(vocab, d, n, ranks, storage):
                                              (97, 128, 4000, 3), (50, 64, 300, 1), (300, 4096, 2000, 16)])
 def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, storage):
     """The peer-memory form of the table-gradient exchange, every rank's buffers on this one GPU and the
-    ranks run one after the other (no barrier is needed then): each rank pushes the rows it has tokens for
-    into the owners' receive areas, each owner adds what arrived in rank order and stores the sum into every
-    rank's dense table.  Every table must equal the single-rank dense gradient, twice in a row (the receive
-    areas must come back zeroed)."""
+    phases run rank after rank (all pushes, then all owner sums: every flag is set before it is waited
+    for, so no kernel waits for a later launch).  A row one rank alone has tokens for is stored into every
+    table by that rank; a shared row goes to its owner, which adds the partial rows in rank order and
+    stores the sum into every table; the small gradients of all ranks are summed in rank order.  Every
+    table must equal the single-rank dense gradient, twice in a row with stale receive areas."""
     dt = torch.bfloat16 if storage == "bf16" else torch.float32
     ids = zipf_ids(rng_for(71, 0), n, vocab)
     dy = dev(rng_for(71, 1).standard_normal((n, d)).astype(np.float32), dt)
@@ -254,38 +313,82 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
     np.add.at(exact, ids, dy.float().cpu().numpy().astype(np.float64))
     assert rel_err(dense, exact) <= 3e-5
     global_plan = ops.embed_sort_tokens(tids, vocab, d)
-    used_host = int(np.unique(ids).size)
-    cap = (min(vocab, n) + ranks - 1) // ranks
-    recv = [torch.zeros(ranks * cap * d, device="cuda") for _ in range(ranks)]
-    tables = [torch.full((vocab, d), 5.0, device="cuda") for _ in range(ranks)]
-    per = n // ranks
+    max_rows = min(vocab, n)
+    cap = (max_rows + ranks - 1) // ranks
+    small_n = 24
+    em = EmulatedRanks(ranks, vocab, d, cap, small_n)
+    small_in = [dev(rng_for(73, r).standard_normal(small_n).astype(np.float32)) for r in range(ranks)]
+    small_want = small_in[0].clone()
+    for r in range(1, ranks):
+        small_want = small_want + small_in[r]
     for attempt in range(2):
-        plans = []
+        epoch = attempt + 1
+        plans, small_out = [], [torch.full((small_n,), 9.0, device="cuda") for _ in range(ranks)]
         for r in range(ranks):
-            lo, hi = r * per, (n if r == ranks - 1 else (r + 1) * per)
-            ids_r, dy_r = tids[lo:hi].contiguous(), dy[lo:hi].contiguous()
-            local_plan = ops.embed_sort_tokens(ids_r, vocab, d)
-            compact_ws = ops.embed_compact_plan(global_plan, n, local_plan, hi - lo, vocab, d)
-            used = int(compact_ws[:4].view(torch.int32)[0].item())
-            assert used == used_host
-            # second round: the launch is sized from an upper bound of the used rows, as a host that does not
-            # wait for the plan would do
-            rows_arg = used if attempt == 0 else min(vocab, n)
-            ops.embed_scatter_bwd_peer(dy_r, local_plan, compact_ws, [t.data_ptr() for t in recv], r, cap, rows_arg, vocab)
-            plans.append(compact_ws)
+            per, lo, hi = shard(n, ranks, r)
+            plans.append(ops.embed_rank_plan(global_plan, n, per, ranks, r, vocab, d))
+            ops.embed_expand_rows(None, plans[r], per, em.tables[r], what=1)
         for r in range(ranks):
-            ops.embed_expand_rows(None, plans[r], tables[r], what=1)
-            ops.embed_reduce_broadcast_peer(recv[r], plans[r], [t.data_ptr() for t in tables], r, cap, vocab, d)
+            per, lo, hi = shard(n, ranks, r)
+            dy_r = dy[lo:hi].contiguous() if hi > lo else dy[:1].contiguous()
+            ops.embed_scatter_bwd_peer(dy_r, global_plan, n, plans[r], per, em.groups[r], small_in[r], max_rows, vocab,
+                                       0, epoch)
+        for r in range(ranks):
+            ops.embed_reduce_broadcast_peer(plans[r], per, em.groups[r], small_out[r], vocab, d, 0, epoch, 1, epoch)
+        for r in range(ranks):
+            ops.peer_wait([f.data_ptr() for f in em.flags], r, 1, epoch, em.status[r], timeout_ms=1000)
         torch.cuda.synchronize()
         for r in range(ranks):
-            got = tables[r].cpu().numpy()
+            assert int(em.status[r].item()) == 0, (attempt, r)
+            got = em.tables[r].cpu().numpy()
             assert rel_err(got, exact) <= 3e-5, (attempt, r)
             assert rel_err(got, dense) <= 3e-5, (attempt, r)  # two fp32 groupings of the same terms
-            assert float(recv[r].abs().sum()) == 0.0, "receive area must be zero again"
+            assert torch.equal(small_out[r], small_want), (attempt, r)
             if r:
-                assert torch.equal(tables[r], tables[0])  # every rank holds the same bits
-        for t in tables:
+                assert torch.equal(em.tables[r], em.tables[0])  # every rank holds the same bits
+        for t in em.tables:
             t.fill_(7.0)
+
+
+def test_peer_reduce_reports_a_receive_area_that_is_too_small():
+    """cap_rows smaller than the rows an owner holds: the kernel drops those rows, raises bit 31 of the
+    status word and touches nothing outside the receive area."""
+    vocab, d, n, ranks = 400, 64, 3000, 2
+    ids = rng_for(75, 0).integers(0, vocab, n).astype(np.int32)  # every row used by both ranks
+    tids = dev(ids)
+    global_plan = ops.embed_sort_tokens(tids, vocab, d)
+    cap = 20  # 2 * 20 = 40 slots, far fewer than the ~400 used rows
+    em = EmulatedRanks(ranks, vocab, d, cap, 0)
+    per, lo, hi = shard(n, ranks, 0)
+    plan = ops.embed_rank_plan(global_plan, n, per, ranks, 0, vocab, d)
+    guard = em.recv[0].clone()
+    ops.embed_reduce_broadcast_peer(plan, per, em.groups[0], None, vocab, d, 3, 0, 1, 1)  # epoch 0: nothing to wait for
+    torch.cuda.synchronize()
+    assert (int(em.status[0].item()) & 0xffffffff) == 1 << 31
+    assert torch.equal(em.recv[0], guard)
+
+
+def test_peer_put_gathers_and_waits():
+    """dlb_peer_put with the ranks emulated: all pushes first (no wait), then the waits pass at once."""
+    ranks, k = 4, 1024
+    flags = [torch.zeros(capi.lib().dlb_peer_flags_bytes() // 4, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+    gathered = [torch.zeros(ranks * k, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    mine = [torch.arange(k, dtype=torch.int32, device="cuda") + 1000 * r for r in range(ranks)]
+    fl, dst = [f.data_ptr() for f in flags], [g.data_ptr() for g in gathered]
+    for r in range(ranks):
+        ops.peer_put(mine[r], dst, fl, r, 2, 1, status, wait=False, timeout_ms=1000)
+    for r in range(ranks):
+        ops.peer_wait(fl, r, 2, 1, status, timeout_ms=1000)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for r in range(ranks):
+        assert torch.equal(gathered[r], torch.cat(mine))
+    # alone in its group a rank gathers from itself and passes its own wait
+    solo = torch.zeros(k, dtype=torch.int32, device="cuda")
+    ops.peer_put(mine[1], [solo.data_ptr()], [flags[0].data_ptr()], 0, 3, 1, status, wait=True, timeout_ms=1000)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and torch.equal(solo, mine[1])
 
 
 def test_peer_barrier_single_rank_and_timeout():
@@ -309,33 +412,51 @@ def test_peer_barrier_single_rank_and_timeout():
 
 
 def test_peer_entry_points_reject_bad_arguments():
+    import ctypes
     lib = capi.lib()
     vocab, d, n = 50, 64, 100
     ids = dev(zipf_ids(rng_for(72, 0), n, vocab))
     dy = dev(rng_for(72, 1).standard_normal((n, d)).astype(np.float32))
     plan = ops.embed_sort_tokens(ids, vocab, d)
-    compact = ops.embed_compact_plan(plan, n, plan, n, vocab, d)
-    recv = torch.zeros(2 * 25 * d, device="cuda")
-    table = torch.zeros(vocab, d, device="cuda")
-    good = ops._addr_array([recv.data_ptr(), recv.data_ptr()])
-    args = lambda ranks, me, cap, used, arr=good: (dy.data_ptr(), plan.data_ptr(), plan.numel(), compact.data_ptr(), arr,
-                                                   ranks, me, cap, used, n, vocab, d, capi.F32, None)
-    assert lib.dlb_embed_scatter_bwd_peer(*args(0, 0, 25, 50)) == capi.ERR_INVALID_ARG      # no ranks
-    assert lib.dlb_embed_scatter_bwd_peer(*args(17, 0, 25, 50)) == capi.ERR_INVALID_ARG     # more than 16 ranks
-    assert lib.dlb_embed_scatter_bwd_peer(*args(2, 2, 25, 50)) == capi.ERR_INVALID_ARG      # rank out of range
-    assert lib.dlb_embed_scatter_bwd_peer(*args(2, 0, 10, 50)) == capi.ERR_INVALID_ARG      # receive areas too small
-    assert lib.dlb_embed_scatter_bwd_peer(*args(2, 0, 25, 50, ops._addr_array([recv.data_ptr(), None]))) \
-        == capi.ERR_INVALID_ARG                                                             # a null receive area
-    tables = ops._addr_array([table.data_ptr(), table.data_ptr()])
-    assert lib.dlb_embed_reduce_broadcast_peer(recv.data_ptr(), compact.data_ptr(), tables, 2, 5, 25, vocab, d, None) \
-        == capi.ERR_INVALID_ARG
-    assert lib.dlb_embed_reduce_broadcast_peer(None, compact.data_ptr(), tables, 2, 0, 25, vocab, d, None) \
-        == capi.ERR_INVALID_ARG
+    rank_plan = ops.embed_rank_plan(plan, n, 50, 2, 0, vocab, d)
+    em = EmulatedRanks(2, vocab, d, 25, 0)
+    recv_before = em.recv[0].clone()
+
+    def scatter_status(group, max_rows=50, channel=0):
+        return lib.dlb_embed_scatter_bwd_peer(dy.data_ptr(), plan.data_ptr(), n, rank_plan.data_ptr(), 50,
+                                              ctypes.byref(group), None, max_rows, vocab, d, capi.F32, channel, 1, None)
+
+    def group(**changes):
+        g = ops.peer_group(2, 0, 25, [f.data_ptr() for f in em.flags], [t.data_ptr() for t in em.recv],
+                           [t.data_ptr() for t in em.tables], em.status[0], None, 0, 1000)
+        for k, v in changes.items():
+            setattr(g, k, v)
+        return g
+
+    assert scatter_status(group(n_ranks=0)) == capi.ERR_INVALID_ARG       # no ranks
+    assert scatter_status(group(n_ranks=17)) == capi.ERR_INVALID_ARG      # more than 16 ranks
+    assert scatter_status(group(my_rank=2)) == capi.ERR_INVALID_ARG       # rank out of range
+    assert scatter_status(group(cap_rows=10)) == capi.ERR_INVALID_ARG     # receive areas too small for max_rows
+    assert scatter_status(group(timeout_ms=0)) == capi.ERR_INVALID_ARG
+    assert scatter_status(group(small_n=6)) == capi.ERR_INVALID_ARG       # not a multiple of 4
+    assert scatter_status(group(), channel=4) == capi.ERR_INVALID_ARG
+    broken = group()
+    broken.recv[1] = None
+    assert scatter_status(broken) == capi.ERR_INVALID_ARG                 # a null receive area
+    assert lib.dlb_embed_reduce_broadcast_peer(rank_plan.data_ptr(), 50, ctypes.byref(group(my_rank=5)), None, vocab, d,
+                                               0, 1, 1, 1, None) == capi.ERR_INVALID_ARG
+    assert lib.dlb_embed_reduce_broadcast_peer(None, 50, ctypes.byref(group()), None, vocab, d, 0, 1, 1, 1, None) \
+        == capi.ERR_WORKSPACE
+    assert lib.dlb_embed_rank_plan(plan.data_ptr(), n, 10, 2, 0, rank_plan.data_ptr(), rank_plan.numel(), vocab, d, None) \
+        == capi.ERR_INVALID_ARG                                           # 2 ranks of 10 tokens do not cover 100
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     flags = torch.zeros(64, dtype=torch.int32, device="cuda")
     one = ops._addr_array([flags.data_ptr()])
     assert lib.dlb_peer_barrier(one, 1, 0, 4, 1, 100, status.data_ptr(), None) == capi.ERR_INVALID_ARG    # channel
     assert lib.dlb_peer_barrier(one, 1, 0, 0, 1, 0, status.data_ptr(), None) == capi.ERR_INVALID_ARG      # timeout
     assert lib.dlb_peer_barrier(one, 1, 0, 0, 1, 100, None, None) == capi.ERR_INVALID_ARG                 # status
+    assert lib.dlb_peer_put(flags.data_ptr(), 24, one, one, 1, 0, 0, 1, 0, 100, status.data_ptr(), None) \
+        == capi.ERR_INVALID_ARG                                                                          # 24 bytes
     torch.cuda.synchronize()
-    assert int(status.item()) == 0 and float(recv.abs().sum()) == 0.0 and float(table.abs().sum()) == 0.0
+    assert int(status.item()) == 0 and torch.equal(em.recv[0], recv_before)
+    assert all(float((t - 5.0).abs().sum()) == 0.0 for t in em.tables)
