@@ -354,20 +354,15 @@ class Chain:
             mark()
         elif self.peer is not None:
             px, ops = self.peer, self.ops
-            # rows no rank uses are zeroed locally, beside the exchange (which is bound by NVLink, not HBM)
-            self.bwd_done.record(main)
-            self.side.wait_event(self.bwd_done)
-            chk(lib.dlb_embed_expand_rows(None, p(self.rank_plan), T, p(self.table_grad), V, D, 1, self.side.cuda_stream))
-            self.zero_done.record(self.side)
-            # No host wait and no library call between the kernels: the launch is sized from an upper bound, the
-            # kernels read the exact row count, announce their stores and wait for the other ranks themselves.
+            # No host wait, no second stream and no library call between the kernels: the launches are sized
+            # from upper bounds, the kernels read the exact row counts, zero the rows nobody uses, announce their
+            # stores and wait for the other ranks themselves.
             pushed, done = px.next_epoch(px.CH_PUSHED), px.next_epoch(px.CH_DONE)
             ops.embed_scatter_bwd_peer(self.dx1, self.ws_global, self.Tg, self.rank_plan, T, px.group, self.small_grads,
                                        min(V, self.Tg), V, px.CH_PUSHED, pushed, stream=st)
             mark()
             ops.embed_reduce_broadcast_peer(self.rank_plan, T, px.group, self.small_grads, V, D, px.CH_PUSHED, pushed,
                                             px.CH_DONE, done, stream=st)
-            main.wait_event(self.zero_done)
             px.wait(px.CH_DONE, stream=st)  # every rank's table holds every row
         else:
             # Compacted form through NCCL: only the rows some rank uses are summed, all-reduced and expanded.

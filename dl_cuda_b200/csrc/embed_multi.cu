@@ -13,9 +13,14 @@
 //   * compact + all-reduce: dlb_embed_scatter_bwd_compact sums the local tokens into a dense
 //     [used, d] buffer (zeros where this rank has no token), the caller all-reduces it, and
 //     dlb_embed_expand_rows writes the dense [vocab, d] gradient;
-//   * peer memory (the fused path): dlb_embed_scatter_bwd_peer stores a row that only this
-//     rank has tokens for straight into row v of EVERY rank's dense table, and a row that
-//     several ranks share into the receive area of the slot's owner (slot % n);
+//   * peer memory (the fused path): dlb_embed_scatter_bwd_peer sums this rank's tokens per
+//     row into a local buffer (only rows it has tokens for: HBM-bound, the same kernel as the
+//     single-GPU scatter) and then streams those rows out in a copy-shaped kernel that keeps
+//     NVLink full: a row that only this rank has tokens for goes straight into row v of EVERY
+//     rank's dense table, a row that several ranks share into the receive area of the slot's
+//     owner (slot % n).  (Storing to the peers from inside the summing kernel was measured at
+//     300 GB/s: its load -> store dependency chains leave the links idle most of the time;
+//     the copy-shaped kernel reaches the 700 GB/s a plain peer copy gets.)
 //     dlb_embed_reduce_broadcast_peer, on the owner, waits for the ranks' arrival flags, adds
 //     the partial rows in rank order and stores the sum into every rank's table.  The kernels
 //     signal and wait through flag words in peer memory themselves; rows no rank uses are
@@ -29,20 +34,33 @@ namespace {
 
 constexpr int kBlock = kEmbBlock;
 
+// header words of a rank plan
+enum { kHdrUsed = 0, kHdrLong = 1, kHdrSub = 2, kHdrMine = 3, kHdrDonePush = 4, kHdrDoneReduce = 5, kHdrMulti = 6 };
+
 struct RankPlan {
-  int32_t *header;     // [16]  {used rows, long rows, sub-segments, -, done counters x4, ...}
-  int32_t *slot_map;   // [V]   slot of a table row, -1 if no rank refers to it
-  int32_t *used_rows;  // [V]   table row of a slot
-  int32_t *row_begin;  // [V]   this rank's range of the global sorted list, per slot
-  int32_t *row_end;    // [V]
-  uint32_t *src_mask;  // [V]   ranks that have tokens for the slot
-  uint32_t *tmp_mask;  // [V]   the same three per TABLE ROW, before the slots are numbered
-  int32_t *tmp_begin;  // [V]
-  int32_t *tmp_end;    // [V]
-  int32_t *long_row;   // [max_long]    slots with more than kSubLen local tokens
-  int32_t *long_first; // [max_long+1]  running count of their sub-segments
-  float *scratch;      // [max_sub][d]
-  int max_long, max_sub;
+  int32_t *header;       // [16]  see kHdr*
+  int32_t *slot_map;     // [V]   slot of a table row, -1 if no rank refers to it
+  int32_t *used_rows;    // [V]   table row of a slot
+  int32_t *row_begin;    // [V]   this rank's range of the global sorted list, per slot
+  int32_t *row_end;      // [V]
+  uint32_t *src_mask;    // [V]   ranks that have tokens for the slot
+  uint32_t *tmp_mask;    // [V]   the same three per TABLE ROW, before the slots are numbered
+  int32_t *tmp_begin;    // [V]
+  int32_t *tmp_end;      // [V]
+  // "my rows": the slots this rank has tokens for, k = 0..mine-1 in ascending id
+  int32_t *my_route;     // [max_mine]  where row k goes: v | 0x80000000 if this rank is its only source
+                         //             (straight into row v of every table), else its slot (to the owner)
+  int32_t *my_src;       // [max_mine]  where row k comes from: the local token index if it has one token,
+                         //             else -(m + 1): row m of my_rows
+  // "multi rows": my rows with two or more local tokens, m = 0..multi-1 in ascending id
+  int32_t *multi_begin;  // [max_multi] range of the global sorted list
+  int32_t *multi_end;    // [max_multi]
+  int32_t *multi_slot;   // [max_multi] slot of multi row m
+  int32_t *long_row;     // [max_long]    multi rows with more than kSubLen tokens
+  int32_t *long_first;   // [max_long+1]  running count of their sub-segments
+  float *scratch;        // [max_sub][d]
+  float *my_rows;        // [max_multi][d] sums of the multi rows (peer exchange only)
+  int max_long, max_sub, max_mine, max_multi;
   size_t bytes;
 };
 
@@ -50,6 +68,9 @@ RankPlan make_rank_plan(void *workspace, int vocab, int tokens_per_rank, int d) 
   RankPlan r{};
   r.max_long = tokens_per_rank / kSubLen + 1;
   r.max_sub = 2 * (tokens_per_rank / kSubLen) + 2;
+  r.max_mine = vocab < tokens_per_rank ? vocab : tokens_per_rank;
+  r.max_multi = vocab < tokens_per_rank / 2 ? vocab : tokens_per_rank / 2;
+  if (r.max_multi < 1) r.max_multi = 1;
   char *base = static_cast<char *>(workspace);
   size_t off = 0;
   auto take = [&](size_t bytes) {
@@ -57,19 +78,26 @@ RankPlan make_rank_plan(void *workspace, int vocab, int tokens_per_rank, int d) 
     off += align_up256(bytes);
     return ptr;
   };
-  const size_t per = sizeof(int32_t) * static_cast<size_t>(vocab);
-  r.header = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * 16));
-  r.slot_map = reinterpret_cast<int32_t *>(take(per));
-  r.used_rows = reinterpret_cast<int32_t *>(take(per));
-  r.row_begin = reinterpret_cast<int32_t *>(take(per));
-  r.row_end = reinterpret_cast<int32_t *>(take(per));
-  r.src_mask = reinterpret_cast<uint32_t *>(take(per));
-  r.tmp_mask = reinterpret_cast<uint32_t *>(take(per));
-  r.tmp_begin = reinterpret_cast<int32_t *>(take(per));
-  r.tmp_end = reinterpret_cast<int32_t *>(take(per));
-  r.long_row = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * r.max_long));
-  r.long_first = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * (r.max_long + 1)));
+  auto ints = [&](size_t n) { return reinterpret_cast<int32_t *>(take(sizeof(int32_t) * n)); };
+  const size_t v = static_cast<size_t>(vocab);
+  r.header = ints(16);
+  r.slot_map = ints(v);
+  r.used_rows = ints(v);
+  r.row_begin = ints(v);
+  r.row_end = ints(v);
+  r.src_mask = reinterpret_cast<uint32_t *>(ints(v));
+  r.tmp_mask = reinterpret_cast<uint32_t *>(ints(v));
+  r.tmp_begin = ints(v);
+  r.tmp_end = ints(v);
+  r.my_route = ints(r.max_mine);
+  r.my_src = ints(r.max_mine);
+  r.multi_begin = ints(r.max_multi);
+  r.multi_end = ints(r.max_multi);
+  r.multi_slot = ints(r.max_multi);
+  r.long_row = ints(r.max_long);
+  r.long_first = ints(r.max_long + 1);
   r.scratch = reinterpret_cast<float *>(take(sizeof(float) * static_cast<size_t>(r.max_sub) * d));
+  r.my_rows = reinterpret_cast<float *>(take(sizeof(float) * static_cast<size_t>(r.max_multi) * d));
   r.bytes = off;
   return r;
 }
@@ -135,14 +163,15 @@ __device__ __forceinline__ unsigned long long cta_scan_u64(unsigned long long v,
   return tmp[warp] + incl - v;
 }
 
-// Phase 3, one CTA: walks the table rows in order, 1024 at a time, and numbers the used rows and
-// this rank's long rows.  Three counts ride in one 64-bit scan: used rows (bits 0..19), long rows
-// (20..39), sub-segments (40..63).
+// Phase 3, one CTA: walks the table rows in order, 1024 at a time, and numbers the used rows
+// (slots), this rank's rows, its rows with several tokens and its long rows.  The counts ride in
+// two 64-bit scans: {used rows (bits 0..19), long rows (20..39), sub-segments (40..63)} and
+// {my rows (0..19), multi rows (20..39)}.
 __global__ void __launch_bounds__(1024)
-rank_plan_number_kernel(const int32_t *seg_global, int vocab, RankPlan r) {
+rank_plan_number_kernel(const int32_t *seg_global, const int32_t *vals, int tok_offset, int me, int vocab, RankPlan r) {
   pdl_prologue();
   __shared__ unsigned long long tmp[33];
-  unsigned long long base = 0;
+  unsigned long long base_a = 0, base_b = 0;
   for (int v0 = 0; v0 < vocab; v0 += 1024) {
     const int v = v0 + threadIdx.x;
     const bool used = v < vocab && ld_co(seg_global + v + 1) > ld_co(seg_global + v);
@@ -154,32 +183,49 @@ rank_plan_number_kernel(const int32_t *seg_global, int vocab, RankPlan r) {
     const int cnt = e - b;
     const bool is_long = cnt > kSubLen;
     const unsigned long long nsub = is_long ? static_cast<unsigned long long>((cnt + kSubLen - 1) / kSubLen) : 0ull;
-    const unsigned long long mine = (used ? 1ull : 0ull) | (is_long ? (1ull << 20) : 0ull) | (nsub << 40);
-    unsigned long long total;
-    const unsigned long long at = base + cta_scan_u64(mine, tmp, &total);
+    const unsigned long long in_a = (used ? 1ull : 0ull) | (is_long ? (1ull << 20) : 0ull) | (nsub << 40);
+    const unsigned long long in_b = (cnt > 0 ? 1ull : 0ull) | (cnt > 1 ? (1ull << 20) : 0ull);
+    unsigned long long total_a, total_b;
+    const unsigned long long at_a = base_a + cta_scan_u64(in_a, tmp, &total_a);
+    const unsigned long long at_b = base_b + cta_scan_u64(in_b, tmp, &total_b);
     if (v < vocab) {
-      const int slot = static_cast<int>(at & 0xfffffull);
+      const int slot = static_cast<int>(at_a & 0xfffffull);
       r.slot_map[v] = used ? slot : -1;
       if (used) {
+        const uint32_t mask = ld_co(r.tmp_mask + v);
         r.used_rows[slot] = v;
         r.row_begin[slot] = b;
         r.row_end[slot] = e;
-        r.src_mask[slot] = ld_co(r.tmp_mask + v);
-        if (is_long) {
-          const int li = static_cast<int>((at >> 20) & 0xfffffull);
-          r.long_row[li] = slot;
-          r.long_first[li] = static_cast<int>(at >> 40);
+        r.src_mask[slot] = mask;
+        if (cnt > 0) {
+          const int k = static_cast<int>(at_b & 0xfffffull);
+          const int m = static_cast<int>((at_b >> 20) & 0xfffffull);
+          r.my_route[k] = mask == (1u << me) ? static_cast<int32_t>(static_cast<uint32_t>(v) | 0x80000000u) : slot;
+          r.my_src[k] = cnt == 1 ? ld_co(vals + b) - tok_offset : -(m + 1);
+          if (cnt > 1) {
+            r.multi_begin[m] = b;
+            r.multi_end[m] = e;
+            r.multi_slot[m] = slot;
+          }
+          if (is_long) {
+            const int li = static_cast<int>((at_a >> 20) & 0xfffffull);
+            r.long_row[li] = m;
+            r.long_first[li] = static_cast<int>(at_a >> 40);
+          }
         }
       }
     }
-    base += total;
+    base_a += total_a;
+    base_b += total_b;
   }
   if (threadIdx.x == 0) {
-    const int n_long = static_cast<int>((base >> 20) & 0xfffffull);
-    r.header[0] = static_cast<int>(base & 0xfffffull);
-    r.header[1] = n_long;
-    r.header[2] = static_cast<int>(base >> 40);
-    r.long_first[n_long] = static_cast<int>(base >> 40);
+    const int n_long = static_cast<int>((base_a >> 20) & 0xfffffull);
+    r.header[kHdrUsed] = static_cast<int>(base_a & 0xfffffull);
+    r.header[kHdrLong] = n_long;
+    r.header[kHdrSub] = static_cast<int>(base_a >> 40);
+    r.header[kHdrMine] = static_cast<int>(base_b & 0xfffffull);
+    r.header[kHdrMulti] = static_cast<int>((base_b >> 20) & 0xfffffull);
+    r.long_first[n_long] = static_cast<int>(base_a >> 40);
   }
 }
 
@@ -212,6 +258,167 @@ expand_rows_kernel(const float *compact, const int32_t *slot_map, float *__restr
       }
     }
   }
+}
+
+// Scatter arguments from a rank plan.  by_slot: one output row per used row (zeros where this rank
+// has no token: the form an all-reduce needs); otherwise one output row per row this rank has
+// SEVERAL tokens for, in the plan's own buffer (rows with one token need no sum).
+ScatterArgs rank_scatter_args(const Plan &pg, const RankPlan &r, int tokens_per_rank, int my_rank, int max_rows, int d,
+                              bool by_slot) {
+  ScatterArgs a{};
+  a.perm = pg.vals[pg.passes & 1];
+  a.seg_b = by_slot ? r.row_begin : r.multi_begin;
+  a.seg_e = by_slot ? r.row_end : r.multi_end;
+  a.long_row = r.long_row;
+  a.long_first = r.long_first;
+  a.long_b = r.multi_begin;
+  a.long_e = r.multi_end;
+  a.long_out = by_slot ? r.multi_slot : nullptr;
+  a.meta = r.header + kHdrLong;
+  a.scratch = r.scratch;
+  a.out_rows_dev = by_slot ? r.header + kHdrUsed : r.header + kHdrMulti;
+  a.out_rows = max_rows;
+  a.tok_offset = my_rank * tokens_per_rank;
+  a.d = d;
+  return a;
+}
+
+// Streams this rank's rows to where they belong and zeroes, in this rank's own table, the rows no
+// rank refers to.  Copy-shaped on purpose: nothing a store needs waits on another store, so the
+// links (and, for the zero rows, HBM) stay full.
+//   CTAs [0, push_ctas): row k of "my rows", k = cta, cta + push_ctas, ...  The row is the token's
+//     gradient itself (one token: read from dy, widened to fp32) or its sum from the local scatter.
+//     Its only source: stored into row v of every rank's table.  Shared with other ranks: stored
+//     into the receive area of the slot's owner.  The small-gradient buffer is copied into slot
+//     `me` of every rank's area first.
+//   CTAs [push_ctas, grid): table rows v = z, z + zero_ctas, ... that have no slot get zeros.
+// When the last CTA has issued its stores the grid announces `sig`.
+struct SmallPush {
+  const float *src;
+  float *dst[kMaxPeers];  // every rank's [n ranks][small_n] area
+  int small_n;
+};
+
+struct PushArgs {
+  const float *my_rows;     // [multi rows][d]
+  const int32_t *my_route;  // see RankPlan
+  const int32_t *my_src;
+  const int32_t *n_mine;    // device word: number of my rows
+  const int32_t *slot_map;
+  int d, vocab, push_ctas;
+};
+
+template <int E>
+__device__ __forceinline__ void store_vec(float *p, const float (&f)[E]) {
+  if constexpr (E == 8) {
+    st_stream32(p, f);  // one whole 32-byte sector per lane: 16-byte stores at a 32-byte stride halve the link rate
+  } else {
+    st_stream(p, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+push_rows_kernel(const T *dy, const __grid_constant__ PushArgs a, const __grid_constant__ PeerRoute pr,
+                 const __grid_constant__ SmallPush sp, const __grid_constant__ PeerSignal sig) {
+  pdl_prologue();
+  using S = Store<T>;
+  constexpr int E = S::kPerVec;
+  const int d = a.d;
+  if (static_cast<int>(blockIdx.x) < a.push_ctas) {
+    if (sp.src != nullptr) {
+      const int n4 = sp.small_n / 4;
+      for (int i = blockIdx.x * kBlock + threadIdx.x; i < n4; i += a.push_ctas * kBlock) {
+        const float4 v = *reinterpret_cast<const float4 *>(sp.src + 4 * static_cast<size_t>(i));
+        for (int q = 0; q < pr.n; q++)
+          __stcs(reinterpret_cast<float4 *>(sp.dst[q] + static_cast<size_t>(pr.me) * sp.small_n) + i, v);
+      }
+    }
+    const int n_mine = ld_co(a.n_mine);
+    const int ncv = d / E, nv4 = d / 4;
+    for (int k = blockIdx.x; k < n_mine; k += a.push_ctas) {
+      const int src = ld_co(a.my_src + k);
+      const int32_t route = ld_co(a.my_route + k);
+      const bool everywhere = route < 0;
+      size_t off;
+      int first = 0, count = 1;  // destinations: ranks first .. first+count-1 of grad[] or one recv[]
+      float *single = nullptr;
+      if (everywhere) {
+        off = static_cast<size_t>(static_cast<uint32_t>(route) & 0x7fffffffu) * d;
+        count = pr.n;
+      } else {
+        const int j = route / pr.n;
+        if (j >= pr.cap) {
+          if (threadIdx.x == 0) atomicOr(pr.status, 1u << 31);
+          continue;
+        }
+        single = pr.recv[route % pr.n] + (static_cast<size_t>(pr.me) * pr.cap + j) * d;
+        off = 0;
+      }
+      (void)first;
+      if (src >= 0) {
+        // one token: the row is dy[src,:] widened to fp32 (0.0f + x carries x's bits)
+        const T *row = dy + static_cast<size_t>(src) * d;
+        for (int cv0 = threadIdx.x; cv0 < ncv; cv0 += 2 * kBlock) {
+          uint4 raw[2];
+#pragma unroll
+          for (int u = 0; u < 2; u++)
+            if (cv0 + u * kBlock < ncv) raw[u] = ld_stream(row + static_cast<size_t>(cv0 + u * kBlock) * E);
+#pragma unroll
+          for (int u = 0; u < 2; u++) {
+            const int cv = cv0 + u * kBlock;
+            if (cv >= ncv) continue;
+            float f[E];
+            S::unpack(raw[u], f);
+#pragma unroll
+            for (int e = 0; e < E; e++) f[e] = 0.0f + f[e];
+            if (everywhere) {
+#pragma unroll 1
+              for (int q = 0; q < count; q++) store_vec<E>(pr.grad[q] + off + static_cast<size_t>(cv) * E, f);
+            } else {
+              store_vec<E>(single + static_cast<size_t>(cv) * E, f);
+            }
+          }
+        }
+      } else {
+        const float4 *row = reinterpret_cast<const float4 *>(a.my_rows + static_cast<size_t>(-src - 1) * d);
+        for (int c0 = threadIdx.x; c0 < nv4; c0 += 4 * kBlock) {
+          float4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; u++)
+            if (c0 + u * kBlock < nv4) v[u] = __ldcs(row + c0 + u * kBlock);
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            const int c = c0 + u * kBlock;
+            if (c >= nv4) continue;
+            if (everywhere) {
+#pragma unroll 1
+              for (int q = 0; q < count; q++) __stcs(reinterpret_cast<float4 *>(pr.grad[q] + off) + c, v[u]);
+            } else {
+              __stcs(reinterpret_cast<float4 *>(single) + c, v[u]);
+            }
+          }
+        }
+      }
+    }
+  } else {
+    const int zero_ctas = gridDim.x - a.push_ctas;
+    const int nv4 = d / 4;
+    float *mine = pr.grad[pr.me];
+    int v = blockIdx.x - a.push_ctas;
+    int slot = v < a.vocab ? ld_co(a.slot_map + v) : 0;
+    while (v < a.vocab) {
+      const int next = v + zero_ctas;
+      const int next_slot = next < a.vocab ? ld_co(a.slot_map + next) : 0;  // fetched one row ahead
+      if (slot < 0) {
+        float4 *dst = reinterpret_cast<float4 *>(mine + static_cast<size_t>(v) * d);
+        for (int c = threadIdx.x; c < nv4; c += kBlock) __stcs(dst + c, make_float4(0.f, 0.f, 0.f, 0.f));
+      }
+      v = next;
+      slot = next_slot;
+    }
+  }
+  signal_when_grid_done(sig);
 }
 
 // Second half of the peer exchange, run by the owner of a slot.  Every CTA first waits until all
@@ -309,26 +516,6 @@ bool group_ok(const dlb_peer_group *g) {
          g->status != nullptr;
 }
 
-// The arguments every rank-plan scatter shares.
-ScatterArgs rank_scatter_args(const Plan &pg, const RankPlan &r, int tokens_per_rank, int my_rank, int max_rows, int d) {
-  ScatterArgs a{};
-  a.perm = pg.vals[pg.passes & 1];
-  a.seg_b = r.row_begin;
-  a.seg_e = r.row_end;
-  a.long_row = r.long_row;
-  a.long_first = r.long_first;
-  a.long_b = r.row_begin;
-  a.long_e = r.row_end;
-  a.long_out = nullptr;
-  a.meta = r.header + 1;
-  a.scratch = r.scratch;
-  a.out_rows_dev = r.header;
-  a.out_rows = max_rows;
-  a.tok_offset = my_rank * tokens_per_rank;
-  a.d = d;
-  return a;
-}
-
 }  // namespace
 }  // namespace dlb
 
@@ -365,7 +552,8 @@ extern "C" int dlb_embed_rank_plan(const void *global_plan, int global_tokens, i
                pg.vals[pg.passes & 1], global_tokens, tokens_per_rank, my_rank, vocab, r);
     DLB_LAUNCH_CHECK("rank_plan_runs");
   }
-  launch_pdl(rank_plan_number_kernel, 1, 1024, 0, st, pg.seg_start, vocab, r);
+  launch_pdl(rank_plan_number_kernel, 1, 1024, 0, st, pg.seg_start, pg.vals[pg.passes & 1], my_rank * tokens_per_rank,
+             my_rank, vocab, r);
   DLB_LAUNCH_CHECK("rank_plan_number");
   return DLB_OK;
 }
@@ -382,14 +570,13 @@ extern "C" int dlb_embed_scatter_bwd_compact(const void *dy, const void *global_
   if (max_rows == 0) return DLB_OK;
   const Plan pg = make_plan(const_cast<void *>(global_plan), global_tokens, vocab, d);
   const RankPlan r = make_rank_plan(rank_plan, vocab, tokens_per_rank, d);
-  ScatterArgs a = rank_scatter_args(pg, r, tokens_per_rank, my_rank, max_rows, d);
+  ScatterArgs a = rank_scatter_args(pg, r, tokens_per_rank, my_rank, max_rows, d, true);
   a.out = compact_rows;
   const int e = dtype == DLB_BF16 ? 8 : 4;
   DLB_REQUIRE(d % e == 0 && aligned16(dy) && (e == 8 ? aligned32(compact_rows) : aligned16(compact_rows)),
               DLB_ERR_UNSUPPORTED, "embed_scatter_bwd_compact: d must be a multiple of %d and the buffers 32-byte aligned", e);
-  if (dtype == DLB_F32) return launch_scatter_rows<float>(dy, a, r.max_sub, 0, nullptr, nullptr, nullptr, as_stream(stream));
-  if (dtype == DLB_BF16)
-    return launch_scatter_rows<__nv_bfloat16>(dy, a, r.max_sub, 0, nullptr, nullptr, nullptr, as_stream(stream));
+  if (dtype == DLB_F32) return launch_scatter_rows<float>(dy, a, r.max_sub, 0, as_stream(stream));
+  if (dtype == DLB_BF16) return launch_scatter_rows<__nv_bfloat16>(dy, a, r.max_sub, 0, as_stream(stream));
   set_error("embed_scatter_bwd_compact: unknown dtype %d", dtype);
   return DLB_ERR_INVALID_ARG;
 }
@@ -466,14 +653,43 @@ extern "C" int dlb_embed_scatter_bwd_peer(const void *dy, const void *global_pla
   const RankPlan r = make_rank_plan(rank_plan, vocab, tokens_per_rank, d);
   route.used_rows = r.used_rows;
   route.src_mask = r.src_mask;
-  ScatterArgs a = rank_scatter_args(pg, r, tokens_per_rank, peers->my_rank, max_rows > 0 ? max_rows : 1, d);
+  cudaStream_t st = as_stream(stream);
+  // 1. the sums of the rows this rank has SEVERAL tokens for, into the plan's own buffer (local,
+  //    HBM-bound).  A looping grid: the exact number of rows is read on the device, so the host neither
+  //    waits for the plan nor launches CTAs for rows that do not exist.
+  int multi_bound = max_rows < r.max_multi ? max_rows : r.max_multi;
+  if (multi_bound < 1) multi_bound = 1;
+  ScatterArgs a = rank_scatter_args(pg, r, tokens_per_rank, peers->my_rank, multi_bound, d, false);
+  a.out = r.my_rows;
+  const int phases = get_option("embed_peer_phases");  // measurements only: 1 sums, 2 push
+  if (phases != 2) {
+    const int row_ctas = 8 * sm_count();
+    const int rc = dtype == DLB_F32 ? launch_scatter_rows<float>(dy, a, r.max_sub, row_ctas, st)
+                                    : launch_scatter_rows<__nv_bfloat16>(dy, a, r.max_sub, row_ctas, st);
+    if (rc != DLB_OK) return rc;
+  }
+  if (phases == 1) return DLB_OK;
+  // 2. every row out to the tables / the owners, the small gradients along with them, zeros into the
+  //    rows nobody uses, then the flag.
+  PushArgs pa{};
+  pa.my_rows = r.my_rows;
+  pa.my_route = r.my_route;
+  pa.my_src = r.my_src;
+  pa.n_mine = r.header + kHdrMine;
+  pa.slot_map = r.slot_map;
+  pa.d = d;
+  pa.vocab = vocab;
+  pa.push_ctas = 4 * sm_count();
   PeerSignal sig{};
-  fill_signal(&sig, peers, r.header + 4, signal_channel, signal_epoch);
-  // A persistent grid: the exact number of used rows is read on the device, so the host neither waits
-  // for the plan nor launches CTAs for rows that do not exist.
-  const int row_ctas = 8 * sm_count();
-  if (dtype == DLB_F32) return launch_scatter_rows<float>(dy, a, r.max_sub, row_ctas, &route, &push, &sig, as_stream(stream));
-  return launch_scatter_rows<__nv_bfloat16>(dy, a, r.max_sub, row_ctas, &route, &push, &sig, as_stream(stream));
+  fill_signal(&sig, peers, r.header + kHdrDonePush, signal_channel, signal_epoch);
+  const int grid = 8 * sm_count();
+  if (dtype == DLB_F32)
+    launch_pdl(push_rows_kernel<float>, grid, kBlock, 0, st, static_cast<const float *>(dy), pa, route, push, sig);
+  else
+    launch_pdl(push_rows_kernel<__nv_bfloat16>, grid, kBlock, 0, st, static_cast<const __nv_bfloat16 *>(dy), pa, route,
+               push, sig);
+  DLB_LAUNCH_CHECK("push_rows");
+  return DLB_OK;
 }
 
 extern "C" int dlb_embed_reduce_broadcast_peer(void *rank_plan, int tokens_per_rank, const dlb_peer_group *peers,
@@ -516,7 +732,7 @@ extern "C" int dlb_embed_reduce_broadcast_peer(void *rank_plan, int tokens_per_r
   a.wait_epoch = wait_epoch;
   a.limit_ns = static_cast<unsigned long long>(peers->timeout_ms) * 1000000ull;
   PeerSignal sig{};
-  fill_signal(&sig, peers, r.header + 5, signal_channel, signal_epoch);
+  fill_signal(&sig, peers, r.header + kHdrDoneReduce, signal_channel, signal_epoch);
   const int grid = 4 * sm_count();
   launch_pdl(reduce_broadcast_kernel, grid, kBlock, 0, as_stream(stream), a, sig);
   DLB_LAUNCH_CHECK("reduce_broadcast");

@@ -132,11 +132,11 @@ __device__ __forceinline__ void wait_for_peers(const uint32_t *my_flags, int n, 
   __syncthreads();
 }
 
-// ---- where an output row goes ------------------------------------------------------------------
-// Peer routing: output row r is a slot of the list of table rows some rank uses.  If this rank is
-// the only one with tokens for it (src_mask[r] has just this rank's bit) the finished row is stored
-// into row used_rows[r] of EVERY rank's dense table; otherwise the partial sum goes to the receive
-// area of the slot's owner (rank r % n), laid out [source rank][r / n][d].
+// ---- where a summed row goes when the ranks exchange over peer memory ---------------------------------
+// A slot is an entry of the list of table rows some rank uses.  If this rank is the only one with
+// tokens for it (src_mask[slot] has just this rank's bit) the finished row is stored into row
+// used_rows[slot] of EVERY rank's dense table; otherwise the partial sum goes to the receive area of
+// the slot's owner (rank slot % n), laid out [source rank][slot / n][d].
 struct PeerRoute {
   float *recv[kMaxPeers];
   float *grad[kMaxPeers];
@@ -155,10 +155,12 @@ struct ScatterArgs {
   const int32_t *long_out;     // output row of a long row (indexed likewise), or null: the entry itself
   const int32_t *meta;         // {number of long rows, number of sub-segments}
   float *scratch;              // [sub-segments][d]
-  float *out;                  // local output [out_rows][d] (unused with peer routing)
+  float *out;                  // output [out_rows][d]
   const int32_t *out_rows_dev; // device word holding the exact number of output rows, or null
   int out_rows;                // number of output rows, or an upper bound when out_rows_dev is given
   int tok_offset;              // subtracted from every perm value (a rank's first token)
+  int skip_empty;              // 1: rows without tokens are not written (their contents are never read)
+  int contiguous;              // 1: seg_e[r] == seg_b[r + 1] (the plan of dlb_embed_sort_tokens itself)
   int d, sub_groups, rows_cta;
 };
 
@@ -234,48 +236,15 @@ __device__ __forceinline__ void store_row(float *dst, int cv0, int tx, int ncv, 
   }
 }
 
-// Output row r, wherever it belongs.  has_tokens: this rank has tokens for r (peer routing sends
-// nothing otherwise; local output writes the zeros).
-template <bool PEER, int E, int KV>
-__device__ __forceinline__ void emit_row(const ScatterArgs &a, const PeerRoute &pr, int r, int cv0, int tx, int ncv,
-                                         const float (&acc)[KV][E]) {
-  if constexpr (!PEER) {
-    store_row<E, KV>(a.out + static_cast<size_t>(r) * a.d, cv0, tx, ncv, acc);
-  } else {
-    const uint32_t mask = ld_co(pr.src_mask + r);
-    if (mask == (1u << pr.me)) {
-      const size_t off = static_cast<size_t>(ld_co(pr.used_rows + r)) * a.d;
-#pragma unroll 1
-      for (int q = 0; q < pr.n; q++) store_row<E, KV>(pr.grad[q] + off, cv0, tx, ncv, acc);
-    } else {
-      const int j = r / pr.n;
-      if (j >= pr.cap) {
-        atomicOr(pr.status, 1u << 31);
-        return;
-      }
-      store_row<E, KV>(pr.recv[r % pr.n] + (static_cast<size_t>(pr.me) * pr.cap + j) * a.d, cv0, tx, ncv, acc);
-    }
-  }
-}
-
 // blockDim = (tx, ty), tx*ty = kEmbBlock.  grid.x = sub_groups + row CTAs; grid.y tiles columns when
 // a row has more than tx*KV vectors.  The sub-segment groups come first so that the heaviest work
 // starts first.  A row CTA takes groups of rows_cta consecutive output rows (group index strides
 // by the number of row CTAs): it fetches their ranges and the token list they share (consecutive
 // rows are consecutive in the sorted list) into shared memory once, then each thread row walks
 // its rows, so the only dependent global access left per row is the dy load itself.
-// SMALL (peer routing): `small` (small_n floats, a multiple of 4) is copied into slot `me` of every
-// rank's small_recv.  (`sig` is announced by combine_long_kernel, which always follows.)
-struct SmallPush {
-  const float *src;
-  float *dst[kMaxPeers];  // every rank's [n ranks][small_n] area
-  int small_n;
-};
-
-template <typename T, int KV, bool PEER>
+template <typename T, int KV>
 __global__ void __launch_bounds__(kEmbBlock, KV >= 4 ? 1 : 3)
-scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a, const __grid_constant__ PeerRoute pr,
-                    const __grid_constant__ SmallPush sp, const __grid_constant__ PeerSignal sig) {
+scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a) {
   pdl_prologue();
   using S = Store<T>;
   constexpr int E = S::kPerVec;
@@ -288,19 +257,6 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a, const __
   const int tid = threadIdx.y * tx + threadIdx.x;
   const int tok_offset = a.tok_offset;
   float acc[KV][E];
-
-  if constexpr (PEER) {
-    if (sp.src != nullptr) {
-      const int n4 = sp.small_n / 4;
-      const int cta = blockIdx.y * gridDim.x + blockIdx.x;
-      const int ctas = gridDim.x * gridDim.y;
-      for (int i = cta * kEmbBlock + tid; i < n4; i += ctas * kEmbBlock) {
-        const float4 v = *reinterpret_cast<const float4 *>(sp.src + 4 * static_cast<size_t>(i));
-        for (int q = 0; q < pr.n; q++)
-          __stcs(reinterpret_cast<float4 *>(sp.dst[q] + static_cast<size_t>(pr.me) * sp.small_n) + i, v);
-      }
-    }
-  }
 
   if (static_cast<int>(blockIdx.x) < a.sub_groups) {
     // ------------------------------------------------ sub-segments of long rows
@@ -333,25 +289,11 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a, const __
         s_e[i] = ld_co(a.seg_e + v_first + i);
       }
       __syncthreads();
-      // Ranges of consecutive rows are consecutive in the sorted list, except that (rank plans) a row
-      // this rank has no token for carries an empty range anywhere: take the span of the non-empty ones.
-      int p0 = 0, np = kScatterPermCap + 1;
-      {
-        int first = -1, last = -1;
-        for (int i = 0; i < nrows; i++) {
-          if (s_e[i] > s_b[i]) {
-            if (first < 0) first = i;
-            last = i;
-          }
-        }
-        if (first >= 0) {
-          p0 = s_b[first];
-          np = s_e[last] - p0;
-        } else {
-          np = 0;
-        }
-      }
-      const bool staged = np >= 0 && np <= kScatterPermCap;
+      // Dense plan: the ranges of consecutive rows are consecutive in the sorted list, so the CTA's
+      // whole token list is one span that is fetched once.  Rank plans leave other ranks' tokens (and
+      // empty rows) between the ranges: no staging there.
+      const int p0 = s_b[0], np = s_e[nrows - 1] - p0;
+      const bool staged = a.contiguous != 0 && np <= kScatterPermCap;
       if (staged)
         for (int i = tid; i < np; i += kEmbBlock) s_perm[i] = ld_co(a.perm + p0 + i) - tok_offset;
       __syncthreads();
@@ -382,8 +324,7 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a, const __
         }
 #pragma unroll
         for (int u = 0; u < U; u++) {
-          if (state[u] < 0) continue;
-          if (PEER && state[u] == 0) continue;  // nothing to send for a row without local tokens
+          if (state[u] < 0 || (state[u] == 0 && a.skip_empty)) continue;
 #pragma unroll
           for (int k = 0; k < KV; k++) {
 #pragma unroll
@@ -395,7 +336,7 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a, const __
               for (int q = 0; q < E; q++) acc[k][q] += f[q];
             }
           }
-          emit_row<PEER, E, KV>(a, pr, v_first + rl0 + u * ty, cv0, tx, ncv, acc);
+          store_row<E, KV>(a.out + static_cast<size_t>(v_first + rl0 + u * ty) * d, cv0, tx, ncv, acc);
         }
       }
       // Rows with 2..kSubLen tokens.
@@ -405,7 +346,7 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a, const __
         // one instance of the loop for both sources of the token list (two cost 40 more registers)
         sum_tokens<T, KV>(dy, [&](int j) { return staged ? s_perm[j - p0] : ld_co(a.perm + j) - tok_offset; }, b, e, d,
                           cv0, tx, ncv, acc);
-        emit_row<PEER, E, KV>(a, pr, v_first + rl, cv0, tx, ncv, acc);
+        store_row<E, KV>(a.out + static_cast<size_t>(v_first + rl) * d, cv0, tx, ncv, acc);
       }
       __syncthreads();  // the staging arrays are refilled by the next group
     }
@@ -415,14 +356,10 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a, const __
 // out[row,:] of every long row = the sum of its scratch rows.  A work item is (long row, block of
 // 32 float4 column vectors); CTAs loop over the items.  Each of the CTA's kCombineSlices warps adds
 // one contiguous slice of the row's sub-segments in order (512 contiguous bytes per sub-segment),
-// then the slice sums are added in warp order through shared memory.  With peer routing this is the
-// last kernel of the pushing phase: its last CTA announces `sig`.
+// then the slice sums are added in warp order through shared memory.
 static_assert(kCombineSlices * 32 == kEmbBlock, "one warp per slice");
 
-template <bool PEER>
-__global__ void __launch_bounds__(kEmbBlock)
-combine_long_kernel(const __grid_constant__ ScatterArgs a, const __grid_constant__ PeerRoute pr,
-                    const __grid_constant__ PeerSignal sig) {
+static __global__ void __launch_bounds__(kEmbBlock) combine_long_kernel(const __grid_constant__ ScatterArgs a) {
   pdl_prologue();
   __shared__ float4 part[kCombineSlices][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -455,24 +392,9 @@ combine_long_kernel(const __grid_constant__ ScatterArgs a, const __grid_constant
       }
       const int li = ld_co(a.long_row + row);
       const int out_row = a.long_out != nullptr ? ld_co(a.long_out + li) : li;
-      if constexpr (!PEER) {
-        __stcs(reinterpret_cast<float4 *>(a.out + static_cast<size_t>(out_row) * d + c), r);
-      } else {
-        const uint32_t mask = ld_co(pr.src_mask + out_row);
-        if (mask == (1u << pr.me)) {
-          const size_t off = static_cast<size_t>(ld_co(pr.used_rows + out_row)) * d + c;
-          for (int q = 0; q < pr.n; q++) __stcs(reinterpret_cast<float4 *>(pr.grad[q] + off), r);
-        } else if (out_row / pr.n < pr.cap) {
-          __stcs(reinterpret_cast<float4 *>(pr.recv[out_row % pr.n] +
-                                            (static_cast<size_t>(pr.me) * pr.cap + out_row / pr.n) * d + c),
-                 r);
-        } else {
-          atomicOr(pr.status, 1u << 31);
-        }
-      }
+      __stcs(reinterpret_cast<float4 *>(a.out + static_cast<size_t>(out_row) * d + c), r);
     }
   }
-  if constexpr (PEER) signal_when_grid_done(sig);
 }
 
 struct BlockShape {
@@ -484,11 +406,11 @@ inline BlockShape shape_for(int ncv) {
   return {tx, kEmbBlock / tx};
 }
 
-// Launches the scatter for storage type T.  `max_sub` bounds the number of sub-segments the plan
-// can hold; `row_ctas` = 0 means one CTA per group of rows.  a.sub_groups / a.rows_cta are set here.
+// Launches the scatter (and the sum of the long rows) for storage type T.  `max_sub` bounds the number
+// of sub-segments the plan can hold; `row_ctas` = 0 means one CTA per group of rows, otherwise that many
+// CTAs loop over the groups (for when the exact row count is only known on the device).
 template <typename T>
-int launch_scatter_rows(const void *dy, ScatterArgs a, int max_sub, int row_ctas, const PeerRoute *peer,
-                        const SmallPush *small, const PeerSignal *sig, cudaStream_t st) {
+int launch_scatter_rows(const void *dy, ScatterArgs a, int max_sub, int row_ctas, cudaStream_t st) {
   constexpr int E = Store<T>::kPerVec;
   const int ncv = a.d / E;
   const BlockShape bs = shape_for(ncv);
@@ -498,33 +420,20 @@ int launch_scatter_rows(const void *dy, ScatterArgs a, int max_sub, int row_ctas
   const int kv = (need >= 4 && E == 8) ? 4 : (need >= 2 ? 2 : 1);
   // Sub-segment groups loop over the sub-segments, so a few hundred CTAs cover any count.
   a.sub_groups = min(ceil_div(max_sub, bs.ty), 4 * sm_count());
-  a.rows_cta = bs.ty > kScatterRowsPerCta ? bs.ty : kScatterRowsPerCta;
-  if (peer != nullptr && a.rows_cta > 8 && bs.ty <= 8) a.rows_cta = 8;  // few rows carry tokens: more, smaller groups
+  // Rows per CTA: 16 where the rows' token lists are one span fetched once; 4 (one round of the row
+  // loop) for a rank plan's rows, which are few and should spread over many CTAs.
+  const int want_rows = a.contiguous ? kScatterRowsPerCta : 4;
+  a.rows_cta = bs.ty > want_rows ? bs.ty : want_rows;
   const int groups = ceil_div(a.out_rows, a.rows_cta);
   const int row_groups = row_ctas > 0 ? min(groups, row_ctas) : groups;
   dim3 grid(a.sub_groups + row_groups, ceil_div(ncv, bs.tx * kv));
-  const PeerRoute no_route{};
-  const SmallPush no_small{};
-  const PeerSignal no_signal{};
-  auto go = [&](auto kern) {
-    launch_pdl(kern, grid, dim3(bs.tx, bs.ty), 0, st, static_cast<const T *>(dy), a, peer ? *peer : no_route,
-               small ? *small : no_small, sig ? *sig : no_signal);
-  };
-  if (peer != nullptr) {
-    if (kv == 4) go(scatter_rows_kernel<T, 4, true>);
-    else if (kv == 2) go(scatter_rows_kernel<T, 2, true>);
-    else go(scatter_rows_kernel<T, 1, true>);
-  } else {
-    if (kv == 4) go(scatter_rows_kernel<T, 4, false>);
-    else if (kv == 2) go(scatter_rows_kernel<T, 2, false>);
-    else go(scatter_rows_kernel<T, 1, false>);
-  }
+  auto go = [&](auto kern) { launch_pdl(kern, grid, dim3(bs.tx, bs.ty), 0, st, static_cast<const T *>(dy), a); };
+  if (kv == 4) go(scatter_rows_kernel<T, 4>);
+  else if (kv == 2) go(scatter_rows_kernel<T, 2>);
+  else go(scatter_rows_kernel<T, 1>);
   DLB_LAUNCH_CHECK("scatter_rows");
-  const int cgrid = 8 * sm_count();  // 8 CTAs fit an SM; each loops over (long row, column block) items
-  if (peer != nullptr)
-    launch_pdl(combine_long_kernel<true>, cgrid, kEmbBlock, 0, st, a, *peer, sig ? *sig : no_signal);
-  else
-    launch_pdl(combine_long_kernel<false>, cgrid, kEmbBlock, 0, st, a, no_route, no_signal);
+  // 8 CTAs fit an SM; each loops over (long row, column block) items
+  launch_pdl(combine_long_kernel, 8 * sm_count(), kEmbBlock, 0, st, a);
   DLB_LAUNCH_CHECK("combine_long");
   return DLB_OK;
 }

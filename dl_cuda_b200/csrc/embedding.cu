@@ -396,8 +396,9 @@ int scatter_typed(const Plan &p, const void *dy, float *grad, int vocab, int d, 
   a.scratch = p.scratch;
   a.out = grad;
   a.out_rows = vocab;
+  a.contiguous = 1;
   a.d = d;
-  return launch_scatter_rows<T>(dy, a, p.max_sub, 0, nullptr, nullptr, nullptr, st);
+  return launch_scatter_rows<T>(dy, a, p.max_sub, 0, st);
 }
 
 bool embed_args_ok(int num_tokens, int vocab, int d) {

@@ -63,13 +63,17 @@ DLB_API uint64_t dlb_launch_count(void);
 /* Kernel-variant overrides for measurements: where a kernel exists in more than one form,
  * the heuristic's choice can be replaced so that both forms are timed in one process on the
  * same buffers.  value 0 gives the choice back to the heuristic; an override that does not
- * fit a call's shape is ignored for that call.  Results are the same whatever the choice.
+ * fit a call's shape is ignored for that call.  Results are the same whatever the choice
+ * (except where an option says otherwise).
  *   "gather_rows_in_flight"      4 | 8   table rows a thread loads before its first store
  *   "ln_bwd_pipe"                1 never the bulk-copy pipeline | 2 whenever the shape allows
  *   "ln_bwd_pipe_threads"        128 | 256 | 512 column threads per CTA
  *   "ln_bwd_pipe_ctas_per_sm"    1 | 2
  *   "ln_bwd_pipe_rows_per_tile"  1 | 2 | 4 | 8
  *   "act_bwd_partial_rows"       upper bound of the partial rows of a fused bias gradient
+ *   "embed_peer_phases"          1 only the local sums | 2 only the push of
+ *                                dlb_embed_scatter_bwd_peer (for timing the halves; results are
+ *                                incomplete while it is set)
  * Process-wide, not synchronised with calls in flight.  No counterpart in the reference. */
 DLB_API int dlb_set_option(const char *name, int value);
 
@@ -328,12 +332,16 @@ DLB_API int dlb_checkpoint_unpack(int n_groups, float *const *h_params, const in
  * and fills a dlb_peer_group with the addresses of all ranks' buffers AS MAPPED ON THE
  * CALLING GPU (its own at index my_rank) plus a device status word of its own.
  *
- * dlb_embed_scatter_bwd_peer: sums this rank's tokens per used row.  A row that ONLY this
- * rank has tokens for is final: it is stored straight into row v of every rank's grad.
- * A row several ranks share goes to the receive area of the slot's owner (slot % n_ranks)
- * at recv[my_rank][slot / n_ranks].  Rows without local tokens send nothing.  If `small`
- * is given, its small_n floats are copied to small[q][my_rank] on every rank q.  When the
- * last CTA has issued its stores the kernel announces (signal_channel, signal_epoch).
+ * dlb_embed_scatter_bwd_peer: (1) sums the rows this rank has several tokens for into a
+ * buffer inside the rank plan (local, HBM-bound); (2) streams every row this rank has tokens
+ * for to where it belongs, in a copy-shaped kernel that keeps NVLink full.  A row that ONLY
+ * this rank has tokens for is final: it is stored straight into row v of every rank's grad
+ * (a row with one token is read from dy itself).  A row several ranks share goes to the
+ * receive area of the slot's owner (slot % n_ranks) at recv[my_rank][slot / n_ranks].  Rows
+ * without local tokens send nothing.  The same kernel writes zeros into the rows of THIS
+ * rank's grad that no rank uses, and, if `small` is given, copies its small_n floats to
+ * small[q][my_rank] on every rank q.  When the last CTA has issued its stores the kernel
+ * announces (signal_channel, signal_epoch).
  *
  * dlb_embed_reduce_broadcast_peer: waits (bounded by timeout_ms) until every rank has
  * announced (wait_channel, wait_epoch); for each slot it owns that several ranks share it
@@ -342,7 +350,6 @@ DLB_API int dlb_checkpoint_unpack(int n_groups, float *const *h_params, const in
  * same bits on every rank).  Then it announces (signal_channel, signal_epoch); follow it
  * with dlb_peer_wait on that channel: after it every rank's table is complete.
  *
- * Rows no rank uses are zeroed locally: dlb_embed_expand_rows(what = 1), any stream.
  * Epochs per channel grow by one per use, the same on all ranks.  A rank may start the
  * next step's dlb_embed_scatter_bwd_peer only when every rank is done with the tables of
  * this step (its consumer has run): the all-gather of the next step's ids (dlb_peer_put

@@ -32,7 +32,6 @@ def main():
     px = PeerExchange(dist, vocab, d, min(vocab, total), dev, tokens_per_rank=per_rank, small_n=small_n)
     px.barrier()
     table = px.table_grad()
-    side = torch.cuda.Stream()
     for step in range(3):
         ids_all = torch.from_numpy(zipf_ids(rng_for(500 + step, 0), total, vocab).astype(np.int32)).to(dev)
         dy_all = torch.from_numpy(rng_for(500 + step, 1).standard_normal((total, d)).astype(np.float32)).to(dev)
@@ -46,14 +45,11 @@ def main():
         gathered = px.ids_all[:total]
         global_plan = ops.embed_sort_tokens(gathered, vocab, d)
         rank_plan = ops.embed_rank_plan(global_plan, total, per_rank, world, rank, vocab, d)
-        side.wait_stream(torch.cuda.current_stream())
-        ops.embed_expand_rows(None, rank_plan, per_rank, table, what=1, stream=side.cuda_stream)
         pushed, done = px.next_epoch(px.CH_PUSHED), px.next_epoch(px.CH_DONE)
         ops.embed_scatter_bwd_peer(dy, global_plan, total, rank_plan, per_rank, px.group, small, min(vocab, total), vocab,
                                    px.CH_PUSHED, pushed)
         ops.embed_reduce_broadcast_peer(rank_plan, per_rank, px.group, small, vocab, d, px.CH_PUSHED, pushed,
                                         px.CH_DONE, done)
-        torch.cuda.current_stream().wait_stream(side)
         px.wait(px.CH_DONE)
         torch.cuda.synchronize()
         assert px.timed_out() == 0, "a wait gave up or the receive area was too small"

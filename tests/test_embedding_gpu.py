@@ -262,7 +262,24 @@ def test_rank_plan_against_numpy():
         row_end = ints[base + 3 * stride:base + 3 * stride + used]
         src_mask = ints[base + 4 * stride:base + 4 * stride + used]
         assert np.array_equal(used_list, used_rows)
-        assert np.array_equal(slot_map[used_rows], np.arange(used)) and np.all(np.delete(slot_map, used_rows) == -1)
+        mine_rows = np.unique(ids[lo:hi][ids[lo:hi] < vocab])
+        assert int(ints[3]) == mine_rows.size  # rows this rank has tokens for
+        local_counts = np.bincount(ids[lo:hi][ids[lo:hi] < vocab], minlength=vocab)
+        assert int(ints[6]) == int((local_counts > 1).sum())  # of those, rows with several tokens
+        mine_stride = (min(vocab, per) * 4 + 255) // 256 * 64  # int32 words per [my rows] array
+        my_route = ints[base + 8 * stride:base + 8 * stride + mine_rows.size]
+        my_src = ints[base + 8 * stride + mine_stride:base + 8 * stride + mine_stride + mine_rows.size]
+        slot_of = {int(v): i for i, v in enumerate(used_rows)}
+        multi_seen = 0
+        for k, v in enumerate(mine_rows):
+            sole = src_mask[slot_of[int(v)]] == (1 << r)
+            want_route = (int(v) | 0x80000000) - (1 << 32) if sole else slot_of[int(v)]
+            assert int(my_route[k]) == want_route
+            if local_counts[v] == 1:
+                assert lo + int(my_src[k]) == int(np.flatnonzero(ids[lo:hi] == v)[0]) + lo
+            else:
+                multi_seen += 1
+                assert int(my_src[k]) == -multi_seen
         for slot in range(0, used, 7):
             v = used_rows[slot]
             toks = order[inside & (ids[order] == v)]
@@ -299,8 +316,9 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
     phases run rank after rank (all pushes, then all owner sums: every flag is set before it is waited
     for, so no kernel waits for a later launch).  A row one rank alone has tokens for is stored into every
     table by that rank; a shared row goes to its owner, which adds the partial rows in rank order and
-    stores the sum into every table; the small gradients of all ranks are summed in rank order.  Every
-    table must equal the single-rank dense gradient, twice in a row with stale receive areas."""
+    stores the sum into every table; every rank zeroes the rows nobody uses in its own table; the small
+    gradients of all ranks are summed in rank order.  Every table must equal the single-rank dense
+    gradient, twice in a row with stale tables and receive areas."""
     dt = torch.bfloat16 if storage == "bf16" else torch.float32
     ids = zipf_ids(rng_for(71, 0), n, vocab)
     dy = dev(rng_for(71, 1).standard_normal((n, d)).astype(np.float32), dt)
@@ -327,7 +345,6 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
         for r in range(ranks):
             per, lo, hi = shard(n, ranks, r)
             plans.append(ops.embed_rank_plan(global_plan, n, per, ranks, r, vocab, d))
-            ops.embed_expand_rows(None, plans[r], per, em.tables[r], what=1)
         for r in range(ranks):
             per, lo, hi = shard(n, ranks, r)
             dy_r = dy[lo:hi].contiguous() if hi > lo else dy[:1].contiguous()
