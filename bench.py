@@ -165,7 +165,7 @@ class Chain:
     OPS = ["sort_tokens", "embed_gather_pe", "ln1_fwd", "relu_fwd", "ln2_fwd",
            "ln2_bwd", "relu_bwd", "ln1_bwd", "embed_scatter", "allreduce"]
 
-    def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist, exchange="peer"):
+    def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist, exchange="peer", clear="incremental"):
         from dl_cuda_b200 import capi, ops
         global allreduce_param_grads
         from dl_cuda_b200.sharding import allreduce_param_grads
@@ -194,9 +194,13 @@ class Chain:
         self.beta2 = torch.randn(D, generator=gp, device=dev) * 0.1
         self.bias1 = torch.randn(F, generator=gp, device=dev) * 0.1
         # token ids: pinned host copy (the only per-step host input) and device copy
+        # Two batches of ids, taken in turn: a step then meets a table gradient whose non-zero rows are
+        # those of ANOTHER batch, as in training (with one batch repeated, nothing would ever need clearing).
         rng = np.random.Generator(np.random.Philox(key=seed))
-        self.h_ids = torch.from_numpy(zipf_ids(rng, T, V)).pin_memory()
-        self.ids = self.h_ids.to(dev)
+        self.h_id_sets = [torch.from_numpy(zipf_ids(rng, T, V)).pin_memory() for _ in range(2)]
+        self.id_sets = [h.to(dev) for h in self.h_id_sets]
+        self.h_ids, self.ids = self.h_id_sets[0], self.id_sets[0]
+        self.step_no = 0
         # stand-ins for GEMM outputs
         self.attn_out, self.ff_out = randn(T, D), randn(T, D)
         self.ff_pre = randn(T, F)
@@ -235,6 +239,10 @@ class Chain:
             # Table-gradient exchange: the library's fused scatter-add + peer-memory exchange, or (asked for, or when
             # symmetric memory cannot be set up) NCCL's all-reduce of the compacted rows.
             self.peer = None
+            # Where the rows nobody uses are cleared: inside the push kernel (beside the NVLink-bound pushes),
+            # or early on the second stream (beside the compute kernels).
+            self.clear_early = clear == "early"
+            self.clear_mode = {"early": 0, "fused": 1, "incremental": 2}[clear]
             self.exchange_note = "nccl all-reduce of the compacted rows"
             if exchange == "peer":
                 try:
@@ -259,7 +267,7 @@ class Chain:
                     self.exchange_note += f" (peer exchange unavailable: {type(exc).__name__})"
             if self.peer is None:
                 self.compact_rows = torch.empty(min(V, Tg), D, device=dev)
-        self.distinct_ids = int(np.unique(self.h_ids.numpy()).size)
+        self.distinct_ids = int(np.mean([np.unique(h.numpy()).size for h in self.h_id_sets]))
 
     # algorithmic HBM bytes of each op for the local tokens (each input byte read once,
     # each output byte written once)
@@ -296,6 +304,8 @@ class Chain:
                 ev.record()
                 marks.append(ev)
 
+        self.h_ids, self.ids = self.h_id_sets[self.step_no % 2], self.id_sets[self.step_no % 2]
+        self.step_no += 1
         if copy_inputs:
             self.ids.copy_(self.h_ids, non_blocking=True)
         mark()
@@ -324,6 +334,14 @@ class Chain:
                 with torch.cuda.stream(plan_stream):
                     self.h_used.copy_(self.rank_plan[:4].view(torch.int32)[:1], non_blocking=True)
         self.plan_ready.record(plan_stream)
+        if self.dist.active and self.peer is not None and self.clear_early:
+            # The rows nobody uses are cleared on the second stream as soon as the plan says which they are,
+            # beside the forward and backward kernels (which, at a few thousand rows per GPU, leave HBM idle
+            # between them).
+            if plan_stream is not self.side:
+                self.side.wait_event(self.plan_ready)
+            chk(lib.dlb_embed_expand_rows(None, p(self.rank_plan), T, p(self.table_grad), V, D, 1, self.side.cuda_stream))
+            self.zero_done.record(self.side)
         mark()
         chk(lib.dlb_embed_gather_fwd(p(self.table), p(self.ids), p(self.pe), S, p(self.x0), T, V, D, code, st))
         mark()
@@ -359,10 +377,12 @@ class Chain:
             # stores and wait for the other ranks themselves.
             pushed, done = px.next_epoch(px.CH_PUSHED), px.next_epoch(px.CH_DONE)
             ops.embed_scatter_bwd_peer(self.dx1, self.ws_global, self.Tg, self.rank_plan, T, px.group, self.small_grads,
-                                       min(V, self.Tg), V, px.CH_PUSHED, pushed, stream=st)
+                                       min(V, self.Tg), V, px.CH_PUSHED, pushed, clear_unused=self.clear_mode, stream=st)
             mark()
-            ops.embed_reduce_broadcast_peer(self.rank_plan, T, px.group, self.small_grads, V, D, px.CH_PUSHED, pushed,
-                                            px.CH_DONE, done, stream=st)
+            ops.embed_reduce_broadcast_peer(self.rank_plan, T, px.group, self.small_grads, V, D, code, px.CH_PUSHED,
+                                            pushed, px.CH_DONE, done, stream=st)
+            if self.clear_early:
+                main.wait_event(self.zero_done)
             px.wait(px.CH_DONE, stream=st)  # every rank's table holds every row
         else:
             # Compacted form through NCCL: only the rows some rank uses are summed, all-reduced and expanded.
@@ -1039,6 +1059,10 @@ def main():
     ap.add_argument("--tokens", type=int, default=BATCH * SEQ, help="global token rows (default: batch 8 x seq 4096)")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: how the embedding-table gradient is exchanged (default: the library's peer-memory kernels)")
+    ap.add_argument("--clear", choices=["incremental", "fused", "early"], default="incremental",
+                    help="N > 1, peer exchange: the table rows no rank uses are cleared inside the push kernel, only "
+                         "those the previous step wrote (incremental) or all of them (fused), or all of them early on "
+                         "the second stream beside the compute kernels")
     ap.add_argument("--skip-kernels", action="store_true", help="skip the per-kernel fp32 sweep")
     ap.add_argument("--skip-cpu", action="store_true",
                     help="skip the baseline legs (the single-threaded host loops and the reference-kernel columns)")
@@ -1065,7 +1089,7 @@ def main():
     _, tokens_local = shard_rows(args.tokens, n, dist.rank, SEQ if args.tokens % (SEQ * n) == 0 else 1)
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     chain = Chain(tokens_local, SEQ, D_MODEL, D_FF, VOCAB, dtype, seed=1234 + dist.rank, dist=dist,
-                  exchange=args.exchange)
+                  exchange=args.exchange, clear=args.clear)
     lib = chain.lib
 
     parity = None

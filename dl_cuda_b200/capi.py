@@ -57,8 +57,8 @@ SIGNATURES = {
     "dlb_checkpoint_body_bytes": (_sz, [_i, _p]),
     "dlb_checkpoint_pack": (_i, [_i, _p, _p, _p, _sz, _p]),
     "dlb_checkpoint_unpack": (_i, [_i, _p, _p, _p, _sz, _p]),
-    "dlb_embed_scatter_bwd_peer": (_i, [_p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, C.c_uint32, _p]),
-    "dlb_embed_reduce_broadcast_peer": (_i, [_p, _i, _p, _p, _i, _i, _i, C.c_uint32, _i, C.c_uint32, _p]),
+    "dlb_embed_scatter_bwd_peer": (_i, [_p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, C.c_uint32, _p]),
+    "dlb_embed_reduce_broadcast_peer": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, C.c_uint32, _i, C.c_uint32, _p]),
     "dlb_peer_flags_bytes": (_sz, []),
     "dlb_peer_barrier": (_i, [_p, _i, _i, _i, C.c_uint32, _i, _p, _p]),
     "dlb_peer_wait": (_i, [_p, _i, _i, _i, C.c_uint32, _i, _p, _p]),
@@ -81,7 +81,7 @@ class PeerGroup(C.Structure):
     """dlb_peer_group of include/dlcuda_b200.h: the buffers of every rank as mapped on this GPU."""
     _fields_ = [("n_ranks", _i), ("my_rank", _i), ("cap_rows", _i), ("small_n", _i), ("timeout_ms", _i),
                 ("reserved", _i), ("flags", _p * MAX_PEERS), ("recv", _p * MAX_PEERS), ("grad", _p * MAX_PEERS),
-                ("small", _p * MAX_PEERS), ("status", _p)]
+                ("small", _p * MAX_PEERS), ("stage", _p * MAX_PEERS), ("status", _p)]
 
 
 class DlbError(RuntimeError):

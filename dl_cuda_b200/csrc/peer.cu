@@ -57,8 +57,7 @@ peer_put_kernel(const __grid_constant__ PutArgs a, const __grid_constant__ PeerF
   pdl_prologue();
   for (int q = 0; q < n; q++)
     for (size_t i = threadIdx.x; i < a.n16; i += 1024) a.dst[q][i] = a.src[i];
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();  // orders every thread's stores before the fences below (a fence is cumulative)
   if (threadIdx.x < n) {
     __threadfence_system();
     uint32_t *theirs = pf.flags[threadIdx.x] + channel * kMaxPeers + me;

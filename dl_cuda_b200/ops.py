@@ -121,7 +121,8 @@ def embed_scatter_bwd(dy, ids, vocab, workspace, grad=None):
 
 
 def embed_rank_plan_workspace(vocab, tokens_per_rank, d, device):
-    return _workspace(capi.lib().dlb_embed_rank_plan_bytes(vocab, tokens_per_rank, d), device)
+    """Zero-filled: the workspace carries a record from one exchange to the next (see clear_unused = 2)."""
+    return _workspace(capi.lib().dlb_embed_rank_plan_bytes(vocab, tokens_per_rank, d), device).zero_()
 
 
 def embed_rank_plan(global_plan, global_tokens, tokens_per_rank, n_ranks, my_rank, vocab, d, rank_plan=None, stream=None):
@@ -314,7 +315,8 @@ def _addr_array(addresses):
     return (ctypes.c_void_p * len(addresses))(*addresses)
 
 
-def peer_group(n_ranks, my_rank, cap_rows, flags, recv, grad, status, small=None, small_n=0, timeout_ms=2000):
+def peer_group(n_ranks, my_rank, cap_rows, flags, recv, grad, status, small=None, small_n=0, timeout_ms=2000,
+               stage=None):
     """A capi.PeerGroup from lists of device addresses (ints), one per rank, as mapped on this GPU."""
     import ctypes
     g = capi.PeerGroup()
@@ -322,26 +324,29 @@ def peer_group(n_ranks, my_rank, cap_rows, flags, recv, grad, status, small=None
     for q in range(n_ranks):
         g.flags[q], g.recv[q], g.grad[q] = flags[q], recv[q], grad[q]
         g.small[q] = small[q] if small is not None else None
+        g.stage[q] = stage[q] if stage is not None else None
     g.status = ptr(status)
     g._keepalive = status
     return g
 
 
 def embed_scatter_bwd_peer(dy, global_plan, global_tokens, rank_plan, tokens_per_rank, group, small, max_rows, vocab,
-                           channel, epoch, stream=None):
+                           channel, epoch, clear_unused=1, stream=None):
     import ctypes
     d = dy.shape[1]
     check(capi.lib().dlb_embed_scatter_bwd_peer(ptr(dy), ptr(global_plan), global_tokens, ptr(rank_plan), tokens_per_rank,
-                                                ctypes.byref(group), ptr(small), max_rows, vocab, d, dtype_of(dy),
-                                                channel, epoch, current_stream() if stream is None else stream))
+                                                ctypes.byref(group), ptr(small), max_rows, int(clear_unused), vocab, d,
+                                                dtype_of(dy), channel, epoch,
+                                                current_stream() if stream is None else stream))
 
 
-def embed_reduce_broadcast_peer(rank_plan, tokens_per_rank, group, small_out, vocab, d, wait_channel, wait_epoch,
+def embed_reduce_broadcast_peer(rank_plan, tokens_per_rank, group, small_out, vocab, d, dtype, wait_channel, wait_epoch,
                                 signal_channel, signal_epoch, stream=None):
+    """dtype: the storage type of the gradients the scatter was given (capi.F32 / capi.BF16)."""
     import ctypes
     check(capi.lib().dlb_embed_reduce_broadcast_peer(ptr(rank_plan), tokens_per_rank, ctypes.byref(group), ptr(small_out),
-                                                     vocab, d, wait_channel, wait_epoch, signal_channel, signal_epoch,
-                                                     current_stream() if stream is None else stream))
+                                                     vocab, d, dtype, wait_channel, wait_epoch, signal_channel,
+                                                     signal_epoch, current_stream() if stream is None else stream))
 
 
 def peer_barrier(peer_flags, my_rank, channel, epoch, status, timeout_ms=2000, stream=None):

@@ -38,8 +38,8 @@ class PeerExchange:
     Symmetric allocations (torch.distributed._symmetric_memory: the same buffer on every rank, each
     mapped into every rank's address space): the receive area [world][cap_rows][d] fp32 that peers push
     shared rows into, the dense [vocab, d] gradient that finished rows are stored into, the area the
-    small parameter gradients of every rank land in, the gathered token ids of all ranks, and the flag
-    words.  The kernels, the flags and the waits are the library's own (dlb_peer_put,
+    small parameter gradients of every rank land in, the gathered token ids of all ranks, the staging
+    rows for gradients that travel as bf16, and the flag words.  The kernels, the flags and the waits are the library's own (dlb_peer_put,
     dlb_embed_scatter_bwd_peer, dlb_embed_reduce_broadcast_peer, dlb_peer_wait); torch only allocates
     the memory and exchanges its handles.
 
@@ -48,7 +48,8 @@ class PeerExchange:
 
     CH_PUSHED, CH_DONE, CH_IDS, CH_SETUP = 0, 1, 2, 3
 
-    def __init__(self, dist, vocab, d, max_used_rows, device, tokens_per_rank=0, small_n=0, timeout_ms=2000):
+    def __init__(self, dist, vocab, d, max_used_rows, device, tokens_per_rank=0, small_n=0, timeout_ms=2000,
+                 narrow_rows=True):
         import torch
         import torch.distributed._symmetric_memory as symm
         from . import capi, ops
@@ -64,15 +65,17 @@ class PeerExchange:
         self.flags = symm.empty(capi.lib().dlb_peer_flags_bytes() // 4, dtype=torch.int32, device=device)
         self.small = symm.empty(max(self.world * small_n, 4), **f32)
         self.ids_all = symm.empty(max(self.world * tokens_per_rank, 4), dtype=torch.int32, device=device)
+        # rows that travel as bf16 (one token in all): [cap_rows * world][d] bf16 on every rank
+        self.stage = symm.empty(self.world * self.cap_rows * d if narrow_rows else 8, dtype=torch.bfloat16, device=device)
         self.flags.zero_()
-        buffers = (self.recv, self.grad, self.flags, self.small, self.ids_all)
+        buffers = (self.recv, self.grad, self.flags, self.small, self.ids_all, self.stage)
         self._handles = [symm.rendezvous(t, group) for t in buffers]
         ptrs = [[int(p) for p in h.buffer_ptrs] for h in self._handles]
-        self.recv_ptrs, self.grad_ptrs, self.flag_ptrs, self.small_ptrs, self.ids_ptrs = ptrs
+        self.recv_ptrs, self.grad_ptrs, self.flag_ptrs, self.small_ptrs, self.ids_ptrs, self.stage_ptrs = ptrs
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.group = ops.peer_group(self.world, self.rank, self.cap_rows, self.flag_ptrs, self.recv_ptrs,
                                     self.grad_ptrs, self.status, self.small_ptrs if small_n else None, small_n,
-                                    timeout_ms)
+                                    timeout_ms, self.stage_ptrs if narrow_rows else None)
         self.epoch = [0, 0, 0, 0]
         torch.cuda.synchronize(device)
         dist.barrier()  # every flag word is zero before anyone writes

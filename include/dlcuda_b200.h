@@ -71,6 +71,8 @@ DLB_API uint64_t dlb_launch_count(void);
  *   "ln_bwd_pipe_ctas_per_sm"    1 | 2
  *   "ln_bwd_pipe_rows_per_tile"  1 | 2 | 4 | 8
  *   "act_bwd_partial_rows"       upper bound of the partial rows of a fused bias gradient
+ *   "embed_push_period"          1..6: one CTA in this many of dlb_embed_scatter_bwd_peer's
+ *                                second kernel pushes rows to the peers, the others clear rows
  *   "embed_peer_phases"          1 only the local sums | 2 only the push of
  *                                dlb_embed_scatter_bwd_peer (for timing the halves; results are
  *                                incomplete while it is set)
@@ -338,14 +340,23 @@ DLB_API int dlb_checkpoint_unpack(int n_groups, float *const *h_params, const in
  * this rank has tokens for is final: it is stored straight into row v of every rank's grad
  * (a row with one token is read from dy itself).  A row several ranks share goes to the
  * receive area of the slot's owner (slot % n_ranks) at recv[my_rank][slot / n_ranks].  Rows
- * without local tokens send nothing.  The same kernel writes zeros into the rows of THIS
- * rank's grad that no rank uses, and, if `small` is given, copies its small_n floats to
+ * without local tokens send nothing.  With bf16 storage and staging areas given, a row whose
+ * ONE token in all lies on this rank travels narrow: the peers get the token's bf16 row (half
+ * the bytes) in stage[q][slot] and widen it themselves in the second call (0.0f + x is exact).
+ * clear_unused = 1: the same kernel writes zeros into the rows of THIS rank's grad that no
+ * rank uses.  clear_unused = 2: it clears only those of them that the PREVIOUS exchange wrote
+ * (the rank plan workspace remembers them across steps; dlb_embed_reduce_broadcast_peer records
+ * them): valid when nothing but these two calls writes the table between steps and the rank
+ * plan workspace was zero-filled once before its first use; without a matching record it clears
+ * everything, as 1 does.  clear_unused = 0: the caller clears (dlb_embed_expand_rows(what = 1)
+ * on any stream once the rank plan is ready).  If `small` is given, its small_n floats are copied to
  * small[q][my_rank] on every rank q.  When the last CTA has issued its stores the kernel
  * announces (signal_channel, signal_epoch).
  *
  * dlb_embed_reduce_broadcast_peer: waits (bounded by timeout_ms) until every rank has
  * announced (wait_channel, wait_epoch); for each slot it owns that several ranks share it
  * adds the partial rows in rank order and stores the sum into row v of every rank's grad;
+ * rows that arrived narrow are widened into this rank's own grad;
  * if small_out is given it receives the rank-order sum of the n_ranks small buffers (the
  * same bits on every rank).  Then it announces (signal_channel, signal_epoch); follow it
  * with dlb_peer_wait on that channel: after it every rank's table is complete.
@@ -367,17 +378,19 @@ typedef struct dlb_peer_group {
   float *recv[DLB_MAX_PEERS];
   float *grad[DLB_MAX_PEERS];
   float *small[DLB_MAX_PEERS];    /* may be NULL when small_n == 0 */
+  void *stage[DLB_MAX_PEERS];     /* optional (all ranks or none): [cap_rows * n_ranks][d] rows of the
+                                     STORAGE type, for rows that travel narrow (see below) */
   uint32_t *status;               /* this rank's device status word (zero before the first use) */
 } dlb_peer_group;
 
 DLB_API int dlb_embed_scatter_bwd_peer(const void *dy, const void *global_plan, int global_tokens,
                                        void *rank_plan, int tokens_per_rank,
                                        const dlb_peer_group *peers, const float *small, int max_rows,
-                                       int vocab, int d, int dtype, int signal_channel,
-                                       uint32_t signal_epoch, void *stream);
+                                       int clear_unused, int vocab, int d, int dtype,
+                                       int signal_channel, uint32_t signal_epoch, void *stream);
 DLB_API int dlb_embed_reduce_broadcast_peer(void *rank_plan, int tokens_per_rank,
                                             const dlb_peer_group *peers, float *small_out, int vocab,
-                                            int d, int wait_channel, uint32_t wait_epoch,
+                                            int d, int dtype, int wait_channel, uint32_t wait_epoch,
                                             int signal_channel, uint32_t signal_epoch, void *stream);
 
 /* Flags between the ranks' streams.  Every rank owns dlb_peer_flags_bytes() bytes of

@@ -18,7 +18,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
 sys.path.insert(0, str(Path(__file__).resolve().parent))
 
 from conftest import rel_err, rng_for, zipf_ids  # noqa: E402
-from dl_cuda_b200 import ops  # noqa: E402
+from dl_cuda_b200 import capi, ops  # noqa: E402
 from dl_cuda_b200.sharding import PeerExchange  # noqa: E402
 
 
@@ -36,6 +36,8 @@ def main():
         ids_all = torch.from_numpy(zipf_ids(rng_for(500 + step, 0), total, vocab).astype(np.int32)).to(dev)
         dy_all = torch.from_numpy(rng_for(500 + step, 1).standard_normal((total, d)).astype(np.float32)).to(dev)
         small_all = torch.from_numpy(rng_for(500 + step, 2).standard_normal((world, small_n)).astype(np.float32)).to(dev)
+        if step % 2:  # bf16 storage: rows with one token in all travel as bf16 and are widened by the receivers
+            dy_all = dy_all.to(torch.bfloat16)
         ids, dy = ids_all[rank * per_rank:(rank + 1) * per_rank].contiguous(), dy_all[rank * per_rank:(rank + 1) * per_rank].contiguous()
         small = small_all[rank].clone()
         table.fill_(float(3 + step))  # stale contents must vanish
@@ -48,8 +50,8 @@ def main():
         pushed, done = px.next_epoch(px.CH_PUSHED), px.next_epoch(px.CH_DONE)
         ops.embed_scatter_bwd_peer(dy, global_plan, total, rank_plan, per_rank, px.group, small, min(vocab, total), vocab,
                                    px.CH_PUSHED, pushed)
-        ops.embed_reduce_broadcast_peer(rank_plan, per_rank, px.group, small, vocab, d, px.CH_PUSHED, pushed,
-                                        px.CH_DONE, done)
+        ops.embed_reduce_broadcast_peer(rank_plan, per_rank, px.group, small, vocab, d, capi.dtype_of(dy), px.CH_PUSHED,
+                                        pushed, px.CH_DONE, done)
         px.wait(px.CH_DONE)
         torch.cuda.synchronize()
         assert px.timed_out() == 0, "a wait gave up or the receive area was too small"

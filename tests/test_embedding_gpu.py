@@ -269,7 +269,13 @@ def test_rank_plan_against_numpy():
         mine_stride = (min(vocab, per) * 4 + 255) // 256 * 64  # int32 words per [my rows] array
         my_route = ints[base + 8 * stride:base + 8 * stride + mine_rows.size]
         my_src = ints[base + 8 * stride + mine_stride:base + 8 * stride + mine_stride + mine_rows.size]
+        my_slot = ints[base + 8 * stride + 2 * mine_stride:base + 8 * stride + 2 * mine_stride + mine_rows.size]
         slot_of = {int(v): i for i, v in enumerate(used_rows)}
+        assert np.array_equal(used_rows[my_slot], mine_rows)
+        global_counts = np.bincount(ids[ids < vocab], minlength=vocab)
+        sources = np.array([bin(int(m)).count("1") for m in src_mask])
+        assert int(ints[7]) == int(((sources >= 2) & (np.arange(used) % ranks == r)).sum())
+        assert int(ints[8]) == int(((sources == 1) & (src_mask != (1 << r)) & (global_counts[used_rows] == 1)).sum())
         multi_seen = 0
         for k, v in enumerate(mine_rows):
             sole = src_mask[slot_of[int(v)]] == (1 << r)
@@ -295,20 +301,24 @@ def test_rank_plan_against_numpy():
 class EmulatedRanks:
     """Every rank's peer buffers on this one GPU (the "mappings" are the plain addresses)."""
 
-    def __init__(self, ranks, vocab, d, cap, small_n):
+    def __init__(self, ranks, vocab, d, cap, small_n, narrow=True):
         z = lambda k: torch.zeros(k, device="cuda")
         self.recv = [torch.full((ranks * cap * d,), 3.0, device="cuda") for _ in range(ranks)]  # needs no zeroing
         self.tables = [torch.full((vocab, d), 5.0, device="cuda") for _ in range(ranks)]
         self.flags = [torch.zeros(capi.lib().dlb_peer_flags_bytes() // 4, dtype=torch.int32, device="cuda") for _ in range(ranks)]
         self.small = [z(max(ranks * small_n, 4)) for _ in range(ranks)]
         self.status = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(ranks)]
+        # rows whose one token lies on another rank arrive here as bf16 and are widened by the receiver
+        self.stage = [torch.full((ranks * cap * d,), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(ranks)] \
+            if narrow else None
         addr = lambda ts: [t.data_ptr() for t in ts]
         self.groups = [ops.peer_group(ranks, r, cap, addr(self.flags), addr(self.recv), addr(self.tables), self.status[r],
-                                      addr(self.small) if small_n else None, small_n, timeout_ms=1000)
+                                      addr(self.small) if small_n else None, small_n, timeout_ms=1000,
+                                      stage=addr(self.stage) if narrow else None)
                        for r in range(ranks)]
 
 
-@pytest.mark.parametrize("storage", ["fp32", "bf16"])
+@pytest.mark.parametrize("storage", ["fp32", "bf16", "bf16-wide"])
 @pytest.mark.parametrize("vocab,d,n,ranks", [(50, 64, 300, 2), (1000, 256, 5000, 4), (32000, 512, 16384, 8),
                                              (97, 128, 4000, 3), (50, 64, 300, 1), (300, 4096, 2000, 16)])
 def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, storage):
@@ -318,8 +328,11 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
     table by that rank; a shared row goes to its owner, which adds the partial rows in rank order and
     stores the sum into every table; every rank zeroes the rows nobody uses in its own table; the small
     gradients of all ranks are summed in rank order.  Every table must equal the single-rank dense
-    gradient, twice in a row with stale tables and receive areas."""
-    dt = torch.bfloat16 if storage == "bf16" else torch.float32
+    gradient, twice in a row with stale tables and receive areas.  With bf16 storage a row whose one
+    token lies on another rank travels as bf16 through a staging area and is widened by the receiver
+    ("bf16-wide": without staging areas every row travels as fp32); the second round lets every rank
+    clear its unused rows with dlb_embed_expand_rows instead of inside the push kernel."""
+    dt = torch.float32 if storage == "fp32" else torch.bfloat16
     ids = zipf_ids(rng_for(71, 0), n, vocab)
     dy = dev(rng_for(71, 1).standard_normal((n, d)).astype(np.float32), dt)
     tids = dev(ids)
@@ -334,7 +347,8 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
     max_rows = min(vocab, n)
     cap = (max_rows + ranks - 1) // ranks
     small_n = 24
-    em = EmulatedRanks(ranks, vocab, d, cap, small_n)
+    em = EmulatedRanks(ranks, vocab, d, cap, small_n, narrow=storage != "bf16-wide")
+    code = capi.F32 if storage == "fp32" else capi.BF16
     small_in = [dev(rng_for(73, r).standard_normal(small_n).astype(np.float32)) for r in range(ranks)]
     small_want = small_in[0].clone()
     for r in range(1, ranks):
@@ -348,10 +362,12 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
         for r in range(ranks):
             per, lo, hi = shard(n, ranks, r)
             dy_r = dy[lo:hi].contiguous() if hi > lo else dy[:1].contiguous()
+            if attempt == 1:
+                ops.embed_expand_rows(None, plans[r], per, em.tables[r], what=1)
             ops.embed_scatter_bwd_peer(dy_r, global_plan, n, plans[r], per, em.groups[r], small_in[r], max_rows, vocab,
-                                       0, epoch)
+                                       0, epoch, clear_unused=attempt == 0)
         for r in range(ranks):
-            ops.embed_reduce_broadcast_peer(plans[r], per, em.groups[r], small_out[r], vocab, d, 0, epoch, 1, epoch)
+            ops.embed_reduce_broadcast_peer(plans[r], per, em.groups[r], small_out[r], vocab, d, code, 0, epoch, 1, epoch)
         for r in range(ranks):
             ops.peer_wait([f.data_ptr() for f in em.flags], r, 1, epoch, em.status[r], timeout_ms=1000)
         torch.cuda.synchronize()
@@ -367,6 +383,43 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
             t.fill_(7.0)
 
 
+@pytest.mark.parametrize("storage", ["fp32", "bf16"])
+def test_peer_exchange_clears_only_what_the_last_step_wrote(storage):
+    """clear_unused = 2 with the ranks emulated: three steps with different ids, nothing else touching the
+    tables in between.  Step 0 finds no record (the rank plan workspaces start zero-filled) and garbage in
+    the tables, so it clears everything; steps 1 and 2 clear only the rows of the step before them that
+    they do not write.  After every step every table equals the single-rank dense gradient."""
+    vocab, d, n, ranks, small_n = 3000, 256, 6000, 4, 0
+    dt = torch.float32 if storage == "fp32" else torch.bfloat16
+    code = capi.F32 if storage == "fp32" else capi.BF16
+    max_rows = min(vocab, n)
+    cap = (max_rows + ranks - 1) // ranks
+    em = EmulatedRanks(ranks, vocab, d, cap, small_n)
+    per = shard(n, ranks, 0)[0]
+    plans = [ops.embed_rank_plan_workspace(vocab, per, d, "cuda") for _ in range(ranks)]
+    for step in range(3):
+        ids = zipf_ids(rng_for(81 + step, 0), n, vocab)
+        dy = dev(rng_for(81 + step, 1).standard_normal((n, d)).astype(np.float32), dt)
+        tids = dev(ids)
+        dense = scatter(dy, tids, vocab)
+        global_plan = ops.embed_sort_tokens(tids, vocab, d)
+        for r in range(ranks):
+            ops.embed_rank_plan(global_plan, n, per, ranks, r, vocab, d, rank_plan=plans[r])
+        for r in range(ranks):
+            _, lo, hi = shard(n, ranks, r)
+            ops.embed_scatter_bwd_peer(dy[lo:hi].contiguous(), global_plan, n, plans[r], per, em.groups[r], None, max_rows,
+                                       vocab, 0, step + 1, clear_unused=2)
+        for r in range(ranks):
+            ops.embed_reduce_broadcast_peer(plans[r], per, em.groups[r], None, vocab, d, code, 0, step + 1, 1, step + 1)
+        torch.cuda.synchronize()
+        for r in range(ranks):
+            assert int(em.status[r].item()) == 0
+            assert rel_err(em.tables[r].cpu().numpy(), dense.cpu().numpy()) <= 3e-5, (step, r)
+            assert torch.equal(em.tables[r], em.tables[0])
+        used_now = np.unique(ids)
+        assert float(em.tables[0][torch.from_numpy(np.setdiff1d(np.arange(vocab), used_now)).cuda()].abs().sum()) == 0.0
+
+
 def test_peer_reduce_reports_a_receive_area_that_is_too_small():
     """cap_rows smaller than the rows an owner holds: the kernel drops those rows, raises bit 31 of the
     status word and touches nothing outside the receive area."""
@@ -379,7 +432,7 @@ def test_peer_reduce_reports_a_receive_area_that_is_too_small():
     per, lo, hi = shard(n, ranks, 0)
     plan = ops.embed_rank_plan(global_plan, n, per, ranks, 0, vocab, d)
     guard = em.recv[0].clone()
-    ops.embed_reduce_broadcast_peer(plan, per, em.groups[0], None, vocab, d, 3, 0, 1, 1)  # epoch 0: nothing to wait for
+    ops.embed_reduce_broadcast_peer(plan, per, em.groups[0], None, vocab, d, capi.F32, 3, 0, 1, 1)  # epoch 0: no wait
     torch.cuda.synchronize()
     assert (int(em.status[0].item()) & 0xffffffff) == 1 << 31
     assert torch.equal(em.recv[0], guard)
@@ -441,7 +494,7 @@ def test_peer_entry_points_reject_bad_arguments():
 
     def scatter_status(group, max_rows=50, channel=0):
         return lib.dlb_embed_scatter_bwd_peer(dy.data_ptr(), plan.data_ptr(), n, rank_plan.data_ptr(), 50,
-                                              ctypes.byref(group), None, max_rows, vocab, d, capi.F32, channel, 1, None)
+                                              ctypes.byref(group), None, max_rows, 1, vocab, d, capi.F32, channel, 1, None)
 
     def group(**changes):
         g = ops.peer_group(2, 0, 25, [f.data_ptr() for f in em.flags], [t.data_ptr() for t in em.recv],
@@ -461,9 +514,11 @@ def test_peer_entry_points_reject_bad_arguments():
     broken.recv[1] = None
     assert scatter_status(broken) == capi.ERR_INVALID_ARG                 # a null receive area
     assert lib.dlb_embed_reduce_broadcast_peer(rank_plan.data_ptr(), 50, ctypes.byref(group(my_rank=5)), None, vocab, d,
-                                               0, 1, 1, 1, None) == capi.ERR_INVALID_ARG
-    assert lib.dlb_embed_reduce_broadcast_peer(None, 50, ctypes.byref(group()), None, vocab, d, 0, 1, 1, 1, None) \
+                                               capi.F32, 0, 1, 1, 1, None) == capi.ERR_INVALID_ARG
+    assert lib.dlb_embed_reduce_broadcast_peer(None, 50, ctypes.byref(group()), None, vocab, d, capi.F32, 0, 1, 1, 1, None) \
         == capi.ERR_WORKSPACE
+    assert lib.dlb_embed_reduce_broadcast_peer(rank_plan.data_ptr(), 50, ctypes.byref(group()), None, vocab, d, 7, 0, 1, 1,
+                                               1, None) == capi.ERR_INVALID_ARG      # unknown dtype
     assert lib.dlb_embed_rank_plan(plan.data_ptr(), n, 10, 2, 0, rank_plan.data_ptr(), rank_plan.numel(), vocab, d, None) \
         == capi.ERR_INVALID_ARG                                           # 2 ranks of 10 tokens do not cover 100
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
