@@ -165,7 +165,8 @@ class Chain:
     OPS = ["sort_tokens", "embed_gather_pe", "ln1_fwd", "relu_fwd", "ln2_fwd",
            "ln2_bwd", "relu_bwd", "ln1_bwd", "embed_scatter", "allreduce"]
 
-    def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist, exchange="peer", clear="incremental"):
+    def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist, exchange="peer", clear="incremental",
+                 split_push=True):
         from dl_cuda_b200 import capi, ops
         global allreduce_param_grads
         from dl_cuda_b200.sharding import allreduce_param_grads
@@ -235,7 +236,8 @@ class Chain:
             self.ws_global = ops.embed_workspace(Tg, V, D, dev)
             self.rank_plan = ops.embed_rank_plan_workspace(V, T, D, dev)
             self.h_used = torch.zeros(1, dtype=torch.int32).pin_memory()
-            self.bwd_done = torch.cuda.Event()
+            self.bwd_done, self.sums_done = torch.cuda.Event(), torch.cuda.Event()
+            self.split_push = split_push
             # Table-gradient exchange: the library's fused scatter-add + peer-memory exchange, or (asked for, or when
             # symmetric memory cannot be set up) NCCL's all-reduce of the compacted rows.
             self.peer = None
@@ -376,8 +378,21 @@ class Chain:
             # from upper bounds, the kernels read the exact row counts, zero the rows nobody uses, announce their
             # stores and wait for the other ranks themselves.
             pushed, done = px.next_epoch(px.CH_PUSHED), px.next_epoch(px.CH_DONE)
-            ops.embed_scatter_bwd_peer(self.dx1, self.ws_global, self.Tg, self.rank_plan, T, px.group, self.small_grads,
-                                       min(V, self.Tg), V, px.CH_PUSHED, pushed, clear_unused=self.clear_mode, stream=st)
+            scatter = lambda part, stream: ops.embed_scatter_bwd_peer(
+                self.dx1, self.ws_global, self.Tg, self.rank_plan, T, px.group, self.small_grads, min(V, self.Tg), V,
+                px.CH_PUSHED, pushed, clear_unused=self.clear_mode, part=part, stream=stream)
+            if marks is None and self.split_push:
+                # The rows with one token need no sum: they go out (with the clearing) while the second stream
+                # adds up the rows with several tokens; those follow, and with them the announcement.
+                self.bwd_done.record(main)
+                self.side.wait_event(self.bwd_done)
+                scatter(1, self.side.cuda_stream)
+                self.sums_done.record(self.side)
+                scatter(2, st)
+                main.wait_event(self.sums_done)
+                scatter(3, st)
+            else:
+                scatter(0, st)
             mark()
             ops.embed_reduce_broadcast_peer(self.rank_plan, T, px.group, self.small_grads, V, D, code, px.CH_PUSHED,
                                             pushed, px.CH_DONE, done, stream=st)
@@ -1063,6 +1078,8 @@ def main():
                     help="N > 1, peer exchange: the table rows no rank uses are cleared inside the push kernel, only "
                          "those the previous step wrote (incremental) or all of them (fused), or all of them early on "
                          "the second stream beside the compute kernels")
+    ap.add_argument("--no-split-push", action="store_true",
+                    help="N > 1, peer exchange: sums and pushes in stream order instead of overlapped on two streams")
     ap.add_argument("--skip-kernels", action="store_true", help="skip the per-kernel fp32 sweep")
     ap.add_argument("--skip-cpu", action="store_true",
                     help="skip the baseline legs (the single-threaded host loops and the reference-kernel columns)")
@@ -1089,7 +1106,7 @@ def main():
     _, tokens_local = shard_rows(args.tokens, n, dist.rank, SEQ if args.tokens % (SEQ * n) == 0 else 1)
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     chain = Chain(tokens_local, SEQ, D_MODEL, D_FF, VOCAB, dtype, seed=1234 + dist.rank, dist=dist,
-                  exchange=args.exchange, clear=args.clear)
+                  exchange=args.exchange, clear=args.clear, split_push=not args.no_split_push)
     lib = chain.lib
 
     parity = None

@@ -57,7 +57,7 @@ SIGNATURES = {
     "dlb_checkpoint_body_bytes": (_sz, [_i, _p]),
     "dlb_checkpoint_pack": (_i, [_i, _p, _p, _p, _sz, _p]),
     "dlb_checkpoint_unpack": (_i, [_i, _p, _p, _p, _sz, _p]),
-    "dlb_embed_scatter_bwd_peer": (_i, [_p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, C.c_uint32, _p]),
+    "dlb_embed_scatter_bwd_peer": (_i, [_p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, C.c_uint32, _p]),
     "dlb_embed_reduce_broadcast_peer": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, C.c_uint32, _i, C.c_uint32, _p]),
     "dlb_peer_flags_bytes": (_sz, []),
     "dlb_peer_barrier": (_i, [_p, _i, _i, _i, C.c_uint32, _i, _p, _p]),

@@ -375,6 +375,7 @@ struct PushArgs {
   const int32_t *slot_map;
   int d, vocab;
   int skip;    // measurements only: 1 no pushes, 2 no zero rows
+  int which;   // rows pushed: 1 those with one token (read from dy), 2 the summed ones, 3 both
   int period;  // one CTA in `period` pushes
 };
 
@@ -424,8 +425,9 @@ push_rows_kernel(const T *dy, const __grid_constant__ PushArgs a, const __grid_c
       const bool everywhere = route < 0;
       size_t off = 0;
       float *single = nullptr;
-      bool ok = true;
-      if (everywhere) {
+      bool ok = (a.which & (src >= 0 ? 1 : 2)) != 0;
+      if (!ok) {
+      } else if (everywhere) {
         off = static_cast<size_t>(static_cast<uint32_t>(route) & 0x7fffffffu) * d;
       } else {
         const int j = route / pr.n;
@@ -793,8 +795,10 @@ static void fill_signal(PeerSignal *s, const dlb_peer_group *g, int32_t *done, i
 
 extern "C" int dlb_embed_scatter_bwd_peer(const void *dy, const void *global_plan, int global_tokens, void *rank_plan,
                                           int tokens_per_rank, const dlb_peer_group *peers, const float *small,
-                                          int max_rows, int clear_unused, int vocab, int d, int dtype,
+                                          int max_rows, int clear_unused, int part, int vocab, int d, int dtype,
                                           int signal_channel, uint32_t signal_epoch, void *stream) {
+  DLB_REQUIRE(part >= 0 && part <= 3, DLB_ERR_INVALID_ARG, "embed_scatter_bwd_peer: part=%d (0 all, 1 sums, 2 first push, "
+              "3 second push)", part);
   DLB_REQUIRE(shape_ok(global_tokens, vocab, d) && tokens_per_rank > 0 && max_rows >= 0 && max_rows <= vocab,
               DLB_ERR_INVALID_ARG, "embed_scatter_bwd_peer: tokens=%d tokens_per_rank=%d vocab=%d d=%d max_rows=%d",
               global_tokens, tokens_per_rank, vocab, d, max_rows);
@@ -846,22 +850,25 @@ extern "C" int dlb_embed_scatter_bwd_peer(const void *dy, const void *global_pla
   ScatterArgs a = rank_scatter_args(pg, r, tokens_per_rank, peers->my_rank, multi_bound, d, false);
   a.out = r.my_rows;
   const int phases = get_option("embed_peer_phases");  // measurements only: 1 sums, 2 push
-  if (phases == 0 || phases == 1) {
+  if ((part == 0 || part == 1) && (phases == 0 || phases == 1)) {
     const int row_ctas = 8 * sm_count();
     const int rc = dtype == DLB_F32 ? launch_scatter_rows<float>(dy, a, r.max_sub, row_ctas, st)
                                     : launch_scatter_rows<__nv_bfloat16>(dy, a, r.max_sub, row_ctas, st);
     if (rc != DLB_OK) return rc;
   }
-  if (phases == 1) return DLB_OK;
+  if (phases == 1 || part == 1) return DLB_OK;
   // 2. every row out to the tables / the owners, the small gradients along with them, zeros into the
-  //    rows nobody uses, then the flag.
+  //    rows nobody uses, then the flag.  In parts: first the rows with one token (they need no sum),
+  //    the clearing and the small gradients; then the summed rows and the flag.
   PushArgs pa{};
   pa.my_rows = r.my_rows;
   pa.my_route = r.my_route;
   pa.my_src = r.my_src;
   pa.my_slot = r.my_slot;
-  pa.clear = clear_unused;
+  pa.which = part == 2 ? 1 : (part == 3 ? 2 : 3);
+  pa.clear = part == 3 ? 0 : clear_unused;
   pa.history = r.history;
+  if (part == 3) push.src = nullptr;  // went out with the first push
   for (int q = 0; q < peers->n_ranks; q++) pa.stage[q] = peers->stage[0] != nullptr ? peers->stage[q] : nullptr;
   pa.n_mine = r.header + kHdrMine;
   pa.slot_map = r.slot_map;
@@ -871,7 +878,7 @@ extern "C" int dlb_embed_scatter_bwd_peer(const void *dy, const void *global_pla
   pa.period = get_option("embed_push_period") > 0 ? get_option("embed_push_period") : kPushPeriod;
   if (!pa.clear) pa.period = 1;  // nothing to clear: every CTA pushes
   PeerSignal sig{};
-  fill_signal(&sig, peers, r.header + kHdrDonePush, signal_channel, signal_epoch);
+  if (part != 2) fill_signal(&sig, peers, r.header + kHdrDonePush, signal_channel, signal_epoch);  // the first push of two is silent
   const int grid = kPushPeriod * sm_count();
   if (dtype == DLB_F32)
     launch_pdl(push_rows_kernel<float>, grid, kBlock, 0, st, static_cast<const float *>(dy), pa, route, push, sig);

@@ -331,12 +331,13 @@ def peer_group(n_ranks, my_rank, cap_rows, flags, recv, grad, status, small=None
 
 
 def embed_scatter_bwd_peer(dy, global_plan, global_tokens, rank_plan, tokens_per_rank, group, small, max_rows, vocab,
-                           channel, epoch, clear_unused=1, stream=None):
+                           channel, epoch, clear_unused=1, part=0, stream=None):
+    """part: 0 everything in stream order; 1 the sums, 2 the first push, 3 the second push (see the header)."""
     import ctypes
     d = dy.shape[1]
     check(capi.lib().dlb_embed_scatter_bwd_peer(ptr(dy), ptr(global_plan), global_tokens, ptr(rank_plan), tokens_per_rank,
-                                                ctypes.byref(group), ptr(small), max_rows, int(clear_unused), vocab, d,
-                                                dtype_of(dy), channel, epoch,
+                                                ctypes.byref(group), ptr(small), max_rows, int(clear_unused), part, vocab,
+                                                d, dtype_of(dy), channel, epoch,
                                                 current_stream() if stream is None else stream))
 
 

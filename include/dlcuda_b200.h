@@ -351,7 +351,11 @@ DLB_API int dlb_checkpoint_unpack(int n_groups, float *const *h_params, const in
  * everything, as 1 does.  clear_unused = 0: the caller clears (dlb_embed_expand_rows(what = 1)
  * on any stream once the rank plan is ready).  If `small` is given, its small_n floats are copied to
  * small[q][my_rank] on every rank q.  When the last CTA has issued its stores the kernel
- * announces (signal_channel, signal_epoch).
+ * announces (signal_channel, signal_epoch).  part = 0 does all of this in stream order.  To
+ * overlap the sums with the pushes that do not need them, call it three times with the same
+ * arguments: part = 1 (the sums alone) on a second stream, part = 2 (rows with one token, the
+ * clearing, the small gradients; announces nothing) on the first, and, once part 1 has
+ * finished (an event), part = 3 (the summed rows, then the announcement) on the first.
  *
  * dlb_embed_reduce_broadcast_peer: waits (bounded by timeout_ms) until every rank has
  * announced (wait_channel, wait_epoch); for each slot it owns that several ranks share it
@@ -386,7 +390,7 @@ typedef struct dlb_peer_group {
 DLB_API int dlb_embed_scatter_bwd_peer(const void *dy, const void *global_plan, int global_tokens,
                                        void *rank_plan, int tokens_per_rank,
                                        const dlb_peer_group *peers, const float *small, int max_rows,
-                                       int clear_unused, int vocab, int d, int dtype,
+                                       int clear_unused, int part, int vocab, int d, int dtype,
                                        int signal_channel, uint32_t signal_epoch, void *stream);
 DLB_API int dlb_embed_reduce_broadcast_peer(void *rank_plan, int tokens_per_rank,
                                             const dlb_peer_group *peers, float *small_out, int vocab,

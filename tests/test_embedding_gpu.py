@@ -364,8 +364,10 @@ def test_peer_exchange_with_the_ranks_emulated_on_one_gpu(vocab, d, n, ranks, st
             dy_r = dy[lo:hi].contiguous() if hi > lo else dy[:1].contiguous()
             if attempt == 1:
                 ops.embed_expand_rows(None, plans[r], per, em.tables[r], what=1)
-            ops.embed_scatter_bwd_peer(dy_r, global_plan, n, plans[r], per, em.groups[r], small_in[r], max_rows, vocab,
-                                       0, epoch, clear_unused=attempt == 0)
+            # first round in one call; second round in the three parts a caller overlaps on two streams
+            for part in ((0,) if attempt == 0 else (1, 2, 3)):
+                ops.embed_scatter_bwd_peer(dy_r, global_plan, n, plans[r], per, em.groups[r], small_in[r], max_rows, vocab,
+                                           0, epoch, clear_unused=int(attempt == 0), part=part)
         for r in range(ranks):
             ops.embed_reduce_broadcast_peer(plans[r], per, em.groups[r], small_out[r], vocab, d, code, 0, epoch, 1, epoch)
         for r in range(ranks):
@@ -494,7 +496,7 @@ def test_peer_entry_points_reject_bad_arguments():
 
     def scatter_status(group, max_rows=50, channel=0):
         return lib.dlb_embed_scatter_bwd_peer(dy.data_ptr(), plan.data_ptr(), n, rank_plan.data_ptr(), 50,
-                                              ctypes.byref(group), None, max_rows, 1, vocab, d, capi.F32, channel, 1, None)
+                                              ctypes.byref(group), None, max_rows, 1, 0, vocab, d, capi.F32, channel, 1, None)
 
     def group(**changes):
         g = ops.peer_group(2, 0, 25, [f.data_ptr() for f in em.flags], [t.data_ptr() for t in em.recv],
