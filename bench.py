@@ -1084,9 +1084,16 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true",
                     help="skip the baseline legs (the single-threaded host loops and the reference-kernel columns)")
     ap.add_argument("--skip-fp32-chain", action="store_true", help="N=1: skip the fp32-storage run of the chain")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="kernel-variant override for A/B measurements (dlb_set_option), may be repeated")
     ap.add_argument("--case", default=None, help="run one small kernel case (for ncu) and exit: " + ", ".join(PROFILE_CASES))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.option and args.impl == "native":
+        from dl_cuda_b200 import capi
+        for item in args.option:
+            name, value = item.split("=", 1)
+            capi.set_option(name, int(value))
     if args.case:
         return profile_case(args.case)
 
@@ -1179,6 +1186,7 @@ def main():
         "value_min": args.tokens / (step_ms[-1] / 1e3), "value_max": args.tokens / (step_ms[0] / 1e3),
         "repeats": REPEATS, "ms_per_step_all": [round(v, 4) for v in step_ms],
         "timing": f"median of {REPEATS} timed regions of {args.steps} steps each (gpu_launches: per region)",
+        "options": args.option,
         "config": {"workload": "transformer-block non-GEMM chain fwd+bwd (embed+PE, LN+residual x2, bias+ReLU, "
                                "scatter-add), token-sharded",
                    "batch": BATCH, "seq_len": SEQ, "d_model": D_MODEL, "d_ff": D_FF, "vocab": VOCAB,

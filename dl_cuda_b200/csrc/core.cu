@@ -42,6 +42,8 @@ struct Option {
 };
 Option g_options[] = {
     {"gather_rows_in_flight", {0}},     // 4 or 8 table rows loaded per thread before the first store
+    {"gather_variant", {0}},            // 2: the bulk-copy (TMA) pipeline instead of rows in registers
+    {"gather_bulk_ctas_per_sm", {0}},   // 1: one CTA per SM with a deeper ring (default 2)
     {"ln_bwd_pipe", {0}},               // 1: never the bulk-copy pipeline, 2: whenever the shape allows
     {"ln_bwd_pipe_threads", {0}},       // column threads per CTA: 128, 256 or 512
     {"ln_bwd_pipe_ctas_per_sm", {0}},   // 1 or 2

@@ -196,23 +196,9 @@ __device__ __forceinline__ void cta_scan3_u64(unsigned long long (&v)[3], unsign
 //   A {used rows (bits 0..19), long rows (20..39), sub-segments (40..63)}
 //   B {my rows (0..19), multi rows (20..39)}
 //   C {owned shared slots (0..19), narrow slots (20..39)}   -- needs the slot, so it trails A by a chunk
-// The inputs of the next chunk are fetched before the scans of the current one.
-struct NumberIn {
-  int seg0, seg1, b, e;
-  uint32_t mask;
-};
-
-__device__ __forceinline__ NumberIn number_load(const int32_t *seg_global, const RankPlan &r, int v, int vocab) {
-  NumberIn in{0, 0, 0, 0, 0u};
-  if (v < vocab) {
-    in.seg0 = ld_co(seg_global + v);
-    in.seg1 = ld_co(seg_global + v + 1);
-    in.b = ld_co(r.tmp_begin + v);
-    in.e = ld_co(r.tmp_end + v);
-    in.mask = ld_co(r.tmp_mask + v);
-  }
-  return in;
-}
+// A thread takes kNumberRows consecutive rows per step and the CTA scans the threads' sums, so the
+// barriers of a scan are paid once per 4096 rows.
+constexpr int kNumberRows = 4;  // table rows per thread and step: 4096 rows per step of the CTA
 
 __global__ void __launch_bounds__(1024)
 rank_plan_number_kernel(const int32_t *seg_global, const int32_t *vals, int tok_offset, int me, int n_ranks, int vocab,
@@ -220,59 +206,91 @@ rank_plan_number_kernel(const int32_t *seg_global, const int32_t *vals, int tok_
   pdl_prologue();
   __shared__ unsigned long long tmp[3][33];
   unsigned long long base[3] = {0, 0, 0};
-  NumberIn next = number_load(seg_global, r, threadIdx.x, vocab);
-  for (int v0 = 0; v0 < vocab; v0 += 1024) {
-    const int v = v0 + threadIdx.x;
-    const NumberIn in = next;
-    next = number_load(seg_global, r, v + 1024, vocab);
-    const bool used = v < vocab && in.seg1 > in.seg0;
-    const int cnt = used ? in.e - in.b : 0;
-    const bool is_long = cnt > kSubLen;
-    const unsigned long long nsub = is_long ? static_cast<unsigned long long>((cnt + kSubLen - 1) / kSubLen) : 0ull;
-    // C's flags need the slot number, which scan A yields: a first pass gives A and B, then C follows.
-    unsigned long long val[3], total[3];
-    val[0] = (used ? 1ull : 0ull) | (is_long ? (1ull << 20) : 0ull) | (nsub << 40);
-    val[1] = (cnt > 0 ? 1ull : 0ull) | (cnt > 1 ? (1ull << 20) : 0ull);
-    val[2] = 0ull;
+  for (int v0 = 0; v0 < vocab; v0 += 1024 * kNumberRows) {
+    const int first = v0 + threadIdx.x * kNumberRows;
+    int seg[kNumberRows + 1], b[kNumberRows], e[kNumberRows];
+    uint32_t mask[kNumberRows];
+#pragma unroll
+    for (int i = 0; i <= kNumberRows; i++) seg[i] = first + i <= vocab ? ld_co(seg_global + first + i) : 0;
+#pragma unroll
+    for (int i = 0; i < kNumberRows; i++) {
+      const int v = first + i;
+      b[i] = v < vocab ? ld_co(r.tmp_begin + v) : 0;
+      e[i] = v < vocab ? ld_co(r.tmp_end + v) : 0;
+      mask[i] = v < vocab ? ld_co(r.tmp_mask + v) : 0u;
+    }
+    // A: {used rows (bits 0..19), long rows (20..39), sub-segments (40..63)}; B: {my rows, multi rows}
+    unsigned long long in_a[kNumberRows], in_b[kNumberRows];
+    unsigned long long val[3] = {0ull, 0ull, 0ull}, total[3];
+#pragma unroll
+    for (int i = 0; i < kNumberRows; i++) {
+      const bool used = first + i < vocab && seg[i + 1] > seg[i];
+      const int cnt = used ? e[i] - b[i] : 0;
+      const bool is_long = cnt > kSubLen;
+      const unsigned long long nsub = is_long ? static_cast<unsigned long long>((cnt + kSubLen - 1) / kSubLen) : 0ull;
+      in_a[i] = (used ? 1ull : 0ull) | (is_long ? (1ull << 20) : 0ull) | (nsub << 40);
+      in_b[i] = (cnt > 0 ? 1ull : 0ull) | (cnt > 1 ? (1ull << 20) : 0ull);
+      val[0] += in_a[i];
+      val[1] += in_b[i];
+    }
     cta_scan3_u64(val, tmp, total);
-    const unsigned long long at_a = base[0] + val[0], at_b = base[1] + val[1];
-    const int slot = static_cast<int>(at_a & 0xfffffull);
-    const int sources = __popc(in.mask);
-    const bool own_shared = used && sources >= 2 && slot % n_ranks == me;
-    const bool narrow = used && sources == 1 && in.mask != (1u << me) && in.seg1 - in.seg0 == 1;
+    unsigned long long at_a = base[0] + val[0], at_b = base[1] + val[1];
     base[0] += total[0];
     base[1] += total[1];
-    unsigned long long val_c[3] = {(own_shared ? 1ull : 0ull) | (narrow ? (1ull << 20) : 0ull), 0ull, 0ull}, total_c[3];
+    // C needs the slot numbers A has just produced: {shared slots this rank owns, narrow slots}
+    unsigned long long in_c[kNumberRows], pre_a[kNumberRows], pre_b[kNumberRows];
+    unsigned long long val_c[3] = {0ull, 0ull, 0ull}, total_c[3];
+#pragma unroll
+    for (int i = 0; i < kNumberRows; i++) {
+      pre_a[i] = at_a;
+      pre_b[i] = at_b;
+      const bool used = (in_a[i] & 1ull) != 0;
+      const int slot = static_cast<int>(at_a & 0xfffffull);
+      const int sources = __popc(mask[i]);
+      const bool own_shared = used && sources >= 2 && slot % n_ranks == me;
+      const bool narrow = used && sources == 1 && mask[i] != (1u << me) && seg[i + 1] - seg[i] == 1;
+      in_c[i] = (own_shared ? 1ull : 0ull) | (narrow ? (1ull << 20) : 0ull);
+      val_c[0] += in_c[i];
+      at_a += in_a[i];
+      at_b += in_b[i];
+    }
     cta_scan3_u64(val_c, tmp, total_c);
-    const unsigned long long at_c = base[2] + val_c[0];
+    unsigned long long at_c = base[2] + val_c[0];
     base[2] += total_c[0];
-    if (v < vocab) {
+#pragma unroll
+    for (int i = 0; i < kNumberRows; i++) {
+      const int v = first + i;
+      if (v >= vocab) continue;
+      const bool used = (in_a[i] & 1ull) != 0;
+      const int slot = static_cast<int>(pre_a[i] & 0xfffffull);
       r.slot_map[v] = used ? slot : -1;
       if (used) {
+        const int cnt = e[i] - b[i];
         r.used_rows[slot] = v;
-        r.row_begin[slot] = in.b;
-        r.row_end[slot] = in.e;
-        r.src_mask[slot] = in.mask;
-        if (own_shared) r.own_shared[at_c & 0xfffffull] = slot;
-        if (narrow) r.narrow[(at_c >> 20) & 0xfffffull] = slot;
+        r.row_begin[slot] = b[i];
+        r.row_end[slot] = e[i];
+        r.src_mask[slot] = mask[i];
+        if (in_c[i] & 1ull) r.own_shared[at_c & 0xfffffull] = slot;
+        if (in_c[i] >> 20) r.narrow[(at_c >> 20) & 0xfffffull] = slot;
         if (cnt > 0) {
-          const int k = static_cast<int>(at_b & 0xfffffull);
-          const int m = static_cast<int>((at_b >> 20) & 0xfffffull);
-          r.my_route[k] = in.mask == (1u << me) ? static_cast<int32_t>(static_cast<uint32_t>(v) | 0x80000000u) : slot;
-          r.my_src[k] = cnt == 1 ? ld_co(vals + in.b) - tok_offset : -(m + 1);
+          const int k = static_cast<int>(pre_b[i] & 0xfffffull);
+          const int m = static_cast<int>((pre_b[i] >> 20) & 0xfffffull);
+          r.my_route[k] = mask[i] == (1u << me) ? static_cast<int32_t>(static_cast<uint32_t>(v) | 0x80000000u) : slot;
+          r.my_src[k] = cnt == 1 ? ld_co(vals + b[i]) - tok_offset : -(m + 1);
           r.my_slot[k] = slot;
           if (cnt > 1) {
-            r.multi_begin[m] = in.b;
-            r.multi_end[m] = in.e;
+            r.multi_begin[m] = b[i];
+            r.multi_end[m] = e[i];
             r.multi_slot[m] = slot;
           }
-          if (is_long) {
-            const int li = static_cast<int>((at_a >> 20) & 0xfffffull);
+          if (cnt > kSubLen) {
+            const int li = static_cast<int>((pre_a[i] >> 20) & 0xfffffull);
             r.long_row[li] = m;
-            r.long_first[li] = static_cast<int>(at_a >> 40);
+            r.long_first[li] = static_cast<int>(pre_a[i] >> 40);
           }
         }
       }
+      at_c += in_c[i];
     }
   }
   if (threadIdx.x == 0) {

@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "embed_plan_cluster.cuh"
 #include "embed_scatter.cuh"
+#include "tma.cuh"
 
 namespace dlb {
 namespace {
@@ -96,6 +97,163 @@ embed_gather_kernel(const T *table, const int32_t *ids,
       }
     }
   }
+}
+
+// The gather as a bulk-copy (TMA) pipeline, the alternative form of embed_gather_kernel
+// (dlb_set_option "gather_variant" = 2).  A CTA takes positions s = cta, cta + grid, ...; the grid is four
+// times what fits the GPU, so that CTAs are handed out as SMs free up (a grid of exactly the resident
+// CTAs lost 100 us per step whenever the plan kernel of the second stream held a few SMs at launch).
+//   producer warp   lane l fetches the id of the l-th token that shares the position, lane 0 then
+//                   streams the positional-encoding row and the table rows of those tokens into a
+//                   ring of shared-memory stages with cp.async.bulk (completion on mbarriers);
+//   consumer warps  keep the position's PE values of their columns in registers, and per row read
+//                   their vectors from the stage, add, and store to the output (coalesced 16-byte
+//                   stores); a stage is handed back once every consumer warp has read it.
+// No thread holds a table row in registers while it is in flight, and the id -> row dependency is the
+// producer's alone, so the bytes in flight are set by the ring depth.
+constexpr int kGatherConsumers = 256;
+constexpr int kGatherThreads = kGatherConsumers + 32;
+
+struct GatherBulkLayout {
+  int stages;
+  unsigned row_bytes, pe_bytes, pe_off, bar_off, total;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kGatherThreads)
+embed_gather_bulk_kernel(const T *table, const int32_t *ids, const float *pe, T *__restrict__ out, int num_tokens,
+                         int vocab, int d, int stride_s, GatherBulkLayout L, unsigned int *timeouts) {
+  pdl_prologue();
+  using S = Store<T>;
+  constexpr int E = S::kPerVec;
+  constexpr int kMaxVec = 4;  // column vectors per consumer thread (rows of up to 1024 vectors)
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char *ring = smem_raw;
+  float *pe_buf = reinterpret_cast<float *>(smem_raw + L.pe_off);       // two rows
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + L.bar_off);  // [stages]
+  uint64_t *empty = full + 16;                                          // [stages]
+  uint64_t *pe_full = empty + 16;                                       // [2]
+  uint64_t *pe_empty = pe_full + 2;                                     // [2]
+  volatile int *dead = reinterpret_cast<volatile int *>(pe_empty + 2);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int stages = L.stages;
+  const int ncv = d / E;
+  if (tid == 0) {
+    for (int i = 0; i < stages; i++) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], kGatherConsumers / 32);
+    }
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&pe_full[i], 1);
+      mbar_init(&pe_empty[i], kGatherConsumers / 32);
+    }
+    *dead = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kGatherConsumers / 32) {
+    // ---------------------------------------------------------------- producer
+    int it = 0, pit = 0;
+    for (int s = blockIdx.x; s < stride_s; s += gridDim.x, ++pit) {
+      const int nb = (num_tokens - s + stride_s - 1) / stride_s;  // tokens that share position s
+      if (lane == 0) {
+        mbar_wait(&pe_empty[pit & 1], ((pit >> 1) & 1) ^ 1, dead, timeouts);
+        mbar_expect_tx(&pe_full[pit & 1], L.pe_bytes);
+        bulk_load(pe_buf + static_cast<size_t>(pit & 1) * d, pe + static_cast<size_t>(s) * d, L.pe_bytes, &pe_full[pit & 1]);
+      }
+      for (int b0 = 0; b0 < nb; b0 += 32) {
+        int id = 0;
+        if (b0 + lane < nb) {
+          id = ld_co(ids + s + static_cast<size_t>(b0 + lane) * stride_s);
+          id = max(0, min(id, vocab - 1));  // out-of-range ids cannot leave the table
+        }
+        const int here = min(32, nb - b0);
+        for (int b = 0; b < here; b++, ++it) {
+          const int row = __shfl_sync(0xffffffffu, id, b);
+          if (lane == 0) {
+            const int st = it % stages;
+            mbar_wait(&empty[st], ((it / stages) & 1) ^ 1, dead, timeouts);
+            mbar_expect_tx(&full[st], L.row_bytes);
+            bulk_load(ring + static_cast<size_t>(st) * L.row_bytes, table + static_cast<size_t>(row) * d, L.row_bytes,
+                      &full[st]);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers
+  int it = 0, pit = 0;
+  for (int s = blockIdx.x; s < stride_s; s += gridDim.x, ++pit) {
+    const int nb = (num_tokens - s + stride_s - 1) / stride_s;
+    float pv[kMaxVec][E];
+    mbar_wait(&pe_full[pit & 1], (pit >> 1) & 1, dead, timeouts);
+    {
+      const float *prow = pe_buf + static_cast<size_t>(pit & 1) * d;
+#pragma unroll
+      for (int k = 0; k < kMaxVec; k++) {
+        const int cv = tid + k * kGatherConsumers;
+#pragma unroll
+        for (int q = 0; q < E / 4; q++) {
+          float4 p4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (cv < ncv) p4 = *reinterpret_cast<const float4 *>(prow + static_cast<size_t>(cv) * E + 4 * q);
+          pv[k][4 * q] = p4.x; pv[k][4 * q + 1] = p4.y; pv[k][4 * q + 2] = p4.z; pv[k][4 * q + 3] = p4.w;
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&pe_empty[pit & 1]);  // the values are in registers now
+    for (int b = 0; b < nb; b++, ++it) {
+      const int st = it % stages;
+      mbar_wait(&full[st], (it / stages) & 1, dead, timeouts);
+      const unsigned char *row = ring + static_cast<size_t>(st) * L.row_bytes;
+      const size_t t = static_cast<size_t>(s) + static_cast<size_t>(b) * stride_s;
+      uint4 raw[kMaxVec];
+#pragma unroll
+      for (int k = 0; k < kMaxVec; k++) {
+        const int cv = tid + k * kGatherConsumers;
+        if (cv < ncv) raw[k] = lds128(row + static_cast<size_t>(cv) * 16);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[st]);  // this warp's reads of the stage have returned
+#pragma unroll
+      for (int k = 0; k < kMaxVec; k++) {
+        const int cv = tid + k * kGatherConsumers;
+        if (cv < ncv) {
+          float v[E];
+          S::unpack(raw[k], v);
+#pragma unroll
+          for (int e = 0; e < E; e++) v[e] = v[e] + pv[k][e];
+          st_stream(out + t * d + static_cast<size_t>(cv) * E, S::pack(v));
+        }
+      }
+    }
+  }
+  // After a wait gave up, copies may still be landing in this CTA's shared memory.
+  if (*dead) {
+    for (int i = 0; i < 1000; i++) __nanosleep(1000);
+  }
+}
+
+// Ring depth and shared-memory layout, or stages == 0 when the shape does not fit this kernel.
+template <typename T>
+GatherBulkLayout gather_bulk_layout(int d, int ctas_per_sm) {
+  constexpr int E = Store<T>::kPerVec;
+  GatherBulkLayout L{};
+  if (d % E != 0 || d / E > 4 * kGatherConsumers) return L;
+  L.row_bytes = static_cast<unsigned>(d * sizeof(T));
+  L.pe_bytes = static_cast<unsigned>(d * sizeof(float));
+  const size_t budget = (216 * 1024) / ctas_per_sm - 1024;
+  const size_t fixed = 2 * static_cast<size_t>(L.pe_bytes) + 512;
+  if (fixed + 2 * static_cast<size_t>(L.row_bytes) > budget) return L;
+  size_t stages = (budget - fixed) / L.row_bytes;
+  L.stages = static_cast<int>(stages > 16 ? 16 : stages);
+  L.pe_off = L.row_bytes * L.stages;
+  L.bar_off = L.pe_off + 2 * L.pe_bytes;
+  L.total = L.bar_off + 512;
+  return L;
 }
 
 template <typename T>
@@ -364,6 +522,21 @@ int gather_typed(const void *table, const int32_t *ids, const float *pe, int seq
                 "embed_gather_fwd: seq_len=%d exceeds %d positions", seq_len, 65535 * bs.ty);
     DLB_REQUIRE(static_cast<int64_t>(num_tokens) + 16LL * stride_s < INT32_MAX, DLB_ERR_UNSUPPORTED,
                 "embed_gather_fwd: %d tokens at a stride of %d overflow the token index", num_tokens, stride_s);
+    if (get_option("gather_variant") == 2 && pe != nullptr) {
+      const int ctas_per_sm = get_option("gather_bulk_ctas_per_sm") == 1 ? 1 : 2;
+      const GatherBulkLayout L = gather_bulk_layout<T>(d, ctas_per_sm);
+      unsigned int *timeouts = wait_timeouts_counter();
+      if (L.stages >= 2 && timeouts != nullptr) {
+        auto kern = embed_gather_bulk_kernel<T>;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L.total));
+        DLB_REQUIRE(e == cudaSuccess, DLB_ERR_CUDA, "embed_gather_fwd: shared memory attribute: %s", cudaGetErrorString(e));
+        const int bgrid = min(stride_s, 4 * ctas_per_sm * sm_count());
+        launch_pdl(kern, bgrid, kGatherThreads, L.total, st, static_cast<const T *>(table), ids, pe, static_cast<T *>(out),
+                   num_tokens, vocab, d, stride_s, L, timeouts);
+        DLB_LAUNCH_CHECK("embed_gather_bulk");
+        return DLB_OK;
+      }
+    }
     // Rows in flight per thread: four (six CTAs fit an SM) unless asked otherwise.
     if (get_option("gather_rows_in_flight") == 8 && ceil_div(num_tokens, stride_s) > 4)
       launch_pdl(embed_gather_kernel<T, 8>, grid, dim3(bs.tx, bs.ty), 0, st, static_cast<const T *>(table), ids, pe,
