@@ -1008,8 +1008,39 @@ def profile_case(name):
         grad, ws = torch.empty(V, D, device=dev), ops.embed_workspace(T, V, D, dev)
         for _ in range(3):
             ops.embed_gather_fwd(table, ids, pe, S, out=out)
+            capi.set_option("gather_variant", 2)  # the bulk-copy form of the same gather
+            ops.embed_gather_fwd(table, ids, pe, S, out=out)
+            capi.set_option("gather_variant", 0)
             ops.embed_sort_tokens(ids, V, D, workspace=ws)
             ops.embed_scatter_bwd(dy, ids, V, ws, grad=grad)
+    elif kind == "peer":
+        # The kernels of the peer-memory exchange as rank 0 of 8 runs them, with the seven peers' buffers
+        # standing in on this one GPU (so the "remote" stores are local: this shows the kernels, not NVLink).
+        world, V, D = 8, 32000, 4096
+        T = 32768 // world
+        Tg = T * world
+        ids_all = torch.cat([torch.from_numpy(zipf_ids(np.random.Generator(np.random.Philox(key=1234 + r)), T, V))
+                             for r in range(world)]).to(dev)
+        dx = randn(T, D).to(dt)
+        small = randn(4 * D + 16384)
+        ws_global = ops.embed_workspace(Tg, V, D, dev)
+        cap = (min(V, Tg) + world - 1) // world
+        flags = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(world)]
+        recv = torch.zeros(world * cap * D, device=dev)
+        mine, theirs = torch.zeros(V, D, device=dev), torch.zeros(V, D, device=dev)
+        small_recv = torch.zeros(world * small.numel(), device=dev)
+        stage = torch.zeros(world * cap * D, dtype=torch.bfloat16, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        group = ops.peer_group(world, 0, cap, [f.data_ptr() for f in flags], [recv.data_ptr()] * world,
+                               [mine.data_ptr()] + [theirs.data_ptr()] * (world - 1), status,
+                               [small_recv.data_ptr()] * world, small.numel(), 1000, stage=[stage.data_ptr()] * world)
+        rank_plan = ops.embed_rank_plan_workspace(V, T, D, dev)
+        small_out = torch.empty_like(small)
+        for step in range(1, 4):
+            ops.embed_sort_tokens(ids_all, V, D, workspace=ws_global)
+            ops.embed_rank_plan(ws_global, Tg, T, world, 0, V, D, rank_plan=rank_plan)
+            ops.embed_scatter_bwd_peer(dx, ws_global, Tg, rank_plan, T, group, small, min(V, Tg), V, 0, step, clear_unused=1)
+            ops.embed_reduce_broadcast_peer(rank_plan, T, group, small_out, V, D, capi.dtype_of(dx), 3, 0, 1, step)
     elif kind == "optim":
         # AdamW over six groups of 8 Mi parameters, then the gradient norm + clip (fp32 only)
         sizes = [8 << 20] * 6
@@ -1029,7 +1060,7 @@ def profile_case(name):
 
 
 PROFILE_CASES = [f"{k}_{s}" for k in ("ln_fwd", "ln_bwd", "ln_bwd2", "relu", "tanh", "embed") for s in ("fp32", "bf16")]
-PROFILE_CASES.append("optim_fp32")
+PROFILE_CASES += ["optim_fp32", "peer_bf16"]
 
 
 # --------------------------------------------------------------------------- main

@@ -298,39 +298,47 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a) {
       if (staged)
         for (int i = tid; i < np; i += kEmbBlock) s_perm[i] = ld_co(a.perm + p0 + i) - tok_offset;
       __syncthreads();
-      // Rows with no token or one token (nearly all of them): U rows at a time, every load of the U
-      // rows issued before the first store, so that U*KV 16-byte loads per thread are in flight.  A
-      // row's sum is still 0.0f + dy (the same bits as the general path below).
+      // Rows with no token (most of them) first: pure stores, nothing to wait for.
+      if (!a.skip_empty) {
+        for (int rl = threadIdx.y; rl < nrows; rl += ty) {
+          if (s_e[rl] != s_b[rl]) continue;
+#pragma unroll
+          for (int k = 0; k < KV; k++)
+#pragma unroll
+            for (int q = 0; q < E; q++) acc[k][q] = 0.f;
+          store_row<E, KV>(a.out + static_cast<size_t>(v_first + rl) * d, cv0, tx, ncv, acc);
+        }
+      }
+      // Rows with one token: U rows at a time, every load of the U rows issued before the first store,
+      // so that U*KV 16-byte loads per thread are in flight.  A row's sum is still 0.0f + dy (the same
+      // bits as the general path below).
       constexpr int U = KV >= 4 ? 2 : 4;
       for (int rl0 = threadIdx.y; rl0 < nrows; rl0 += ty * U) {
         uint4 v[U][KV];
-        int state[U];  // -1: not mine or handled below, 0: empty row, 1: one token
+        bool one[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
           const int rl = rl0 + u * ty;
-          state[u] = -1;
-          if (rl < nrows) {
-            const int b = s_b[rl], cnt = s_e[rl] - b;
-            if (cnt <= 1) state[u] = cnt;
-            if (cnt == 1) {
-              const int t = staged ? s_perm[b - p0] : ld_co(a.perm + b) - tok_offset;
-              const T *src = dy + static_cast<size_t>(t) * d;
+          one[u] = rl < nrows && s_e[rl] - s_b[rl] == 1;
+          if (one[u]) {
+            const int b = s_b[rl];
+            const int t = staged ? s_perm[b - p0] : ld_co(a.perm + b) - tok_offset;
+            const T *src = dy + static_cast<size_t>(t) * d;
 #pragma unroll
-              for (int k = 0; k < KV; k++) {
-                const int cv = cv0 + k * tx;
-                if (cv < ncv) v[u][k] = ld_stream(src + static_cast<size_t>(cv) * E);
-              }
+            for (int k = 0; k < KV; k++) {
+              const int cv = cv0 + k * tx;
+              if (cv < ncv) v[u][k] = ld_stream(src + static_cast<size_t>(cv) * E);
             }
           }
         }
 #pragma unroll
         for (int u = 0; u < U; u++) {
-          if (state[u] < 0 || (state[u] == 0 && a.skip_empty)) continue;
+          if (!one[u]) continue;
 #pragma unroll
           for (int k = 0; k < KV; k++) {
 #pragma unroll
             for (int q = 0; q < E; q++) acc[k][q] = 0.f;
-            if (state[u] == 1 && cv0 + k * tx < ncv) {
+            if (cv0 + k * tx < ncv) {
               float f[E];
               S::unpack(v[u][k], f);
 #pragma unroll
