@@ -642,38 +642,52 @@ reduce_broadcast_kernel(const __grid_constant__ ReduceArgs a, const __grid_const
     for (int q = 0; q < a.n; q++) __stcs(reinterpret_cast<float4 *>(a.grad[q] + row_off) + c, acc);
   }
   if (a.stage != nullptr) {
-    // one row per step; the next row's slot and table row are fetched while this one moves
+    // Two rows per step (their loads in flight together); the slots and table rows of the next step
+    // are fetched while these move.
     const int narrow = ld_co(a.header + kHdrNarrow);
     const int ncv = d / E;
     const T *stage = static_cast<const T *>(a.stage);
     float *mine = a.grad[a.me];
-    int item = blockIdx.x;
-    int slot = item < narrow ? ld_co(a.narrow + item) : 0;
-    int row = item < narrow ? ld_co(a.used_rows + slot) : 0;
+    int item = 2 * blockIdx.x;
+    int slot[2], row[2];
+#pragma unroll
+    for (int u = 0; u < 2; u++) slot[u] = item + u < narrow ? ld_co(a.narrow + item + u) : 0;
+#pragma unroll
+    for (int u = 0; u < 2; u++) row[u] = item + u < narrow ? ld_co(a.used_rows + slot[u]) : 0;
     while (item < narrow) {
-      const int item_next = item + gridDim.x;
-      const int slot_next = item_next < narrow ? ld_co(a.narrow + item_next) : 0;
-      const uint4 *src = reinterpret_cast<const uint4 *>(stage + static_cast<size_t>(slot) * d);
-      float *dst = mine + static_cast<size_t>(row) * d;
+      const int item_next = item + 2 * gridDim.x;
+      int slot_next[2];
+#pragma unroll
+      for (int u = 0; u < 2; u++) slot_next[u] = item_next + u < narrow ? ld_co(a.narrow + item_next + u) : 0;
       for (int cv0 = threadIdx.x; cv0 < ncv; cv0 += 2 * kBlock) {
-        uint4 raw[2];
+        uint4 raw[2][2];
 #pragma unroll
-        for (int u = 0; u < 2; u++)
-          if (cv0 + u * kBlock < ncv) raw[u] = __ldcg(src + cv0 + u * kBlock);  // written by a peer: read at L2
+        for (int r = 0; r < 2; r++) {
+          const uint4 *src = reinterpret_cast<const uint4 *>(stage + static_cast<size_t>(slot[r]) * d);
 #pragma unroll
-        for (int u = 0; u < 2; u++) {
-          if (cv0 + u * kBlock >= ncv) continue;
-          float f[E];
-          S::unpack(raw[u], f);
+          for (int u = 0; u < 2; u++)
+            if (item + r < narrow && cv0 + u * kBlock < ncv) raw[r][u] = __ldcg(src + cv0 + u * kBlock);  // written by a peer
+        }
 #pragma unroll
-          for (int e = 0; e < E; e++) f[e] = 0.0f + f[e];
-          store_vec<E>(dst + static_cast<size_t>(cv0 + u * kBlock) * E, f);
+        for (int r = 0; r < 2; r++) {
+          float *dst = mine + static_cast<size_t>(row[r]) * d;
+#pragma unroll
+          for (int u = 0; u < 2; u++) {
+            if (item + r >= narrow || cv0 + u * kBlock >= ncv) continue;
+            float f[E];
+            S::unpack(raw[r][u], f);
+#pragma unroll
+            for (int e = 0; e < E; e++) f[e] = 0.0f + f[e];
+            store_vec<E>(dst + static_cast<size_t>(cv0 + u * kBlock) * E, f);
+          }
         }
       }
-      const int row_next = item_next < narrow ? ld_co(a.used_rows + slot_next) : 0;
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        row[u] = item_next + u < narrow ? ld_co(a.used_rows + slot_next[u]) : 0;
+        slot[u] = slot_next[u];
+      }
       item = item_next;
-      slot = slot_next;
-      row = row_next;
     }
   }
   {
@@ -693,12 +707,21 @@ reduce_broadcast_kernel(const __grid_constant__ ReduceArgs a, const __grid_const
     const int n4 = a.small_n / 4;
     for (int i = blockIdx.x * kBlock + threadIdx.x; i < n4; i += gridDim.x * kBlock) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int src = 0; src < a.n; src++) {
-        const float4 p = __ldcg(reinterpret_cast<const float4 *>(a.small_recv + static_cast<size_t>(src) * a.small_n) + i);
-        if (src == 0) {
-          acc = p;
-        } else {
-          acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+#pragma unroll 1
+      for (int base = 0; base < a.n; base += 8) {
+        float4 part[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+          if (base + u < a.n)
+            part[u] = __ldcg(reinterpret_cast<const float4 *>(a.small_recv + static_cast<size_t>(base + u) * a.small_n) + i);
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          if (base + u >= a.n) continue;
+          if (base + u == 0) {
+            acc = part[u];
+          } else {
+            acc.x += part[u].x; acc.y += part[u].y; acc.z += part[u].z; acc.w += part[u].w;
+          }
         }
       }
       reinterpret_cast<float4 *>(a.small_out)[i] = acc;
@@ -957,7 +980,7 @@ extern "C" int dlb_embed_reduce_broadcast_peer(void *rank_plan, int tokens_per_r
   a.limit_ns = static_cast<unsigned long long>(peers->timeout_ms) * 1000000ull;
   PeerSignal sig{};
   fill_signal(&sig, peers, r.header + kHdrDoneReduce, signal_channel, signal_epoch);
-  const int grid = 6 * sm_count();
+  const int grid = 4 * sm_count();  // what fits the GPU at once: one wave
   if (dtype == DLB_BF16)
     launch_pdl(reduce_broadcast_kernel<__nv_bfloat16>, grid, kBlock, 0, as_stream(stream), a, sig);
   else
