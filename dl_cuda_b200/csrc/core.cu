@@ -49,6 +49,8 @@ Option g_options[] = {
     {"ln_bwd_pipe_ctas_per_sm", {0}},   // 1 or 2
     {"ln_bwd_pipe_rows_per_tile", {0}}, // 1, 2, 4 or 8
     {"act_bwd_partial_rows", {0}},      // upper bound of the partial rows of a fused bias gradient
+    {"scatter_variant", {0}},           // 2: the bulk-copy (TMA) pipeline instead of rows in registers
+    {"scatter_bulk_ctas_per_sm", {0}},  // ring sized for this many CTAs per SM (default 3)
     {"scatter_zero_kernel", {0}},       // 1: empty rows are cleared by a kernel of their own before the scatter-add
     {"embed_push_period", {0}},         // one CTA in this many pushes rows over NVLink, the others clear rows
     {"embed_peer_phases", {0}},         // 1: only the local sums, 2: only the push of dlb_embed_scatter_bwd_peer

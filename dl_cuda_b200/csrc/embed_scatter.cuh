@@ -17,6 +17,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace dlb {
 
@@ -362,6 +363,197 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a) {
   }
 }
 
+// The same sums as a bulk-copy (TMA) pipeline, the alternative form of scatter_rows_kernel
+// (dlb_set_option "scatter_variant" = 2; rows of up to 1024 column vectors that fit the ring).
+// A CTA takes up to kBulkJobs jobs: a group of consecutive output rows, or (the first sub_groups
+// CTAs) sub-segments of long rows.  It first lists the jobs' token indices in shared memory, then
+//   producer warp   lane 0 streams the dy rows of those tokens, job after job, into a ring of
+//                   shared-memory stages with cp.async.bulk (completion on mbarriers);
+//   consumer warps  store the rows without tokens, then per job add the staged rows in token
+//                   order into registers and store the sum once.
+// No thread holds a dy row in registers while it is in flight and the producer runs ahead over row
+// boundaries, so the bytes in flight are set by the ring depth, not by the register file.  The order
+// of every row's additions is the one of scatter_rows_kernel: the two forms give the same bits.
+constexpr int kBulkConsumers = 256;
+constexpr int kBulkThreads = kBulkConsumers + 32;
+constexpr int kBulkJobs = 16;
+
+struct ScatterBulkLayout {
+  int stages;
+  unsigned row_bytes, bar_off, total;
+};
+
+template <typename T, int KV>
+__global__ void __launch_bounds__(kBulkThreads)
+scatter_rows_bulk_kernel(const T *dy, const __grid_constant__ ScatterArgs a, ScatterBulkLayout L,
+                         unsigned int *timeouts) {
+  pdl_prologue();
+  using S = Store<T>;
+  constexpr int E = S::kPerVec;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char *ring = smem_raw;
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + L.bar_off);  // [stages]
+  uint64_t *empty = full + 16;                                          // [stages]
+  volatile int *dead = reinterpret_cast<volatile int *>(empty + 16);
+  __shared__ int s_b[kBulkJobs], s_n[kBulkJobs];  // first token (index into perm) and token count; -1: not this CTA's
+  __shared__ float *s_dst[kBulkJobs];
+  __shared__ int s_tok[kBulkJobs * kSubLen];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int stages = L.stages;
+  const int d = a.d;
+  const int ncv = d / E;
+  if (tid == 0) {
+    for (int i = 0; i < stages; i++) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], kBulkConsumers / 32);
+    }
+    *dead = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const bool sub_cta = static_cast<int>(blockIdx.x) < a.sub_groups;
+  int n_long = 0, n_sub = 0, out_rows = 0, rounds;
+  if (sub_cta) {
+    n_long = ld_co(a.meta);
+    n_sub = ld_co(a.meta + 1);
+    // sub-segment blockIdx.x + i * sub_groups is job i; kBulkJobs of them per round
+    const int mine = (max(n_sub - static_cast<int>(blockIdx.x), 0) + a.sub_groups - 1) / a.sub_groups;
+    rounds = (mine + kBulkJobs - 1) / kBulkJobs;
+  } else {
+    out_rows = a.out_rows_dev != nullptr ? min(a.out_rows, ld_co(a.out_rows_dev)) : a.out_rows;
+    const int row_ctas = gridDim.x - a.sub_groups;
+    const int groups = (out_rows + kBulkJobs - 1) / kBulkJobs;
+    rounds = (max(groups - static_cast<int>(blockIdx.x - a.sub_groups), 0) + row_ctas - 1) / row_ctas;
+  }
+  int st = 0;           // ring position, the same sequence in the producer and in every consumer
+  unsigned phase = 0;
+  for (int round = 0; round < rounds; round++) {
+    // ---- the jobs of this round
+    if (tid < kBulkJobs) {
+      int b = 0, n = -1;
+      float *dst = nullptr;
+      if (sub_cta) {
+        const int idx = blockIdx.x + (round * kBulkJobs + tid) * a.sub_groups;
+        if (idx < n_sub) {
+          int lo = 0, hi = n_long;  // last long row whose first sub-segment is <= idx
+          while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (ld_co(a.long_first + mid) <= idx) lo = mid; else hi = mid;
+          }
+          const int li = ld_co(a.long_row + lo);
+          b = ld_co(a.long_b + li) + (idx - ld_co(a.long_first + lo)) * kSubLen;
+          n = min(ld_co(a.long_e + li), b + kSubLen) - b;
+          dst = a.scratch + static_cast<size_t>(idx) * d;
+        }
+      } else {
+        const int row_ctas = gridDim.x - a.sub_groups;
+        const int r = ((blockIdx.x - a.sub_groups) + round * row_ctas) * kBulkJobs + tid;
+        if (r < out_rows) {
+          b = ld_co(a.seg_b + r);
+          n = ld_co(a.seg_e + r) - b;
+          if (n > kSubLen || (n == 0 && a.skip_empty)) n = -1;  // long rows are written by the sub-segment CTAs
+          dst = a.out + static_cast<size_t>(r) * d;
+        }
+      }
+      s_b[tid] = b;
+      s_n[tid] = n;
+      s_dst[tid] = dst;
+    }
+    __syncthreads();
+    for (int slot = tid; slot < kBulkJobs * kSubLen; slot += kBulkThreads) {
+      const int j = slot / kSubLen, k = slot % kSubLen;
+      if (k < s_n[j]) s_tok[slot] = ld_co(a.perm + s_b[j] + k) - a.tok_offset;
+    }
+    __syncthreads();
+
+    if (warp == kBulkConsumers / 32) {
+      // ------------------------------------------------------------ producer
+      if (lane == 0) {
+        for (int j = 0; j < kBulkJobs; j++) {
+          const int n = s_n[j];
+          for (int k = 0; k < n; k++) {
+            mbar_wait(&empty[st], phase ^ 1, dead, timeouts);
+            mbar_expect_tx(&full[st], L.row_bytes);
+            bulk_load(ring + static_cast<size_t>(st) * L.row_bytes,
+                      dy + static_cast<size_t>(s_tok[j * kSubLen + k]) * d, L.row_bytes, &full[st]);
+            if (++st == stages) { st = 0; phase ^= 1; }
+          }
+        }
+      }
+    } else {
+      // ------------------------------------------------------------ consumers
+      float acc[KV][E];
+      // Rows with no token (most of them) first: pure stores, nothing to wait for.
+      for (int j = 0; j < kBulkJobs; j++) {
+        if (s_n[j] != 0) continue;
+#pragma unroll
+        for (int k = 0; k < KV; k++)
+#pragma unroll
+          for (int q = 0; q < E; q++) acc[k][q] = 0.f;
+        store_row<E, KV>(s_dst[j], tid, kBulkConsumers, ncv, acc);
+      }
+      for (int j = 0; j < kBulkJobs; j++) {
+        const int n = s_n[j];
+        if (n <= 0) continue;
+#pragma unroll
+        for (int k = 0; k < KV; k++)
+#pragma unroll
+          for (int q = 0; q < E; q++) acc[k][q] = 0.f;
+        for (int t = 0; t < n; t++) {
+          mbar_wait(&full[st], phase, dead, timeouts);
+          const unsigned char *row = ring + static_cast<size_t>(st) * L.row_bytes;
+          uint4 raw[KV];
+#pragma unroll
+          for (int k = 0; k < KV; k++) {
+            const int cv = tid + k * kBulkConsumers;
+            if (cv < ncv) raw[k] = lds128(row + static_cast<size_t>(cv) * 16);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[st]);  // this warp's reads of the stage have returned
+          if (++st == stages) { st = 0; phase ^= 1; }
+#pragma unroll
+          for (int k = 0; k < KV; k++) {
+            if (tid + k * kBulkConsumers < ncv) {
+              float f[E];
+              S::unpack(raw[k], f);
+#pragma unroll
+              for (int q = 0; q < E; q++) acc[k][q] += f[q];
+            }
+          }
+        }
+        store_row<E, KV>(s_dst[j], tid, kBulkConsumers, ncv, acc);
+      }
+    }
+    // The producer (lanes other than 0 too) must follow the ring position of lane 0.
+    if (warp == kBulkConsumers / 32) {
+      st = __shfl_sync(0xffffffffu, st, 0);
+      phase = __shfl_sync(0xffffffffu, phase, 0);
+    }
+    __syncthreads();  // the job arrays are refilled by the next round
+  }
+  // After a wait gave up, copies may still be landing in this CTA's shared memory.
+  if (*dead) {
+    for (int i = 0; i < 1000; i++) __nanosleep(1000);
+  }
+}
+
+// Ring depth and shared-memory layout, or stages == 0 when the shape does not fit the kernel.
+template <typename T>
+ScatterBulkLayout scatter_bulk_layout(int d, int ctas_per_sm) {
+  constexpr int E = Store<T>::kPerVec;
+  ScatterBulkLayout L{};
+  if (d % E != 0 || d / E > 4 * kBulkConsumers) return L;
+  L.row_bytes = static_cast<unsigned>(d * sizeof(T));
+  const size_t budget = (216 * 1024) / ctas_per_sm - 4096;  // the static arrays take 2.3 KB
+  if (2 * static_cast<size_t>(L.row_bytes) + 512 > budget) return L;
+  const size_t stages = (budget - 512) / L.row_bytes;
+  L.stages = static_cast<int>(stages > 16 ? 16 : stages);
+  L.bar_off = L.row_bytes * L.stages;
+  L.total = L.bar_off + 512;
+  return L;
+}
+
 // out[row,:] of every long row = the sum of its scratch rows.  A work item is (long row, block of
 // 32 float4 column vectors); CTAs loop over the items.  Each of the CTA's kCombineSlices warps adds
 // one contiguous slice of the row's sub-segments in order (512 contiguous bytes per sub-segment),
@@ -462,11 +654,40 @@ int launch_scatter_rows(const void *dy, ScatterArgs a, int max_sub, int row_ctas
     DLB_LAUNCH_CHECK("zero_empty_rows");
     a.skip_empty = 1;
   }
-  auto go = [&](auto kern) { launch_pdl(kern, grid, dim3(bs.tx, bs.ty), 0, st, static_cast<const T *>(dy), a); };
-  if (kv == 4) go(scatter_rows_kernel<T, 4>);
-  else if (kv == 2) go(scatter_rows_kernel<T, 2>);
-  else go(scatter_rows_kernel<T, 1>);
-  DLB_LAUNCH_CHECK("scatter_rows");
+  bool launched = false;
+  if (get_option("scatter_variant") == 2) {
+    int per_sm = get_option("scatter_bulk_ctas_per_sm");
+    if (per_sm < 1 || per_sm > 6) per_sm = 3;
+    const ScatterBulkLayout L = scatter_bulk_layout<T>(a.d, per_sm);
+    unsigned int *timeouts = wait_timeouts_counter();
+    if (L.stages >= 2 && timeouts != nullptr && aligned16(dy)) {
+      ScatterArgs b = a;
+      b.sub_groups = min(max_sub, 4 * sm_count());
+      const int bgroups = ceil_div(a.out_rows, kBulkJobs);
+      const int brow = row_ctas > 0 ? min(bgroups, row_ctas) : bgroups;
+      const int bkv = ceil_div(ncv, kBulkConsumers);
+      auto go_bulk = [&](auto kern) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L.total));
+        DLB_REQUIRE(e == cudaSuccess, DLB_ERR_CUDA, "scatter_rows_bulk: shared memory attribute: %s", cudaGetErrorString(e));
+        launch_pdl(kern, b.sub_groups + brow, kBulkThreads, L.total, st, static_cast<const T *>(dy), b, L, timeouts);
+        return DLB_OK;
+      };
+      int rc;
+      if (bkv > 2) rc = go_bulk(scatter_rows_bulk_kernel<T, 4>);
+      else if (bkv == 2) rc = go_bulk(scatter_rows_bulk_kernel<T, 2>);
+      else rc = go_bulk(scatter_rows_bulk_kernel<T, 1>);
+      if (rc != DLB_OK) return rc;
+      DLB_LAUNCH_CHECK("scatter_rows_bulk");
+      launched = true;
+    }
+  }
+  if (!launched) {
+    auto go = [&](auto kern) { launch_pdl(kern, grid, dim3(bs.tx, bs.ty), 0, st, static_cast<const T *>(dy), a); };
+    if (kv == 4) go(scatter_rows_kernel<T, 4>);
+    else if (kv == 2) go(scatter_rows_kernel<T, 2>);
+    else go(scatter_rows_kernel<T, 1>);
+    DLB_LAUNCH_CHECK("scatter_rows");
+  }
   // 8 CTAs fit an SM; each loops over (long row, column block) items
   launch_pdl(combine_long_kernel, 8 * sm_count(), kEmbBlock, 0, st, a);
   DLB_LAUNCH_CHECK("combine_long");

@@ -73,6 +73,8 @@ DLB_API uint64_t dlb_launch_count(void);
  *   "ln_bwd_pipe_ctas_per_sm"    1 | 2
  *   "ln_bwd_pipe_rows_per_tile"  1 | 2 | 4 | 8
  *   "act_bwd_partial_rows"       upper bound of the partial rows of a fused bias gradient
+ *   "scatter_variant"            2 the bulk-copy (TMA) pipeline for the sorted-segment sums
+ *   "scatter_bulk_ctas_per_sm"   1..6: its ring is sized for this many CTAs per SM (default 3)
  *   "scatter_zero_kernel"        1 the rows without tokens are cleared by a kernel of their own
  *                                that runs before the scatter-add
  *   "embed_push_period"          1..6: one CTA in this many of dlb_embed_scatter_bwd_peer's

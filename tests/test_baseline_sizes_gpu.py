@@ -18,7 +18,7 @@ import pytest
 import torch
 
 import bench
-from bench import rel_err_dev, same_bits
+from bench import rel_err_dev, rel_err_rows_dev, same_bits
 from conftest import rng_for, zipf_ids
 from dl_cuda_b200 import capi, ops
 from oracle import cpu as oracle
@@ -48,19 +48,6 @@ def rel_l2_dev(got, want) -> float:
         num += float(((g - w) ** 2).sum())
         den += float((w * w).sum())
     return (num / max(den, 1e-300)) ** 0.5
-
-
-def rel_err_rows_dev(got, want) -> float:
-    """rel_err with the rms of each ROW of `want` as the floor of the denominator: a table gradient is
-    mostly zero rows beside a few rows that sum thousands of terms, so the rms of the whole tensor says
-    nothing about the scale of either kind.  A zero row must be matched exactly."""
-    worst = 0.0
-    for r0 in range(0, want.shape[0], 4096):
-        g, w = got[r0:r0 + 4096].double(), want[r0:r0 + 4096].double()
-        rms = (w * w).mean(dim=1, keepdim=True).sqrt()
-        denom = torch.maximum(torch.maximum(g.abs(), w.abs()), rms).clamp_min(1e-300)
-        worst = max(worst, float(((g - w).abs() / denom).max()))
-    return worst
 
 
 def randn(gen, *shape, scale=1.0):
