@@ -166,7 +166,7 @@ class Chain:
            "ln2_bwd", "relu_bwd", "ln1_bwd", "embed_scatter", "allreduce"]
 
     def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist, exchange="peer", clear="incremental",
-                 split_push=True):
+                 split_push=True, plan_after_gather=True):
         from dl_cuda_b200 import capi, ops
         global allreduce_param_grads
         from dl_cuda_b200.sharding import allreduce_param_grads
@@ -228,6 +228,9 @@ class Chain:
         self.h_result = torch.empty(4 * D + F, dtype=torch.float32).pin_memory()
         self.side = torch.cuda.Stream()
         self.plan_ready = torch.cuda.Event()
+        self.gather_done = torch.cuda.Event()
+        self.plan_after_gather = plan_after_gather
+        self.plan_on_main = False
         self.zero_done = torch.cuda.Event()
         if dist.active:
             Tg = T * dist.world
@@ -314,11 +317,14 @@ class Chain:
         # The sorted-segment plan depends on the ids alone and is needed only by the last kernel of
         # backward: in the headline pass it is built on a side stream, beside the forward kernels.
         main = torch.cuda.current_stream()
-        plan_stream = self.side if marks is None else main
+        plan_stream = self.side if marks is None and not self.plan_on_main else main
         pst = plan_stream.cuda_stream
-        if marks is None:
+        if marks is None and not self.plan_on_main:
             self.side.wait_stream(main)
-        if not self.dist.active:
+        plan_later = not self.dist.active and marks is None and self.plan_after_gather
+        if plan_later:
+            pass  # launched below, once the gather is in the queue
+        elif not self.dist.active:
             chk(lib.dlb_embed_sort_tokens(p(self.ids), p(self.ws_embed), self.ws_embed.numel(), T, V, D, pst))
         else:
             # Every rank needs every rank's ids: one sort of the gathered list gives the numbering of the rows
@@ -335,7 +341,8 @@ class Chain:
             if self.peer is None:
                 with torch.cuda.stream(plan_stream):
                     self.h_used.copy_(self.rank_plan[:4].view(torch.int32)[:1], non_blocking=True)
-        self.plan_ready.record(plan_stream)
+        if not plan_later:
+            self.plan_ready.record(plan_stream)
         if self.dist.active and self.peer is not None and self.clear_early:
             # The rows nobody uses are cleared on the second stream as soon as the plan says which they are,
             # beside the forward and backward kernels (which, at a few thousand rows per GPU, leave HBM idle
@@ -346,6 +353,13 @@ class Chain:
             self.zero_done.record(self.side)
         mark()
         chk(lib.dlb_embed_gather_fwd(p(self.table), p(self.ids), p(self.pe), S, p(self.x0), T, V, D, code, st))
+        if plan_later:
+            # One GPU: the plan (a latency-bound kernel of a few CTAs) starts once the gather has ended, beside
+            # the first layer norm: next to the gather, whose CTAs each hold one position, it cost more.
+            self.gather_done.record(main)
+            self.side.wait_event(self.gather_done)
+            chk(lib.dlb_embed_sort_tokens(p(self.ids), p(self.ws_embed), self.ws_embed.numel(), T, V, D, pst))
+            self.plan_ready.record(plan_stream)
         mark()
         chk(lib.dlb_ln_residual_fwd(p(self.x0), p(self.attn_out), p(self.gamma1), p(self.beta1), p(self.y1),
                                     p(self.xhat1), p(self.inv1), T, D, 1e-5, code, st))
@@ -1128,6 +1142,11 @@ def main():
                          "the second stream beside the compute kernels")
     ap.add_argument("--no-split-push", action="store_true",
                     help="N > 1, peer exchange: sums and pushes in stream order instead of overlapped on two streams")
+    ap.add_argument("--plan-beside-gather", action="store_true",
+                    help="N = 1: start the sorted-segment plan on the second stream at the start of the step (beside the "
+                         "gather) instead of after the gather")
+    ap.add_argument("--plan-on-main", action="store_true",
+                    help="build the sorted-segment plan on the main stream (no second stream in the headline pass)")
     ap.add_argument("--skip-kernels", action="store_true", help="skip the per-kernel fp32 sweep")
     ap.add_argument("--skip-cpu", action="store_true",
                     help="skip the baseline legs (the single-threaded host loops and the reference-kernel columns)")
@@ -1161,8 +1180,10 @@ def main():
     _, tokens_local = shard_rows(args.tokens, n, dist.rank, SEQ if args.tokens % (SEQ * n) == 0 else 1)
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     chain = Chain(tokens_local, SEQ, D_MODEL, D_FF, VOCAB, dtype, seed=1234 + dist.rank, dist=dist,
-                  exchange=args.exchange, clear=args.clear, split_push=not args.no_split_push)
+                  exchange=args.exchange, clear=args.clear, split_push=not args.no_split_push,
+                  plan_after_gather=not args.plan_beside_gather)
     lib = chain.lib
+    chain.plan_on_main = args.plan_on_main
 
     parity = None
     if dist.active:

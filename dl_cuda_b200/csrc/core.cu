@@ -42,14 +42,14 @@ struct Option {
 };
 Option g_options[] = {
     {"gather_rows_in_flight", {0}},     // 4 or 8 table rows loaded per thread before the first store
-    {"gather_variant", {0}},            // 2: the bulk-copy (TMA) pipeline instead of rows in registers
+    {"gather_variant", {0}},            // 1: rows in registers, 2: the bulk-copy (TMA) pipeline
     {"gather_bulk_ctas_per_sm", {0}},   // 1: one CTA per SM with a deeper ring (default 2)
     {"ln_bwd_pipe", {0}},               // 1: never the bulk-copy pipeline, 2: whenever the shape allows
     {"ln_bwd_pipe_threads", {0}},       // column threads per CTA: 128, 256 or 512
     {"ln_bwd_pipe_ctas_per_sm", {0}},   // 1 or 2
     {"ln_bwd_pipe_rows_per_tile", {0}}, // 1, 2, 4 or 8
     {"act_bwd_partial_rows", {0}},      // upper bound of the partial rows of a fused bias gradient
-    {"scatter_variant", {0}},           // 2: the bulk-copy (TMA) pipeline instead of rows in registers
+    {"scatter_variant", {0}},           // 1: rows in registers, 2: the bulk-copy (TMA) pipeline
     {"scatter_bulk_ctas_per_sm", {0}},  // ring sized for this many CTAs per SM (default 3)
     {"scatter_zero_kernel", {0}},       // 1: empty rows are cleared by a kernel of their own before the scatter-add
     {"embed_push_period", {0}},         // one CTA in this many pushes rows over NVLink, the others clear rows

@@ -363,8 +363,8 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a) {
   }
 }
 
-// The same sums as a bulk-copy (TMA) pipeline, the alternative form of scatter_rows_kernel
-// (dlb_set_option "scatter_variant" = 2; rows of up to 1024 column vectors that fit the ring).
+// The same sums as a bulk-copy (TMA) pipeline, the other form of scatter_rows_kernel (rows of up to
+// 1024 column vectors that fit the ring; launch_scatter_rows says when it is used).
 // A CTA takes up to kBulkJobs jobs: a group of consecutive output rows, or (the first sub_groups
 // CTAs) sub-segments of long rows.  It first lists the jobs' token indices in shared memory, then
 //   producer warp   lane 0 streams the dy rows of those tokens, job after job, into a ring of
@@ -654,8 +654,13 @@ int launch_scatter_rows(const void *dy, ScatterArgs a, int max_sub, int row_ctas
     DLB_LAUNCH_CHECK("zero_empty_rows");
     a.skip_empty = 1;
   }
+  // Which form: the bulk-copy pipeline where a dy row keeps all of its consumer threads busy (256 column
+  // vectors or more) and the plan is the dense one, whose CTAs each have 16 consecutive rows to work on
+  // (V 32000 x D 4096, 32768 Zipf tokens: 150 against 165 us with bf16 input, 192 against 216 us with
+  // fp32); rows in registers otherwise.  "scatter_variant" 1 / 2 asks for one form.
   bool launched = false;
-  if (get_option("scatter_variant") == 2) {
+  const int want_form = get_option("scatter_variant");
+  if (want_form == 2 || (want_form == 0 && a.contiguous && ncv >= kBulkConsumers)) {
     int per_sm = get_option("scatter_bulk_ctas_per_sm");
     if (per_sm < 1 || per_sm > 6) per_sm = 3;
     const ScatterBulkLayout L = scatter_bulk_layout<T>(a.d, per_sm);

@@ -66,14 +66,15 @@ DLB_API uint64_t dlb_launch_count(void);
  * fit a call's shape is ignored for that call.  Results are the same whatever the choice
  * (except where an option says otherwise).
  *   "gather_rows_in_flight"      4 | 8   table rows a thread loads before its first store
- *   "gather_variant"             2 the bulk-copy (TMA) pipeline instead of rows in registers
+ *   "gather_variant"             1 rows in registers | 2 the bulk-copy (TMA) pipeline
  *   "gather_bulk_ctas_per_sm"    1 one CTA per SM with a deeper ring (default 2)
  *   "ln_bwd_pipe"                1 never the bulk-copy pipeline | 2 whenever the shape allows
  *   "ln_bwd_pipe_threads"        128 | 256 | 512 column threads per CTA
  *   "ln_bwd_pipe_ctas_per_sm"    1 | 2
  *   "ln_bwd_pipe_rows_per_tile"  1 | 2 | 4 | 8
  *   "act_bwd_partial_rows"       upper bound of the partial rows of a fused bias gradient
- *   "scatter_variant"            2 the bulk-copy (TMA) pipeline for the sorted-segment sums
+ *   "scatter_variant"            1 rows in registers | 2 the bulk-copy (TMA) pipeline, for the
+ *                                sorted-segment sums
  *   "scatter_bulk_ctas_per_sm"   1..6: its ring is sized for this many CTAs per SM (default 3)
  *   "scatter_zero_kernel"        1 the rows without tokens are cleared by a kernel of their own
  *                                that runs before the scatter-add

@@ -42,7 +42,8 @@ SCATTER_CASES = [  # vocab, d, tokens, storage
 ]
 
 
-@pytest.mark.parametrize("form", [dict(scatter_variant=2), dict(scatter_variant=2, scatter_bulk_ctas_per_sm=1),
+@pytest.mark.parametrize("form", [dict(scatter_variant=1), dict(scatter_variant=2),
+                                  dict(scatter_variant=2, scatter_bulk_ctas_per_sm=1),
                                   dict(scatter_variant=2, scatter_bulk_ctas_per_sm=5), dict(scatter_zero_kernel=1),
                                   dict(scatter_variant=2, scatter_zero_kernel=1)])
 @pytest.mark.parametrize("vocab,d,n,storage", SCATTER_CASES)
@@ -69,13 +70,15 @@ def test_scatter_bulk_form_edge_patterns(pattern):
     else:
         ids = (rng_for(71, 1).integers(0, vocab // 2, n)).astype(np.int32)
     dy = dev(rng_for(71, 2).standard_normal((n, d)).astype(np.float32), torch.bfloat16)
-    want = scatter(dy, dev(ids), vocab)
+    with options(scatter_variant=1):
+        want = scatter(dy, dev(ids), vocab)
     with options(scatter_variant=2):
         got = scatter(dy, dev(ids), vocab)
     assert torch.equal(got.view(torch.int32), want.view(torch.int32))
 
 
-@pytest.mark.parametrize("form", [dict(gather_variant=2), dict(gather_variant=2, gather_bulk_ctas_per_sm=1),
+@pytest.mark.parametrize("form", [dict(gather_variant=1), dict(gather_variant=2),
+                                  dict(gather_variant=2, gather_bulk_ctas_per_sm=1),
                                   dict(gather_rows_in_flight=8)])
 @pytest.mark.parametrize("vocab,d,batch,seq,storage", [(2000, 4096, 5, 300, "bf16"), (2000, 4096, 3, 200, "fp32"),
                                                         (65, 64, 32, 64, "fp32"), (500, 1024, 9, 77, "bf16"),
@@ -85,7 +88,8 @@ def test_gather_forms_give_the_same_bits(vocab, d, batch, seq, storage, form):
     table = dev((0.02 * rng_for(72, 0).standard_normal((vocab, d))).astype(np.float32), dt)
     ids = dev(zipf_ids(rng_for(72, 1), batch * seq, vocab))
     pe = ops.pe_table(seq, d).cuda()
-    want = ops.embed_gather_fwd(table, ids, pe, seq)
+    with options(gather_variant=1, gather_rows_in_flight=4):
+        want = ops.embed_gather_fwd(table, ids, pe, seq)
     with options(**form):
         got = ops.embed_gather_fwd(table, ids, pe, seq)
     assert torch.equal(got.view(torch.int16 if storage == "bf16" else torch.int32),
