@@ -166,7 +166,7 @@ class Chain:
            "ln2_bwd", "relu_bwd", "ln1_bwd", "embed_scatter", "allreduce"]
 
     def __init__(self, tokens, seq, d, f, vocab, dtype, seed, dist: Dist, exchange="peer", clear="incremental",
-                 split_push=True, plan_after_gather=True):
+                 split_push=True, plan_after_gather=True, first_position=0, seq_total=None):
         from dl_cuda_b200 import capi, ops
         global allreduce_param_grads
         from dl_cuda_b200.sharding import allreduce_param_grads
@@ -188,7 +188,8 @@ class Chain:
         gp = torch.Generator(device=dev)
         gp.manual_seed(4242)
         self.table = (torch.randn(V, D, generator=gp, device=dev) * 0.02).to(dtype)
-        self.pe = ops.pe_table(seq, D).to(dev)
+        # this rank's rows of the positional-encoding table (all of it unless the ranks split the positions)
+        self.pe = ops.pe_table(seq_total or seq, D)[first_position:first_position + seq].contiguous().to(dev)
         self.gamma1 = torch.rand(D, generator=gp, device=dev) + 0.5
         self.beta1 = torch.randn(D, generator=gp, device=dev) * 0.1
         self.gamma2 = torch.rand(D, generator=gp, device=dev) + 0.5
@@ -938,7 +939,7 @@ def reference_kernel_sweep():
 # by token rows: the traffic of these streaming kernels grows in proportion to the rows.
 # (chain op, storage) -> (summary file, kernel-name fragments whose traffic adds up, rows of the captured case)
 PROFILE_TRAFFIC = {
-    ("embed_gather_pe", "bf16"): ("embedding_kernels_bf16_V32000_D4096_T32768.txt", ["embed_gather"], 32768),
+    ("embed_gather_pe", "bf16"): ("embedding_kernels_bf16_V32000_D4096_T32768.txt", ["embed_gather_bulk_kernel"], 32768),
     ("ln1_fwd", "bf16"): ("ln_fwd_kernel_bf16_16384x4096.txt", ["ln_fwd_kernel"], 16384),
     ("ln2_fwd", "bf16"): ("ln_fwd_kernel_bf16_16384x4096.txt", ["ln_fwd_kernel"], 16384),
     ("relu_fwd", "bf16"): ("act_relu_kernels_bf16_8192x16384.txt", ["act_fwd_kernel"], 8192),
@@ -946,10 +947,10 @@ PROFILE_TRAFFIC = {
     ("ln2_bwd", "bf16"): ("ln_bwd_pipe_kernel_bf16_16384x4096.txt", ["ln_bwd_pipe_kernel"], 16384),
     ("ln1_bwd", "bf16"): ("ln_bwd_pipe_kernel_two_grads_bf16_16384x4096.txt", ["ln_bwd_pipe_kernel"], 16384),
     ("embed_scatter", "bf16"): ("embedding_kernels_bf16_V32000_D4096_T32768.txt",
-                                ["scatter_rows_kernel", "combine_long_kernel"], 32768),
-    ("embed_gather_pe", "fp32"): ("embedding_kernels_fp32_V32000_D4096_T32768.txt", ["embed_gather"], 32768),
+                                ["scatter_rows_bulk_kernel", "combine_long_kernel"], 32768),
+    ("embed_gather_pe", "fp32"): ("embedding_kernels_fp32_V32000_D4096_T32768.txt", ["embed_gather_kernel"], 32768),
     ("embed_scatter", "fp32"): ("embedding_kernels_fp32_V32000_D4096_T32768.txt",
-                                ["scatter_rows_kernel", "combine_long_kernel"], 32768),
+                                ["scatter_rows_bulk_kernel", "combine_long_kernel"], 32768),
 }
 NCU_TRAFFIC_NOTE = ("ncu dram__bytes_read+write per launch, parsed from profiles/*.txt (a quarter-size or full-size "
                     "capture) and scaled by rows; writes still in L2 when the kernel ends are not counted by ncu, "
@@ -1038,12 +1039,16 @@ def profile_case(name):
         pe, out, dy = ops.pe_table(S, D).to(dev), torch.empty(T, D, device=dev, dtype=dt), randn(T, D).to(dt)
         grad, ws = torch.empty(V, D, device=dev), ops.embed_workspace(T, V, D, dev)
         for _ in range(3):
-            ops.embed_gather_fwd(table, ids, pe, S, out=out)
-            capi.set_option("gather_variant", 2)  # the bulk-copy form of the same gather
-            ops.embed_gather_fwd(table, ids, pe, S, out=out)
+            # both forms of the gather and of the scatter-add, on the same buffers: seven launches per round
+            for form in (1, 2):  # rows in registers, bulk-copy pipeline
+                capi.set_option("gather_variant", form)
+                ops.embed_gather_fwd(table, ids, pe, S, out=out)
             capi.set_option("gather_variant", 0)
             ops.embed_sort_tokens(ids, V, D, workspace=ws)
-            ops.embed_scatter_bwd(dy, ids, V, ws, grad=grad)
+            for form in (1, 2):
+                capi.set_option("scatter_variant", form)
+                ops.embed_scatter_bwd(dy, ids, V, ws, grad=grad)
+            capi.set_option("scatter_variant", 0)
     elif kind == "peer":
         # The kernels of the peer-memory exchange as rank 0 of 8 runs them, with the seven peers' buffers
         # standing in on this one GPU (so the "remote" stores are local: this shows the kernels, not NVLink).
@@ -1145,6 +1150,8 @@ def main():
     ap.add_argument("--plan-beside-gather", action="store_true",
                     help="N = 1: start the sorted-segment plan on the second stream at the start of the step (beside the "
                          "gather) instead of after the gather")
+    ap.add_argument("--shard", choices=["positions", "sequences"], default="positions",
+                    help="N > 1: a rank takes a slice of the positions of every sequence (default) or whole sequences")
     ap.add_argument("--plan-on-main", action="store_true",
                     help="build the sorted-segment plan on the main stream (no second stream in the headline pass)")
     ap.add_argument("--skip-kernels", action="store_true", help="skip the per-kernel fp32 sweep")
@@ -1177,11 +1184,19 @@ def main():
     peak, peak_kind = measured_peak()
     n = dist.world
     from dl_cuda_b200.sharding import shard_rows
-    _, tokens_local = shard_rows(args.tokens, n, dist.rank, SEQ if args.tokens % (SEQ * n) == 0 else 1)
+    # Which token rows a rank takes: the same slice of positions of every sequence (a rank then reads 1/N of the
+    # positional-encoding table, each row shared by all sequences), or whole sequences.
+    by_position = (n > 1 and args.shard == "positions" and args.tokens % SEQ == 0 and SEQ % n == 0)
+    if by_position:
+        from dl_cuda_b200.sharding import shard_positions
+        first_position, seq_local, tokens_local = shard_positions(args.tokens // SEQ, SEQ, n, dist.rank)
+    else:
+        _, tokens_local = shard_rows(args.tokens, n, dist.rank, SEQ if args.tokens % (SEQ * n) == 0 else 1)
+        first_position, seq_local = 0, SEQ
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
-    chain = Chain(tokens_local, SEQ, D_MODEL, D_FF, VOCAB, dtype, seed=1234 + dist.rank, dist=dist,
+    chain = Chain(tokens_local, seq_local, D_MODEL, D_FF, VOCAB, dtype, seed=1234 + dist.rank, dist=dist,
                   exchange=args.exchange, clear=args.clear, split_push=not args.no_split_push,
-                  plan_after_gather=not args.plan_beside_gather)
+                  plan_after_gather=not args.plan_beside_gather, first_position=first_position, seq_total=SEQ)
     lib = chain.lib
     chain.plan_on_main = args.plan_on_main
 
@@ -1260,7 +1275,9 @@ def main():
                                "scatter-add), token-sharded",
                    "batch": BATCH, "seq_len": SEQ, "d_model": D_MODEL, "d_ff": D_FF, "vocab": VOCAB,
                    "global_tokens": args.tokens, "tokens_per_gpu": tokens_local, "ids": "zipf(1.1)",
-                   "parallelism": f"token rows / {n}", "l2": "inputs larger than L2 (about 10 GB touched per step)"},
+                   "parallelism": (f"token rows / {n}" + (f": positions {first_position}..{first_position + seq_local - 1} of "
+                                                             f"every sequence on rank 0" if by_position else
+                                                             ": whole sequences per rank" if n > 1 else "")), "l2": "inputs larger than L2 (about 10 GB touched per step)"},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "kernel": dominant["op"], "achieved": dominant["gbs"], "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": dominant["frac"],

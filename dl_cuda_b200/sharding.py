@@ -22,6 +22,21 @@ def shard_rows(total_rows: int, world_size: int, rank: int, multiple_of: int = 1
     return first * multiple_of, mine * multiple_of
 
 
+def shard_positions(batch: int, seq_len: int, world_size: int, rank: int) -> tuple[int, int, int]:
+    """(first position, positions, local token rows) of `rank` when every rank takes the same slice of
+    positions of ALL `batch` sequences instead of whole sequences.  A rank's local rows are ordered
+    [sequence][position of its slice], so a row's position is first + (local row mod positions) and the
+    rank reads only its `positions` rows of the positional-encoding table, each shared by `batch` token
+    rows (with whole sequences per rank, a rank with one sequence reads one table row per token).
+    seq_len must divide evenly; shard_rows is the fallback."""
+    if not (0 <= rank < world_size) or batch <= 0 or seq_len <= 0:
+        raise ValueError("bad sharding arguments")
+    if seq_len % world_size:
+        raise ValueError(f"{seq_len} positions do not divide over {world_size} ranks")
+    positions = seq_len // world_size
+    return rank * positions, positions, batch * positions
+
+
 def allreduce_param_grads(dist, small_grads, table_grad) -> None:
     """Sums the parameter gradients over the ranks: one call for the buffer holding every small
     gradient (gamma/beta of the layer norms, biases), one for the embedding-table gradient."""

@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from conftest import rel_err, rng_for
-from dl_cuda_b200.sharding import allreduce_param_grads, shard_rows
+from dl_cuda_b200.sharding import allreduce_param_grads, shard_positions, shard_rows
 
 
 def test_shard_rows_covers_everything_once():
@@ -77,3 +77,19 @@ def test_two_gloo_ranks_match_the_unsharded_result():
     grad = oracle.embed_scatter(p["dx"], p["ids"], p["vocab"])
     assert rel_err(small[: p["d"]], dgamma) <= 1e-5 and rel_err(small[p["d"]:], dbeta) <= 1e-5
     assert rel_err(table, grad) <= 1e-5
+
+
+def test_shard_positions_covers_every_token_once():
+    batch, seq = 8, 4096
+    for world in (1, 2, 4, 8):
+        seen = np.zeros((batch, seq), np.int32)
+        for r in range(world):
+            first, positions, rows = shard_positions(batch, seq, world, r)
+            assert rows == batch * positions
+            local = np.arange(rows)
+            seen[local // positions, first + local % positions] += 1
+        assert (seen == 1).all()
+    with pytest.raises(ValueError):
+        shard_positions(8, 4096, 3, 0)
+    with pytest.raises(ValueError):
+        shard_positions(8, 4096, 4, 4)
