@@ -9,9 +9,15 @@
 //     summed by its own thread group into a scratch row; a second kernel
 //     (combine_long_kernel, many CTAs per row) adds a row's scratch rows:
 //     kCombineSlices contiguous slices of the sub-segments are summed in order,
-//     then the slice sums in order.  (Letting the CTA that stores a row's last
-//     sub-segment add them in the same launch was tried: one CTA cannot keep
-//     enough loads in flight for a row of 150 sub-segments, 220 against 156 us.)
+//     then the slice sums in order.  Measured alternatives, all slower on B200
+//     (V 32000 x D 4096, 32768 Zipf tokens, bf16): the CTA that stores a row's
+//     last sub-segment adds them all in the same launch (one CTA cannot keep
+//     enough loads in flight for a row of 150 sub-segments: 220 against 156 us);
+//     the later row CTAs of the bulk-copy form each take a few (row, column
+//     block) items once a per-row counter says the sub-segments are stored (CTAs
+//     that hold a shared-memory ring are too few to hide this latency-bound work,
+//     the kernel of its own runs 8 CTAs per SM: 160 against 149 us); items of 2 or
+//     4 column blocks in the second kernel (161 and 173 against 153 us).
 // Every addition's order is a function of the ids alone, so two runs give the
 // same bits whatever the scheduling; there are no floating-point atomics.
 #pragma once

@@ -36,6 +36,7 @@ def scatter(dy_t, ids_t, vocab):
 
 
 SCATTER_CASES = [  # vocab, d, tokens, storage
+    (30, 2048, 20000, "bf16"), (3, 4096, 9000, "fp32"),  # nearly every token in a long row
     (2000, 4096, 6000, "bf16"), (2000, 4096, 3000, "fp32"), (500, 512, 9000, "bf16"), (40000, 256, 5000, "fp32"),
     (300, 64, 70000, "fp32"), (65, 64, 2048, "bf16"), (17, 8, 40, "fp32"), (3000, 1024, 100, "bf16"),
     (129, 100, 700, "fp32"), (64, 8192, 300, "bf16"),
