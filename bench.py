@@ -435,6 +435,118 @@ class Chain:
             return float(self.h_result[0])
         return None
 
+    # ---- the exchange of step i beside the forward pass of step i+1 (an extra figure, not the headline) ----
+    def enable_overlap(self):
+        """A second set of everything the exchange touches (peer buffers with their own dense table, global plan,
+        rank plan, reduced small gradients) and a stream of its own for the exchange kernels, so that step i+1
+        can start while the table gradient of step i is still on its way.  Returns False where the peer
+        exchange is not in use."""
+        if self.peer is None:
+            return False
+        from dl_cuda_b200.sharding import PeerExchange
+        ops, dev, T, D, V = self.ops, self.table.device, self.T, self.D, self.V
+        second = PeerExchange(self.dist.dist, V, D, min(V, self.Tg), dev, tokens_per_rank=T,
+                              small_n=self.small_grads.numel())
+        second.barrier()
+        verdict = torch.tensor([second.timed_out()], dtype=torch.int64, device=dev)
+        self.dist.dist.all_reduce(verdict, op=self.dist.dist.ReduceOp.MAX)
+        if int(verdict.item()) != 0:
+            return False
+        mk = lambda peer, ws_global, rank_plan: dict(
+            peer=peer, ws_global=ws_global, rank_plan=rank_plan, table_grad=peer.table_grad(),
+            small_out=torch.empty_like(self.small_grads), plan_ready=torch.cuda.Event(), done=torch.cuda.Event())
+        self.sets = [mk(self.peer, self.ws_global, self.rank_plan),
+                     mk(second, ops.embed_workspace(self.Tg, V, D, dev), ops.embed_rank_plan_workspace(V, T, D, dev))]
+        self.ex = torch.cuda.Stream(priority=-1)
+        self.ex_pushed = torch.cuda.Event()
+        self.ov_step = 0
+        return True
+
+    def step_overlapped(self):
+        """One step whose table-gradient exchange runs on its own stream: the next step's kernels do not wait for
+        it.  Step i uses buffer set i % 2; a set is reused once ITS last exchange has ended on this rank, and
+        the gather of the token ids that opens a step is where the ranks learn that of one another."""
+        lib, capi, ops = self.lib, self.capi, self.ops
+        p = lambda t: t.data_ptr()
+        T, D, F, V, S, code = self.T, self.D, self.F, self.V, self.S, self.code
+        chk = capi.check
+        main, side, ex = torch.cuda.current_stream(), self.side, self.ex
+        st, sst = main.cuda_stream, side.cuda_stream
+        cur = self.sets[self.ov_step % 2]
+        ids = self.id_sets[self.ov_step % 2]
+        self.ids = ids
+        self.ov_step += 1
+        px = cur["peer"]
+        # plan of this step on the second stream, in this set's buffers
+        side.wait_event(cur["done"])
+        px.gather_ids(ids, stream=sst)
+        chk(lib.dlb_embed_sort_tokens(p(px.ids_all), p(cur["ws_global"]), cur["ws_global"].numel(), self.Tg, V, D, sst))
+        chk(lib.dlb_embed_rank_plan(p(cur["ws_global"]), self.Tg, T, self.dist.world, self.dist.rank,
+                                    p(cur["rank_plan"]), cur["rank_plan"].numel(), V, D, sst))
+        cur["plan_ready"].record(side)
+        # forward
+        chk(lib.dlb_embed_gather_fwd(p(self.table), p(ids), p(self.pe), S, p(self.x0), T, V, D, code, st))
+        chk(lib.dlb_ln_residual_fwd(p(self.x0), p(self.attn_out), p(self.gamma1), p(self.beta1), p(self.y1),
+                                    p(self.xhat1), p(self.inv1), T, D, 1e-5, code, st))
+        chk(lib.dlb_act_fwd(capi.RELU, p(self.ff_pre), p(self.bias1), p(self.act), p(self.mask), T, F, code, st))
+        chk(lib.dlb_ln_residual_fwd(p(self.y1), p(self.ff_out), p(self.gamma2), p(self.beta2), p(self.y2),
+                                    p(self.xhat2), p(self.inv2), T, D, 1e-5, code, st))
+        # backward writes the small gradients and dx1, which the exchange of the step before still may read
+        main.wait_event(self.ex_pushed)
+        chk(lib.dlb_ln_bwd(p(self.dy), None, p(self.xhat2), p(self.inv2), p(self.gamma2), p(self.dx2),
+                           p(self.dgamma2), p(self.dbeta2), p(self.ws_ln), self.ws_ln.numel(), T, D, code, st))
+        chk(lib.dlb_act_bwd(capi.RELU, p(self.d_act), p(self.mask), p(self.d_pre), p(self.dbias1), p(self.ws_act),
+                            self.ws_act.numel(), T, F, code, st))
+        chk(lib.dlb_ln_bwd(p(self.dx2), p(self.d_ff_in), p(self.xhat1), p(self.inv1), p(self.gamma1), p(self.dx1),
+                           p(self.dgamma1), p(self.dbeta1), p(self.ws_ln), self.ws_ln.numel(), T, D, code, st))
+        self.bwd_done.record(main)
+        # the exchange, on its own stream
+        ex.wait_event(self.bwd_done)
+        ex.wait_event(cur["plan_ready"])
+        xst = ex.cuda_stream
+        pushed, done = px.next_epoch(px.CH_PUSHED), px.next_epoch(px.CH_DONE)
+        ops.embed_scatter_bwd_peer(self.dx1, cur["ws_global"], self.Tg, cur["rank_plan"], T, px.group, self.small_grads,
+                                   min(V, self.Tg), V, px.CH_PUSHED, pushed, clear_unused=self.clear_mode, part=0, stream=xst)
+        self.ex_pushed.record(ex)
+        ops.embed_reduce_broadcast_peer(cur["rank_plan"], T, px.group, cur["small_out"], V, D, code, px.CH_PUSHED,
+                                        pushed, px.CH_DONE, done, stream=xst)
+        px.wait(px.CH_DONE, stream=xst)
+        cur["done"].record(ex)
+        return cur
+
+    def drain_overlapped(self):
+        """The main stream waits for the exchange still in flight (the end of a timed region)."""
+        torch.cuda.current_stream().wait_stream(self.ex)
+
+    def verify_overlapped(self):
+        """Untimed: overlapped steps, then the table and the small gradients of the LAST step (whose inputs are
+        still in place) against the single-rank result of all tokens; once for each buffer set."""
+        d, ops = self.dist.dist, self.ops
+        T, D, V, Tg = self.T, self.D, self.V, self.Tg
+        worst_table = worst_small = 0.0
+        for steps in (3, 1):  # the last step lands in set 0, then in set 1
+            for _ in range(steps):
+                cur = self.step_overlapped()
+            self.drain_overlapped()
+            torch.cuda.synchronize()
+            dx_all = torch.empty(Tg, D, dtype=self.dtype, device=self.dx1.device)
+            d.all_gather_into_tensor(dx_all, self.dx1)
+            ids_all = torch.empty(Tg, dtype=torch.int32, device=self.dx1.device)
+            d.all_gather_into_tensor(ids_all, self.ids)
+            want = ops.embed_scatter_bwd(dx_all, ids_all, V, ops.embed_sort_tokens(ids_all, V, D))
+            worst_table = max(worst_table, rel_err_rows_dev(cur["table_grad"], want))
+            del want, dx_all
+            small_all = torch.empty(self.dist.world, self.small_grads.numel(), device=self.dx1.device)
+            d.all_gather_into_tensor(small_all, self.small_grads)
+            worst_small = max(worst_small, rel_err_dev(cur["small_out"], small_all.double().sum(0)))
+        status = 0
+        for cur in self.sets:
+            status |= cur["peer"].timed_out()
+        worst = torch.tensor([worst_table, worst_small, float(status != 0)], dtype=torch.float64, device=self.dx1.device)
+        d.all_reduce(worst, op=d.ReduceOp.MAX)
+        return {"max_rel_err_table_grad": float(worst[0]), "max_rel_err_small_grads": float(worst[1]),
+                "status_bits_clear": float(worst[2]) == 0.0, "tolerance": 1e-5}
+
     def verify(self):
         """N > 1, untimed: one step, then every rank checks its dense table gradient and its reduced small
         gradients against the single-rank result of ALL tokens (the other ranks' gradients and ids are
@@ -1100,7 +1212,7 @@ PROFILE_CASES += ["optim_fp32", "peer_bf16"]
 
 
 # --------------------------------------------------------------------------- main
-def run_timed(step, dist: Dist, steps, warmup):
+def run_timed(step, dist: Dist, steps, warmup, drain=None):
     for _ in range(warmup):
         step()
     dist.barrier()
@@ -1108,6 +1220,8 @@ def run_timed(step, dist: Dist, steps, warmup):
     start.record()
     for _ in range(steps):
         step()
+    if drain is not None:
+        drain()  # work the steps left on other streams belongs to the timed region
     stop.record()
     dist.barrier()
     return dist.max_float(start.elapsed_time(stop))
@@ -1116,10 +1230,10 @@ def run_timed(step, dist: Dist, steps, warmup):
 REPEATS = 7  # timed regions of K steps each; the median is reported
 
 
-def run_repeats(step, dist: Dist, steps, repeats=REPEATS):
+def run_repeats(step, dist: Dist, steps, repeats=REPEATS, drain=None):
     """`repeats` back-to-back timed regions of `steps` steps (each: barrier + synchronize on both sides,
     CUDA events, max over ranks).  Returns the per-step times in ms, sorted."""
-    return sorted(run_timed(step, dist, steps, 0) / steps for _ in range(repeats))
+    return sorted(run_timed(step, dist, steps, 0, drain) / steps for _ in range(repeats))
 
 
 def capi_timeouts() -> int:
@@ -1158,6 +1272,8 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true",
                     help="skip the baseline legs (the single-threaded host loops and the reference-kernel columns)")
     ap.add_argument("--skip-fp32-chain", action="store_true", help="N=1: skip the fp32-storage run of the chain")
+    ap.add_argument("--skip-overlapped", action="store_true",
+                    help="N > 1: skip the extra figure with the exchange of a step beside the next step's forward pass")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="kernel-variant override for A/B measurements (dlb_set_option), may be repeated")
     ap.add_argument("--case", default=None, help="run one small kernel case (for ncu) and exit: " + ", ".join(PROFILE_CASES))
@@ -1302,6 +1418,30 @@ def main():
             if gave_up:
                 raise SystemExit(f"peer exchange status {gave_up:#x} (a wait gave up or the receive area was too small): "
                                  "the measurement is void")
+        # The second figure: the exchange of step i beside the forward pass of step i+1 (every exchange buffer
+        # twice).  Not the headline: a training step's optimizer would have to wait for the exchange.
+        if chain.peer is not None and not args.skip_overlapped and chain.enable_overlap():
+            check = chain.verify_overlapped()
+            good = (check["max_rel_err_table_grad"] <= check["tolerance"] and check["status_bits_clear"]
+                    and check["max_rel_err_small_grads"] <= check["tolerance"])
+            if good:
+                run_timed(chain.step_overlapped, dist, args.warmup, 0, chain.drain_overlapped)
+                ov_ms = run_repeats(chain.step_overlapped, dist, args.steps, drain=chain.drain_overlapped)
+                ms_ov = median(ov_ms)
+                status = 0
+                for cur in chain.sets:
+                    status |= cur["peer"].timed_out()
+                good = status == 0 and capi_timeouts() == 0
+            if good:
+                result["value_overlapped"] = {
+                    "value": args.tokens / (ms_ov / 1e3), "unit": "tokens/s", "ms_per_step": round(ms_ov, 4),
+                    "value_min": args.tokens / (ov_ms[-1] / 1e3), "value_max": args.tokens / (ov_ms[0] / 1e3),
+                    "parity_check": check,
+                    "what": "not the critical-path figure: the table-gradient exchange of step i runs on a stream of its "
+                            "own beside the forward pass of step i+1 (every exchange buffer and the dense table twice); "
+                            "each timed region ends when its last exchange has ended"}
+            else:
+                result["value_overlapped"] = {"error": "the overlapped steps failed their check", "parity_check": check}
     del chain
     torch.cuda.empty_cache()
     if n == 1 and args.dtype == "bf16" and not args.skip_fp32_chain:
