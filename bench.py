@@ -1420,7 +1420,12 @@ def main():
                                  "the measurement is void")
         # The second figure: the exchange of step i beside the forward pass of step i+1 (every exchange buffer
         # twice).  Not the headline: a training step's optimizer would have to wait for the exchange.
-        if chain.peer is not None and not args.skip_overlapped and chain.enable_overlap():
+        try:
+            overlapped = chain.peer is not None and not args.skip_overlapped and chain.enable_overlap()
+        except Exception as exc:  # the second set of symmetric buffers could not be set up
+            overlapped = False
+            result["value_overlapped"] = {"error": f"{type(exc).__name__}: {exc}"}
+        if overlapped:
             check = chain.verify_overlapped()
             good = (check["max_rel_err_table_grad"] <= check["tolerance"] and check["status_bits_clear"]
                     and check["max_rel_err_small_grads"] <= check["tolerance"])
