@@ -940,8 +940,9 @@ def kernel_sweep(peak, with_reference=False):
     ms = time_op(lambda: ops.embed_scatter_bwd(dyb, ids, V, wse, grad=grad))
     add("embed_scatter_bwd", "V32000 D4096 T32768 zipf1.1", T * D * 4 + V * D * 4 + T * 4, ms,
         lambda: ref.embed_bwd(ref.pe_bwd(dyb, dx=dpe_r), ids, V, grad=grad_r),
-        lambda: {"grad": rel_err_dev(grad, grad_r)},
-        lambda: (lambda e64: ({"grad": rel_err_dev(grad, e64)}, {"grad": rel_err_dev(grad_r, e64)}))(
+        # per table row (rel_err_rows_dev): the rms of the whole, mostly empty, table says nothing about a hot row
+        lambda: {"grad": rel_err_rows_dev(grad, grad_r)},
+        lambda: (lambda e64: ({"grad": rel_err_rows_dev(grad, e64)}, {"grad": rel_err_rows_dev(grad_r, e64)}))(
             torch.zeros(V, D, dtype=torch.float64, device=dev).index_add_(0, ids.long(), dyb.double())))
     del table, outb, dyb, grad
     if ref is not None:
@@ -1245,7 +1246,46 @@ def median(values):
     return float(np.median(values))
 
 
+def print_table(path):
+    """Markdown tables of a recorded bench line (`python bench.py --table FILE`): the chain's ops and the
+    per-kernel sweep with the reference columns.  The tables in the design notes are this output."""
+    line = [json.loads(l) for l in Path(path).read_text().splitlines() if l.startswith("{")][-1]
+    peak = line["roofline"]["peak"]
+    print(f"N={line['n_gpus']} {line['dtype']}: {line['ms_per_step']:.4f} ms/step = {line['value'] / 1e6:.2f} M tokens/s "
+          f"(min {line['value_min'] / 1e6:.2f}, max {line['value_max'] / 1e6:.2f}); e2e {line['e2e']['ms_per_step']:.4f} ms = "
+          f"{line['e2e']['value'] / 1e6:.2f} M tokens/s; chain {line['chain_gbs']:.0f} GB/s = "
+          f"{line['chain_gbs'] / peak:.3f} of {peak:.1f}; clocks {line['clocks']}")
+    if "chain_fp32" in line:
+        c = line["chain_fp32"]
+        print(f"fp32 chain: {c['ms_per_step']:.4f} ms/step = {c['value'] / 1e6:.2f} M tokens/s, {c['chain_gbs']:.0f} GB/s")
+    print("\n| chain op | ms | algorithmic GB/s | of measured peak | ncu DRAM bytes / algorithmic |")
+    print("|---|---|---|---|---|")
+    for op in line["chain_ops"]:
+        if op["gbs"] is None:
+            print(f"| {op['op']} | {op['ms']:.4f} | — | — | — |")
+        else:
+            ratio = f"{op['ncu_traffic'] / op['bytes']:.2f}" if op.get("ncu_traffic") else "—"
+            print(f"| {op['op']} | {op['ms']:.4f} | {op['gbs']:.0f} | {op['frac']:.3f} | {ratio} |")
+    if "kernels_fp32" in line:
+        print("\n| kernel | config | ms | GB/s | of measured peak | reference ms | speed-up | max rel. error vs reference | "
+              "vs fp64: ours / reference |")
+        print("|---|---|---|---|---|---|---|---|---|")
+        for k in line["kernels_fp32"]:
+            ref = (f"{k['ref_ms']:.4f} | {k['speedup_vs_ref']:.2f}x | "
+                   f"{'bit-exact' if k.get('bit_exact_vs_ref') else format(k.get('max_rel_err_vs_ref', float('nan')), '.2g')}"
+                   if "ref_ms" in k else "— | — | —")
+            if "err_vs_fp64" in k:
+                ref += f" | {max(k['err_vs_fp64'].values()):.2g} / {max(k['ref_err_vs_fp64'].values()):.2g}"
+            else:
+                ref += " | —"
+            gbs = f"{k['gbs']:.0f} | {k['frac_measured']:.3f}" if k.get("gbs") else "— | —"
+            print(f"| {k['kernel']} | {k['config']} | {k['ms']:.4f} | {gbs} | {ref} |")
+
+
 def main():
+    if len(sys.argv) == 3 and sys.argv[1] == "--table":
+        print_table(sys.argv[2])
+        return
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
