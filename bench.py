@@ -158,6 +158,38 @@ class Dist:
             self.dist.destroy_process_group()
 
 
+class LaggedReadback:
+    """Device-to-host read of every step's result, consumed one step late: the copy of step i's result is
+    queued behind step i's kernels, and the host waits for it (and reads it) only after it has queued step
+    i+1 -- what a training loop that logs its loss does, so the GPU never idles while the host catches up.
+    Every result is still copied and read inside the timed region; drain() takes the last one."""
+
+    def __init__(self, n):
+        self.bufs = [torch.empty(n, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self.events = [torch.cuda.Event(), torch.cuda.Event()]
+        self.count, self.pending = 0, False
+
+    def push(self, src):
+        k = self.count & 1
+        self.bufs[k].copy_(src, non_blocking=True)
+        self.events[k].record()
+        self.count += 1
+        previous = None
+        if self.pending:
+            self.events[k ^ 1].synchronize()
+            previous = float(self.bufs[k ^ 1][0])
+        self.pending = True
+        return previous
+
+    def drain(self):
+        if not self.pending:
+            return None
+        k = (self.count - 1) & 1
+        self.events[k].synchronize()
+        self.pending = False
+        return float(self.bufs[k][0])
+
+
 # --------------------------------------------------------------------------- the chain (this library)
 class Chain:
     """Buffers and the step of the block chain for `tokens` local token rows."""
@@ -227,6 +259,7 @@ class Chain:
         self.ws_act = ops.act_bwd_workspace(capi.RELU, T, F, dev)
         self.ws_embed = ops.embed_workspace(T, V, D, dev)
         self.h_result = torch.empty(4 * D + F, dtype=torch.float32).pin_memory()
+        self.readback = LaggedReadback(4 * D + F)
         self.side = torch.cuda.Stream()
         self.plan_ready = torch.cuda.Event()
         self.gather_done = torch.cuda.Event()
@@ -298,7 +331,7 @@ class Chain:
         """Table rows some rank refers to, from the rank plan of the last step (synchronises)."""
         return int(self.rank_plan[:4].view(torch.int32)[0].item())
 
-    def step(self, marks=None, copy_inputs=False, capture=None):
+    def step(self, marks=None, copy_inputs=False, capture=None, lagged=False):
         lib, capi, st = self.lib, self.capi, torch.cuda.current_stream().cuda_stream
         p = lambda t: t.data_ptr()
         T, D, F, V, S, code = self.T, self.D, self.F, self.V, self.S, self.code
@@ -429,6 +462,8 @@ class Chain:
             main.wait_event(self.zero_done)
             chk(lib.dlb_embed_expand_rows(p(self.compact_rows), p(self.rank_plan), T, p(self.table_grad), V, D, 2, st))
         mark()
+        if copy_inputs and lagged:
+            return self.readback.push(self.small_grads)
         if copy_inputs:
             self.h_result.copy_(self.small_grads, non_blocking=True)
             main.synchronize()
@@ -634,7 +669,7 @@ class ReferenceChain:
         self.pre = torch.empty_like(self.ff_pre)
         return self
 
-    def step(self, copy_inputs=False):
+    def step(self, copy_inputs=False, lagged=False):
         r, D, F = self.ref, self.D, self.F
         B = self.T // self.S if self.T >= self.S else 1
         S = min(self.S, self.T)
@@ -668,6 +703,10 @@ class ReferenceChain:
                                      self.V, D)
         if code != 0:
             raise RuntimeError(f"reference kernels failed: CUDA error {code}")
+        if copy_inputs and lagged:
+            if not hasattr(self, "readback"):
+                self.readback = LaggedReadback(self.small.numel())
+            return self.readback.push(self.small)
         if copy_inputs:
             self.h_result.copy_(self.small, non_blocking=True)
             torch.cuda.synchronize()
@@ -1409,15 +1448,23 @@ def main():
     dominant = max((o for o in ops_report if o["gbs"]), key=lambda o: o["ms"])
 
     # end to end: ids from pinned host memory in, parameter gradients out, every step
-    run_timed(lambda: chain.step(copy_inputs=True), dist, args.warmup, 0)
-    e2e_all = run_repeats(lambda: chain.step(copy_inputs=True), dist, args.steps)
+    e2e_step = lambda: chain.step(copy_inputs=True, lagged=True)
+    run_timed(e2e_step, dist, args.warmup, 0, chain.readback.drain)
+    e2e_all = run_repeats(e2e_step, dist, args.steps, drain=chain.readback.drain)
     e2e_ms = median(e2e_all)
+    # the same with the host waiting for every step's result before it queues the next step
+    run_timed(lambda: chain.step(copy_inputs=True), dist, 2, 0)
+    strict_ms = median(run_repeats(lambda: chain.step(copy_inputs=True), dist, args.steps, repeats=3))
     e2e = {"value": args.tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
            "value_min": args.tokens / (e2e_all[-1] / 1e3), "value_max": args.tokens / (e2e_all[0] / 1e3),
            "h2d_bytes_per_step": int(chain.h_ids.numel() * 4 * n),
            "d2h_bytes_per_step": int(chain.h_result.numel() * 4 * n),
+           "host_waits_every_step": {"value": args.tokens / (strict_ms / 1e3), "ms_per_step": round(strict_ms, 4)},
            "what": "per step: token ids copied from pinned host memory, the chain through the C ABI, "
-                   "gamma/beta/bias gradients read back to the host"}
+                   "gamma/beta/bias gradients copied back to pinned host memory and read there. The host reads the "
+                   "result of step i after it has queued step i+1 (one step of lag, as a training loop that logs "
+                   "its loss does); each region ends when its last result has been read. host_waits_every_step: "
+                   "the same with a host synchronisation after every step"}
 
     result = {
         "metric": "tokens/s", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
@@ -1497,8 +1544,9 @@ def main():
         ms32_all = run_repeats(chain32.step, dist, args.steps)
         ms32 = median(ms32_all)
         bytes32 = sum(chain32.bytes_per_op().values())
-        run_timed(lambda: chain32.step(copy_inputs=True), dist, args.warmup, 0)
-        e2e32 = median(run_repeats(lambda: chain32.step(copy_inputs=True), dist, args.steps))
+        e2e32_step = lambda: chain32.step(copy_inputs=True, lagged=True)
+        run_timed(e2e32_step, dist, args.warmup, 0, chain32.readback.drain)
+        e2e32 = median(run_repeats(e2e32_step, dist, args.steps, drain=chain32.readback.drain))
         result["chain_fp32"] = {"ms_per_step": round(ms32, 4), "value": args.tokens / (ms32 / 1e3), "unit": "tokens/s",
                                 "value_min": args.tokens / (ms32_all[-1] / 1e3),
                                 "value_max": args.tokens / (ms32_all[0] / 1e3),
@@ -1543,7 +1591,9 @@ def main_reference(args, dist: Dist):
     with sampler:
         total_ms = run_timed(chain.step, one, args.steps, 0)
     ms = total_ms / args.steps
-    e2e_ms = run_timed(lambda: chain.step(copy_inputs=True), one, args.steps, 1) / args.steps
+    # end to end, the way the native arm measures it: the host reads a step's result one step late
+    drain = lambda: chain.readback.drain() if hasattr(chain, "readback") else None
+    e2e_ms = run_timed(lambda: chain.step(copy_inputs=True, lagged=True), one, args.steps, 1, drain) / args.steps
     value = args.tokens / (ms / 1e3)
     h2d, d2h = int(chain.h_ids.numel() * 4), int(chain.h_result.numel() * 4)
     del chain
