@@ -43,6 +43,7 @@ struct Option {
 Option g_options[] = {
     {"gather_rows_in_flight", {0}},     // 4 or 8 table rows loaded per thread before the first store
     {"gather_variant", {0}},            // 1: rows in registers, 2: the bulk-copy (TMA) pipeline
+    {"gather_bulk_waves", {0}},         // grid of the bulk-copy gather in units of the CTAs that fit the GPU (default 4)
     {"gather_bulk_ctas_per_sm", {0}},   // 1: one CTA per SM with a deeper ring (default 2)
     {"ln_bwd_pipe", {0}},               // 1: never the bulk-copy pipeline, 2: whenever the shape allows
     {"ln_bwd_pipe_threads", {0}},       // column threads per CTA: 128, 256 or 512

@@ -100,9 +100,8 @@ embed_gather_kernel(const T *table, const int32_t *ids,
 }
 
 // The gather as a bulk-copy (TMA) pipeline, the alternative form of embed_gather_kernel
-// (dlb_set_option "gather_variant" = 2).  A CTA takes positions s = cta, cta + grid, ...; the grid is four
-// times what fits the GPU, so that CTAs are handed out as SMs free up (a grid of exactly the resident
-// CTAs lost 100 us per step whenever the plan kernel of the second stream held a few SMs at launch).
+// (dlb_set_option "gather_variant" = 2).  A CTA takes positions s = cta, cta + grid, ...; the launch code
+// sizes the grid so that a CTA moves about 450 KB of table rows.
 //   producer warp   lane l fetches the id of the l-th token that shares the position, lane 0 then
 //                   streams the positional-encoding row and the table rows of those tokens into a
 //                   ring of shared-memory stages with cp.async.bulk (completion on mbarriers);
@@ -522,11 +521,11 @@ int gather_typed(const void *table, const int32_t *ids, const float *pe, int seq
                 "embed_gather_fwd: seq_len=%d exceeds %d positions", seq_len, 65535 * bs.ty);
     DLB_REQUIRE(static_cast<int64_t>(num_tokens) + 16LL * stride_s < INT32_MAX, DLB_ERR_UNSUPPORTED,
                 "embed_gather_fwd: %d tokens at a stride of %d overflow the token index", num_tokens, stride_s);
-    // Which form: the bulk-copy pipeline for 2-byte storage when a row keeps all of its consumer threads
-    // busy (inside the block chain at V 32000 x D 4096: 74.5 against 77.5 us; with fp32 storage the rows in
-    // registers are faster, 131.7 against 136.3 us).  "gather_variant" 1 / 2 asks for one form.
+    // Which form: the bulk-copy pipeline when a row keeps all of its consumer threads busy (V 32000 x D 4096,
+    // each form alone: bf16, 8 x 4096 tokens, 71.7 against 80.1 us; fp32, 16 x 2048 tokens, 122.9 against
+    // 129.0 us).  "gather_variant" 1 / 2 asks for one form.
     const int want_form = get_option("gather_variant");
-    if (pe != nullptr && (want_form == 2 || (want_form == 0 && sizeof(T) == 2 && ncv >= kGatherConsumers))) {
+    if (pe != nullptr && (want_form == 2 || (want_form == 0 && ncv >= kGatherConsumers))) {
       const int ctas_per_sm = get_option("gather_bulk_ctas_per_sm") == 1 ? 1 : 2;
       const GatherBulkLayout L = gather_bulk_layout<T>(d, ctas_per_sm);
       unsigned int *timeouts = wait_timeouts_counter();
@@ -534,7 +533,17 @@ int gather_typed(const void *table, const int32_t *ids, const float *pe, int seq
         auto kern = embed_gather_bulk_kernel<T>;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L.total));
         DLB_REQUIRE(e == cudaSuccess, DLB_ERR_CUDA, "embed_gather_fwd: shared memory attribute: %s", cudaGetErrorString(e));
-        const int bgrid = min(stride_s, 4 * ctas_per_sm * sm_count());
+        // Grid: a CTA should move about 450 KB of table rows (measured best for both storage types: fewer,
+        // longer-lived CTAs pay for their start-up once, more of them even out the end of the kernel), and
+        // there should be at least as many CTAs as fit the GPU.  "gather_bulk_waves" sets the grid in units of
+        // the CTAs that fit instead.
+        const int resident = ctas_per_sm * sm_count();
+        const int64_t per_position = static_cast<int64_t>(ceil_div(num_tokens, stride_s)) * L.row_bytes;
+        const int positions_per_cta = static_cast<int>(std::max<int64_t>(1, (450 * 1024) / std::max<int64_t>(per_position, 1)));
+        int bgrid = std::max(ceil_div(stride_s, positions_per_cta), std::min(stride_s, resident));
+        const int waves = get_option("gather_bulk_waves");
+        if (waves >= 1 && waves <= 16) bgrid = waves * resident;
+        bgrid = std::min(bgrid, stride_s);
         launch_pdl(kern, bgrid, kGatherThreads, L.total, st, static_cast<const T *>(table), ids, pe, static_cast<T *>(out),
                    num_tokens, vocab, d, stride_s, L, timeouts);
         DLB_LAUNCH_CHECK("embed_gather_bulk");

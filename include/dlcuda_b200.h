@@ -68,6 +68,8 @@ DLB_API uint64_t dlb_launch_count(void);
  *   "gather_rows_in_flight"      4 | 8   table rows a thread loads before its first store
  *   "gather_variant"             1 rows in registers | 2 the bulk-copy (TMA) pipeline
  *   "gather_bulk_ctas_per_sm"    1 one CTA per SM with a deeper ring (default 2)
+ *   "gather_bulk_waves"          1..16: grid of the bulk-copy gather in units of the CTAs that fit the GPU
+ *                                (default: about 450 KB of table rows per CTA)
  *   "ln_bwd_pipe"                1 never the bulk-copy pipeline | 2 whenever the shape allows
  *   "ln_bwd_pipe_threads"        128 | 256 | 512 column threads per CTA
  *   "ln_bwd_pipe_ctas_per_sm"    1 | 2

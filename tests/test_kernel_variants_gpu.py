@@ -80,6 +80,7 @@ def test_scatter_bulk_form_edge_patterns(pattern):
 
 @pytest.mark.parametrize("form", [dict(gather_variant=1), dict(gather_variant=2),
                                   dict(gather_variant=2, gather_bulk_ctas_per_sm=1),
+                                  dict(gather_variant=2, gather_bulk_waves=1), dict(gather_variant=2, gather_bulk_waves=7),
                                   dict(gather_rows_in_flight=8)])
 @pytest.mark.parametrize("vocab,d,batch,seq,storage", [(2000, 4096, 5, 300, "bf16"), (2000, 4096, 3, 200, "fp32"),
                                                         (65, 64, 32, 64, "fp32"), (500, 1024, 9, 77, "bf16"),
