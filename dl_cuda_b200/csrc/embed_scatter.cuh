@@ -382,7 +382,7 @@ scatter_rows_kernel(const T *dy, const __grid_constant__ ScatterArgs a) {
 // of every row's additions is the one of scatter_rows_kernel: the two forms give the same bits.
 constexpr int kBulkConsumers = 256;
 constexpr int kBulkThreads = kBulkConsumers + 32;
-constexpr int kBulkJobs = 16;
+constexpr int kBulkJobs = 8;  // measured on B200 (V 32000 x D 4096, 32768 Zipf tokens, bf16): 32 -> 154.6, 16 -> 151, 8 -> 146.5, 4 -> 148.5 us
 
 struct ScatterBulkLayout {
   int stages;
@@ -661,8 +661,8 @@ int launch_scatter_rows(const void *dy, ScatterArgs a, int max_sub, int row_ctas
     a.skip_empty = 1;
   }
   // Which form: the bulk-copy pipeline where a dy row keeps all of its consumer threads busy (256 column
-  // vectors or more) and the plan is the dense one, whose CTAs each have 16 consecutive rows to work on
-  // (V 32000 x D 4096, 32768 Zipf tokens: 150 against 165 us with bf16 input, 192 against 216 us with
+  // vectors or more) and the plan is the dense one, whose CTAs each have 8 consecutive rows to work on
+  // (V 32000 x D 4096, 32768 Zipf tokens: 147 against 165 us with bf16 input, 190 against 216 us with
   // fp32); rows in registers otherwise.  "scatter_variant" 1 / 2 asks for one form.
   bool launched = false;
   const int want_form = get_option("scatter_variant");
