@@ -35,3 +35,27 @@ def test_traffic_follows_the_file(tmp_path, monkeypatch):
 def test_ops_without_a_capture_report_none():
     assert bench.ncu_traffic("allreduce", "bf16", 1024) is None
     assert bench.ncu_traffic("ln1_fwd", "fp32", 1024) is None
+
+
+def test_table_of_a_recorded_line(tmp_path, capsys):
+    """`python bench.py --table FILE` renders the chain ops and the kernel sweep of a recorded line."""
+    import json
+    line = {
+        "n_gpus": 1, "dtype": "bf16", "ms_per_step": 1.5, "value": 2.0e7, "value_min": 1.9e7, "value_max": 2.1e7,
+        "e2e": {"ms_per_step": 1.6, "value": 1.95e7}, "chain_gbs": 6000.0, "clocks": {"sm_mhz": 1965.0},
+        "roofline": {"peak": 6556.8},
+        "chain_ops": [{"op": "sort_tokens", "ms": 0.05, "bytes": 0, "gbs": None, "frac": None, "ncu_traffic": None},
+                      {"op": "ln1_fwd", "ms": 0.17, "bytes": 1000, "gbs": 6100.0, "frac": 0.93, "ncu_traffic": 900}],
+        "kernels_fp32": [{"kernel": "ln_bwd", "config": "65536x1024 fp32", "ms": 0.128, "gbs": 6300.0,
+                          "frac_measured": 0.96, "ref_ms": 7.1, "speedup_vs_ref": 55.5, "max_rel_err_vs_ref": 1.5e-5,
+                          "err_vs_fp64": {"dgamma": 9e-7}, "ref_err_vs_fp64": {"dgamma": 1.5e-5}},
+                         {"kernel": "embed_sort_tokens", "config": "T32768", "ms": 0.05, "gbs": None}],
+    }
+    path = tmp_path / "line.json"
+    path.write_text("noise\n" + json.dumps(line) + "\n")
+    bench.print_table(path)
+    out = capsys.readouterr().out
+    assert "| ln1_fwd | 0.1700 | 6100 | 0.930 | 0.90 |" in out
+    assert "| sort_tokens | 0.0500 | — | — | — |" in out
+    assert "| ln_bwd | 65536x1024 fp32 | 0.1280 | 6300 | 0.960 | 7.1000 | 55.50x | 1.5e-05 | 9e-07 / 1.5e-05 |" in out
+    assert "| embed_sort_tokens | T32768 | 0.0500 | — | — | — | — | — | — |" in out
