@@ -93,3 +93,22 @@ def test_shard_positions_covers_every_token_once():
         shard_positions(8, 4096, 3, 0)
     with pytest.raises(ValueError):
         shard_positions(8, 4096, 4, 4)
+
+
+def test_position_shards_reproduce_the_unsharded_forward():
+    """A rank that takes positions [first, first + n) of every sequence, with its n rows of the PE table and
+    seq_len = n, computes exactly the rows b * seq + first + p of the unsharded gather + PE output."""
+    from oracle import cpu as oracle
+    batch, seq, d, vocab = 3, 8, 12, 11
+    g = rng_for(78, 0)
+    table = (0.02 * g.standard_normal((vocab, d))).astype(np.float32)
+    ids = g.integers(0, vocab, batch * seq).astype(np.int32)
+    pe = oracle.pe_table(seq, d)
+    whole = oracle.embed_gather(table, ids, pe, seq).reshape(batch, seq, d)
+    for world in (1, 2, 4, 8):
+        for r in range(world):
+            first, n, rows = shard_positions(batch, seq, world, r)
+            local_ids = ids.reshape(batch, seq)[:, first:first + n].reshape(-1).copy()
+            out = oracle.embed_gather(table, local_ids, np.ascontiguousarray(pe[first:first + n]), n)
+            assert rows == local_ids.size
+            assert np.array_equal(out.reshape(batch, n, d), whole[:, first:first + n])
